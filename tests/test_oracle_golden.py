@@ -1,0 +1,86 @@
+"""The CPU oracle against fixtures produced by the reference's own source (tests/golden/make_golden.py).
+
+Tolerance is the reference's own: rtol = atol = 1e-3 (tpa/tpa_test.py:125,
+tpa/ring_tpa_test.py:138).  A tighter 2e-5 bound is also asserted because both
+sides are numpy evaluations of the same formulas.
+"""
+
+import numpy as np
+import pytest
+
+from conftest import load_golden
+from oracle import tpa_oracle as orc
+
+FWD = load_golden("fwd_matrix")
+RING = load_golden("ring_matrix")
+EXTRA = load_golden("extra")
+
+
+def _close(a, b, tight=2e-5):
+    np.testing.assert_allclose(a, b, rtol=1e-3, atol=1e-3, equal_nan=True)
+    assert np.array_equal(np.isnan(a), np.isnan(b))
+    assert np.nanmax(np.abs(a - b)) <= tight
+
+
+@pytest.mark.parametrize("case", sorted(FWD))
+def test_forward_matrix(case):
+    g = FWD[case]
+    seed, b, lq, lk, rq, rk, h, dk, dv, seg = (int(x) for x in g["meta"])
+    q, k, v = orc.make_factors(seed, b, lq, lk, rq, rk, h, dk, dv, dist="uniform")
+    qs = orc.segment_ids(b, lq, seg) if seg else None
+    ks = orc.segment_ids(b, lk, seg) if seg else None
+    o, l = orc.tpa_reference(q, k, v, h, qs, ks, return_lse=True)
+    _close(o, g["o"])
+    _close(l, g["lse"])
+    ob, lb = orc.tpa_fwd_blockwise(q, k, v, h, qs, ks)
+    _close(ob, g["o"])
+    _close(lb, g["lse"])
+
+
+@pytest.mark.parametrize("case", sorted(RING))
+def test_ring_matrix(case):
+    g = RING[case]
+    seed, b, lq, lk, rq, rk, h, dk, dv, seg, n = (int(x) for x in g["meta"])
+    q, k, v = orc.make_factors(seed, b, lq, lk, rq, rk, h, dk, dv, dist="uniform")
+    qs, ks = orc.segment_ids(b, lq, seg), orc.segment_ids(b, lk, seg)
+    o = orc.ring_tpa_reference(q, k, v, qs, ks, h, n)
+    _close(o, g["o"])
+    # non-causal: the ring equals the unsharded definition
+    _close(orc.tpa_reference(q, k, v, h, qs, ks), g["o"])
+
+
+@pytest.mark.parametrize("case", ["c0_causal", "causal_seg", "peaky", "empty_rows"])
+def test_untested_by_reference_forward(case):
+    g = EXTRA[case]
+    seed, b, lq, lk, rq, rk, h, dk, dv, sq, sk, causal, dist = (int(x) for x in g["meta"])
+    sm = float(g["sm_scale"])
+    q, k, v = orc.make_factors(seed, b, lq, lk, rq, rk, h, dk, dv, dist=["normal", "uniform"][dist])
+    qs = orc.segment_ids(b, lq, sq) if sq else None
+    ks = orc.segment_ids(b, lk, sk) if sk else None
+    o, l = orc.tpa_reference(q, k, v, h, qs, ks, sm_scale=sm, causal=bool(causal), return_lse=True)
+    _close(o, g["o"])
+    _close(l, g["lse"])
+    ob, lb = orc.tpa_fwd_blockwise(q, k, v, h, qs, ks, sm_scale=sm, causal=bool(causal))
+    _close(ob, g["o"])
+    _close(lb, g["lse"])
+    if case == "empty_rows":
+        assert np.isnan(g["o"]).any() and np.isneginf(g["lse"]).any()
+    # the torch variant used for large cases and the CPU baseline agrees too
+    ot = orc.tpa_reference_torch(q, k, v, h, qs, ks, sm_scale=sm, causal=bool(causal)).numpy()
+    _close(ot, g["o"], tight=1e-4)
+
+
+@pytest.mark.parametrize("case", ["ring_causal_n4", "ring_causal_n8_seg"])
+def test_ring_causal_is_shard_local_in_the_reference(case):
+    g = EXTRA[case]
+    seed, b, l, _, rq, rk, h, dk, dv, seg, n, causal = (int(x) for x in g["meta"])
+    sm = float(g["sm_scale"])
+    q, k, v = orc.make_factors(seed, b, l, l, rq, rk, h, dk, dv, dist="normal")
+    qs = orc.segment_ids(b, l, seg) if seg else np.zeros((b, l), np.int32)
+    o = orc.ring_tpa_reference(q, k, v, qs, qs, h, n, sm_scale=sm, causal=True,
+                               mask_mode="reference_local")
+    _close(o, g["o"])
+    # and global causal is a different function (it equals the unsharded causal forward)
+    og = orc.ring_tpa_reference(q, k, v, qs, qs, h, n, sm_scale=sm, causal=True, mask_mode="global")
+    _close(og, orc.tpa_reference(q, k, v, h, qs, qs, sm_scale=sm, causal=True), tight=1e-9)
+    assert np.nanmax(np.abs(og - g["o"])) > 1e-2
