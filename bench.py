@@ -1,0 +1,329 @@
+"""Benchmark of the TPA forward hot path.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload c0..c4]
+
+N = 1 runs the headline configuration (c2: bf16 causal B=1 T=32768 h=32 d=128 R 12/4/4)
+through tpa_fwd on one GPU.  N > 1 (under torchrun, one rank per GPU) runs the ring
+configuration (c3: bf16 causal B=1 T=131072 h=32 d=128 R 6/2/2) over contiguous length
+shards.  One step = one forward pass over the whole batch.  Rank 0 prints one JSON line.
+
+`value` is algorithmic attention TFLOP/s (4*B*h*d*pairs / time; pairs = T(T+1)/2 causal),
+tokens/s is reported beside it.  `e2e` is the same quantity through the public
+tpa_b200.tpa.tpa() call on pinned host arrays (host<->device copies inside the timing).
+`--impl reference` times the CPU oracle (a restatement of the reference's math; the
+reference itself needs jax, which is not installed) on the host cores instead.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (ROOT, os.path.join(ROOT, "tensor-product-attention-jax_b200")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import torch  # noqa: E402
+
+# name: (dtype, B, T, h, d, Rq, Rk, causal)
+WORKLOADS = {
+    "c0": ("f32", 1, 512, 8, 64, 6, 2, True),
+    "c1": ("bf16", 4, 4096, 32, 128, 6, 2, True),
+    "c2": ("bf16", 1, 32768, 32, 128, 12, 4, True),
+    "c3": ("bf16", 1, 131072, 32, 128, 6, 2, True),
+    "c4": ("bf16", 8, 2048, 16, 64, 8, 8, False),
+}
+METRIC = "TPA forward throughput (algorithmic attention FLOPs 4*B*h*d*pairs per second; tokens/s beside it)"
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
+# captures summarised under profiles/ (bytes; None until a capture for that workload exists)
+NCU_TRAFFIC = {}
+
+
+def flops(b, t, h, d, causal):
+    pairs = t * (t + 1) // 2 if causal else t * t
+    return 4.0 * b * h * d * pairs
+
+
+def peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            m = json.load(f)
+        return m["bf16_tflops"], m.get("bf16_tflops_sustained"), m["hbm_gbs"], "measured"
+    except (OSError, KeyError, ValueError):
+        return 1590.0, 1400.0, 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def make_inputs(name, device, shard=None, seed=0):
+    """Seeded synthetic factors with the configuration's shapes and distributions
+    (A ~ N(0,1), B ~ N(0,1)/sqrt(d)), in the reference's concatenated layout."""
+    dt, b, t, h, d, rq, rk, causal = WORKLOADS[name]
+    dtype = torch.float32 if dt == "f32" else torch.bfloat16
+    g = torch.Generator(device=device).manual_seed(1000 + seed)
+    def fac(r):
+        x = torch.randn((b, t, r, h + d), generator=g, device=device, dtype=torch.float32)
+        x[..., h:] *= d**-0.5
+        return x.to(dtype)
+    q, k, v = fac(rq), fac(rk), fac(rk)
+    if shard is not None:
+        rank, n = shard
+        per = t // n
+        q, k, v = (x[:, rank * per:(rank + 1) * per].contiguous() for x in (q, k, v))
+    return q, k, v
+
+
+def cpu_sample(name, max_rows=256):
+    """Bounded CPU sample of a workload: `max_rows` evenly spaced query rows against all keys,
+    which for a causal workload has the whole job's mean cost per token."""
+    import numpy as np
+    from oracle import tpa_oracle as orc
+
+    dt, b, t, h, d, rq, rk, causal = WORKLOADS[name]
+    q, k, v = orc.make_factors(2, b, t, t, rq, rk, h, d, d)
+    n = min(max_rows, t)
+    rows = torch.from_numpy(np.linspace(0, t - 1, n).round().astype(np.int64))
+    tq, tk, tv = (torch.from_numpy(x) for x in (q, k, v))
+    if dt == "bf16":
+        tq, tk, tv = (x.bfloat16().float() for x in (tq, tk, tv))
+    fl = 4.0 * b * h * d * float(((rows + 1) if causal else torch.full_like(rows, t)).sum())
+    run = lambda: orc.tpa_reference_torch(tq, tk, tv, h, sm_scale=d**-0.5, causal=causal, rows=rows)  # noqa: E731
+    return run, fl, b * n, f"{n} evenly spaced query rows of {name} against all {t} keys, torch fp32, {torch.get_num_threads()} threads"
+
+
+def time_cpu(name, steps, warmup):
+    run, fl, toks, sample = cpu_sample(name)
+    for _ in range(warmup):
+        run()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        run()
+    dt = (time.perf_counter() - t0) / steps
+    return fl / dt / 1e12, toks / dt, dt, sample
+
+
+def reference_arm(args, name):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps, warmup = min(args.steps, 3), min(args.warmup, 1)
+    tf, toks, dt, sample = time_cpu(name, steps, warmup)
+    dtn, b, t, h, d, rq, rk, causal = WORKLOADS[name]
+    cores = torch.get_num_threads()
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tf, "unit": "TFLOP/s", "tokens_per_s": toks,
+        "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": name, "shape": f"B{b} T{t} h{h} d{d} R{rq}/{rk}/{rk} causal={causal}",
+                   "note": "CPU oracle (restatement of the reference math); the reference itself needs jax, which is not installed"},
+        "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
+    ap.add_argument("--mask-mode", default="reference_local", choices=["reference_local", "global"])
+    ap.add_argument("--kernel", default="auto", choices=["auto", "simt", "sm100"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 0)
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    name = args.workload or ("c2" if world == 1 else "c3")
+    if args.impl == "reference":
+        return reference_arm(args, name)
+
+    import torch.distributed as dist
+    import tpa_b200
+    from tpa_b200 import _capi
+
+    assert torch.cuda.is_available(), "bench.py needs a GPU (no CPU path exists)"
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    dtn, b, t, h, d, rq, rk, causal = WORKLOADS[name]
+    sm_scale = d**-0.5
+    ring = world > 1
+    q, k, v = make_inputs(name, device, shard=(rank, world) if ring else None)
+    ids = torch.zeros((b, q.shape[1]), dtype=torch.int32, device=device) if ring else None
+
+    def step():
+        if ring:
+            return tpa_b200.ring_tpa.ring_tpa(q, k, v, ids, ids, None, h, sm_scale=sm_scale, causal=causal,
+                                              mask_mode=args.mask_mode)
+        return tpa_b200.tpa.fwd_device(q, k, v, h, None, None, sm_scale, causal, kernel=args.kernel)[0]
+
+    def sync():
+        torch.cuda.synchronize(device)
+        if ring:
+            dist.barrier()
+            torch.cuda.synchronize(device)
+
+    for _ in range(args.warmup):
+        step()
+    sync()
+    n0 = _capi.lib.tpa_launch_count()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    with ClockSampler(local_rank) as clocks:
+        sync()
+        ev[0].record()
+        for i in range(args.steps):
+            step()
+            ev[i + 1].record()
+        sync()
+    launches = _capi.lib.tpa_launch_count() - n0
+    total_ms = ev[0].elapsed_time(ev[-1])
+    per_step = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
+    if ring:
+        tt = torch.tensor([total_ms], device=device)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        total_ms = float(tt.item())
+    ms = total_ms / args.steps
+    fl = flops(b, t, h, d, causal)
+    value = fl / (ms * 1e-3) / 1e12
+    toks = b * t / (ms * 1e-3)
+
+    # ------------------------------------------------------------- end to end on pinned host arrays
+    e2e = None
+    if not args.no_e2e:
+        hq, hk, hv = (x.cpu().pin_memory() for x in (q, k, v))
+        hid = ids.cpu().pin_memory() if ring else None
+        out_host = torch.empty((b, q.shape[1], h, d), dtype=q.dtype).pin_memory()
+
+        def e2e_step():
+            dq, dk, dv_ = (x.to(device, non_blocking=True) for x in (hq, hk, hv))
+            if ring:
+                did = hid.to(device, non_blocking=True)
+                o = tpa_b200.ring_tpa.ring_tpa(dq, dk, dv_, did, did, None, h, sm_scale=sm_scale, causal=causal,
+                                               mask_mode=args.mask_mode)
+            else:
+                o = tpa_b200.tpa.tpa(dq, dk, dv_, num_heads=h, sm_scale=sm_scale, causal=causal)
+            out_host.copy_(o, non_blocking=True)
+
+        n_e2e = max(2, min(args.steps, 5))
+        e2e_step()
+        sync()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n_e2e):
+            e2e_step()
+        e1.record()
+        sync()
+        e_ms = e0.elapsed_time(e1) / n_e2e
+        if ring:
+            tt = torch.tensor([e_ms], device=device)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            e_ms = float(tt.item())
+        h2d = sum(x.numel() * x.element_size() for x in (hq, hk, hv)) + (hid.numel() * 4 if ring else 0)
+        e2e = {"value": fl / (e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "tokens_per_s": b * t / (e_ms * 1e-3),
+               "ms_per_step": e_ms, "h2d_bytes_per_step": h2d * world,
+               "d2h_bytes_per_step": out_host.numel() * out_host.element_size() * world}
+
+    if rank != 0:
+        if ring:
+            dist.destroy_process_group()
+        return
+
+    burst, sustained, hbm, src = peaks()
+    info = tpa_b200.tpa.query_kernel(q, k, v, h, kernel=args.kernel, causal=causal, segments=ring)
+    # the dominant (only) kernel of a step; at N > 1 every rank runs `world` launches per step
+    kernel_ms = statistics.median(per_step) / (world if ring else 1)
+    fl_launch = fl / (world * world) if ring else fl
+    achieved = fl_launch / (kernel_ms * 1e-3) / 1e12
+    roofline = {"bound": "tensor", "achieved": achieved, "peak": burst, "unit": "TFLOP/s", "frac": achieved / burst,
+                "frac_of_sustained": achieved / sustained if sustained else None, "peak_source": src,
+                "traffic": NCU_TRAFFIC.get(name), "kernel": info["kernel"],
+                "hbm_algorithmic_bytes": sum(x.numel() * x.element_size() for x in (q, k, v))
+                + b * q.shape[1] * h * d * q.element_size() + b * q.shape[1] * h * 4,
+                "hbm_peak_gbs": hbm}
+    cpu = None
+    if not args.no_cpu_baseline and world == 1:
+        tf, ctoks, cdt, sample = time_cpu(name, 1, 0)
+        cpu = {"value": tf, "unit": "TFLOP/s", "tokens_per_s": ctoks, "cores": torch.get_num_threads(), "kind": "port",
+               "sample": sample}
+    line = {
+        "metric": METRIC, "value": value, "unit": "TFLOP/s", "tokens_per_s": toks, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": dtn, "data": "synthetic",
+        "config": {"workload": name, "shape": f"B{b} T{t} h{h} d{d} R{rq}/{rk}/{rk} causal={causal}",
+                   "parallelism": f"ring sp{world} ({args.mask_mode} causal mask)" if ring else "single GPU",
+                   "l2": "inputs + outputs larger than L2 (no flush needed)" if name in ("c1", "c2", "c3") else "smaller than L2, not flushed",
+                   "kernel": info},
+        "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks.summary(),
+    }
+    print(json.dumps(line), flush=True)
+    if ring:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,130 @@
+/*
+ * tpa_b200.h — C ABI of libtpa_b200.so: Tensor Product Attention forward on B200 (sm_100a).
+ *
+ * The reference (jondeaton/tensor-product-attention-jax) has no FFI of its own; its
+ * narrowest seam is the Pallas custom call in tpa/tpa.py:492-543,
+ *
+ *     (qa, qb, ka, kb, va, vb, q_segment_ids | None, kv_segment_ids | None) -> (o, lse)
+ *
+ * vmapped over batch by tpa/tpa.py:144-163 and tpa/ring_tpa.py:242-255.  The entry
+ * points below are what a jax.ffi (or ctypes / cffi) binding for that seam binds.
+ * Everything is plain C: pointers, sizes, element strides.  All pointers are device
+ * pointers unless stated otherwise; every call only enqueues work on `stream`
+ * (a cudaStream_t passed as void*) and returns without synchronising.  The library
+ * never allocates device memory in these calls: outputs and workspace are the caller's.
+ */
+#ifndef TPA_B200_H_
+#define TPA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TPA_B200_ABI_VERSION 1
+
+/* Status codes.  0 = success; negative = the call did nothing. */
+enum {
+  TPA_OK = 0,
+  TPA_ERR_BAD_ARG = -1,      /* null pointer, non-positive size, wrong struct_size            */
+  TPA_ERR_UNSUPPORTED = -2,  /* shape/dtype outside what any kernel here handles               */
+  TPA_ERR_WORKSPACE = -3,    /* workspace missing or smaller than tpa_fwd_workspace_bytes()    */
+  TPA_ERR_CUDA = -4,         /* a CUDA runtime call failed (see tpa_last_cuda_error)           */
+  TPA_ERR_KERNEL_FORCED = -5,/* args->kernel forces a kernel that cannot run this shape        */
+  TPA_ERR_DEVICE_TIMEOUT = -6/* a bounded device-side wait ran out (read via tpa_read_status)  */
+};
+
+enum { TPA_DTYPE_F32 = 0, TPA_DTYPE_BF16 = 1 };
+
+/* Which kernel runs.  AUTO picks SM100 when the shape allows, else SIMT. */
+enum { TPA_KERNEL_AUTO = 0, TPA_KERNEL_SIMT = 1, TPA_KERNEL_SM100 = 2 };
+
+/* flags */
+enum {
+  TPA_FLAG_CAUSAL = 1,      /* keep key j for query i iff i + q_offset >= j + k_offset
+                               (tpa/tpa.py:376-379 with both offsets 0)                        */
+  TPA_FLAG_STATE_LOAD = 2,  /* start from the partial result in state_o / state_lse
+                               (the carry of tpa/ring_tpa.py:69-71) instead of (0, -inf)       */
+  TPA_FLAG_STATE_STORE = 4  /* write the merged partial back to state_o / state_lse
+                               (tpa/ring_tpa.py:82-91) instead of the final o / lse            */
+};
+
+/* One factor operand: `ptr[b*stride[0] + l*stride[1] + r*stride[2] + c]`, c contiguous.
+ * The reference passes the concatenated arrays q[b,l,r,h+d]; A = base, B = base + h
+ * (tpa/tpa.py:477-479), both with stride {l*r*(h+d), r*(h+d), h+d} — zero copy. */
+typedef struct TpaFactor {
+  const void* ptr;
+  int64_t stride[3]; /* elements: batch, row (token), rank */
+} TpaFactor;
+
+/* Replaces the operand list of the custom call at tpa/tpa.py:492-543 (plus the batch
+ * vmap of tpa/tpa.py:144-163).  Zero-initialise, then fill. */
+typedef struct TpaFwdArgs {
+  uint32_t struct_size; /* = sizeof(TpaFwdArgs) */
+  int32_t dtype;        /* TPA_DTYPE_*: element type of the factors and of `o`            */
+  int32_t batch, lq, lk;
+  int32_t rank_q, rank_k; /* rank of v must equal rank of k (tpa/tpa.py:474-475)           */
+  int32_t heads, dk, dv;
+  TpaFactor qa, qb;     /* [batch, lq, rank_q, heads], [batch, lq, rank_q, dk]             */
+  TpaFactor ka, kb;     /* [batch, lk, rank_k, heads], [batch, lk, rank_k, dk]             */
+  TpaFactor va, vb;     /* [batch, lk, rank_k, heads], [batch, lk, rank_k, dv]             */
+  const int32_t* q_segment_ids;  /* [batch, lq] or NULL                                    */
+  const int32_t* kv_segment_ids; /* [batch, lk] or NULL; both or neither (tpa/tpa.py:369-371) */
+  int64_t q_segment_batch_stride;  /* elements; 0 = one row shared by the batch            */
+  int64_t kv_segment_batch_stride;
+  void* o;              /* [batch, lq, heads, dv] contiguous, dtype; rows with no visible
+                           key are NaN (tpa/tpa.py:439).  Unused with STATE_STORE.         */
+  float* lse;           /* [batch, lq, heads] fp32 natural-log LSE of the scaled masked
+                           logits (tpa/tpa.py:443), -inf for empty rows; may be NULL       */
+  float* state_o;       /* [batch, lq, heads, dv] fp32 normalised partial output           */
+  float* state_lse;     /* [batch, lq, heads] fp32 partial LSE                             */
+  float sm_scale;       /* tpa/tpa.py:367                                                  */
+  uint32_t flags;       /* TPA_FLAG_*                                                      */
+  int64_t q_offset, k_offset; /* global positions of local row 0 (causal comparison only)  */
+  int32_t kernel;       /* TPA_KERNEL_*                                                    */
+  int32_t reserved;
+} TpaFwdArgs;
+
+typedef struct TpaKernelInfo {
+  int32_t kernel;       /* TPA_KERNEL_SIMT or TPA_KERNEL_SM100                             */
+  int32_t block_q, block_kv; /* tile sizes the kernel will use                             */
+  int32_t threads;      /* threads per CTA                                                 */
+  int32_t grid[3];
+  int32_t smem_bytes;   /* dynamic shared memory per CTA                                   */
+  int32_t launches;     /* kernel launches one tpa_fwd call makes for these arguments      */
+} TpaKernelInfo;
+
+/* Forward pass.  Replaces pl.pallas_call(_fwd_kernel ...) at tpa/tpa.py:492-543 for the
+ * whole batch.  `workspace` must hold tpa_fwd_workspace_bytes(args) bytes (may be NULL
+ * when that is 0) and be 256-byte aligned; its first 16 bytes are a device status block
+ * (see tpa_read_status). */
+int tpa_fwd(const TpaFwdArgs* args, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Bytes of scratch the call above needs for these arguments (0 is possible). */
+size_t tpa_fwd_workspace_bytes(const TpaFwdArgs* args);
+
+/* Which kernel, tiles and grid tpa_fwd would use; TPA_OK or the error tpa_fwd would return. */
+int tpa_query_kernel(const TpaFwdArgs* args, TpaKernelInfo* info);
+
+/* Synchronises `stream`, reads the status block at the start of `workspace` and returns
+ * TPA_OK or TPA_ERR_DEVICE_TIMEOUT.  `detail` (host, may be NULL) receives the raw
+ * device words {flag, where, block, spins}. */
+int tpa_read_status(const void* workspace, void* stream, uint32_t detail[4]);
+
+/* Human-readable text for a status code (static storage). */
+const char* tpa_status_string(int status);
+
+/* Text of the last CUDA error this library saw on the calling thread (static storage). */
+const char* tpa_last_cuda_error(void);
+
+/* Number of kernel launches this library has issued in this process. */
+uint64_t tpa_launch_count(void);
+
+int tpa_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TPA_B200_H_ */

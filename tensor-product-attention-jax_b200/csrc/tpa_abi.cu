@@ -1,0 +1,154 @@
+// C ABI of libtpa_b200.so: argument validation, kernel choice, status reporting.
+// Declarations and the reference interfaces they replace are in include/tpa_b200.h.
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+
+#include "tpa_common.cuh"
+
+namespace tpa {
+
+static std::atomic<uint64_t> g_launches{0};
+static thread_local char g_cuda_error[256] = "";
+
+void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
+
+static int fail_cuda(cudaError_t e) {
+  std::snprintf(g_cuda_error, sizeof(g_cuda_error), "%s: %s", cudaGetErrorName(e),
+                cudaGetErrorString(e));
+  return TPA_ERR_CUDA;
+}
+
+static bool factor_ok(const TpaFactor& f) {
+  return f.ptr != nullptr && f.stride[1] > 0 && f.stride[2] > 0 && f.stride[0] >= 0;
+}
+
+// Mirrors the checks the reference makes at trace time (tpa/tpa.py:474-475, 369-371) plus
+// what a C caller can get wrong.
+static int validate(const TpaFwdArgs* a, Params* p) {
+  if (a == nullptr || a->struct_size != sizeof(TpaFwdArgs)) return TPA_ERR_BAD_ARG;
+  if (a->dtype != TPA_DTYPE_F32 && a->dtype != TPA_DTYPE_BF16) return TPA_ERR_UNSUPPORTED;
+  if (a->batch <= 0 || a->lq <= 0 || a->lk <= 0 || a->rank_q <= 0 || a->rank_k <= 0 ||
+      a->heads <= 0 || a->dk <= 0 || a->dv <= 0)
+    return TPA_ERR_BAD_ARG;
+  if (!factor_ok(a->qa) || !factor_ok(a->qb) || !factor_ok(a->ka) || !factor_ok(a->kb) ||
+      !factor_ok(a->va) || !factor_ok(a->vb))
+    return TPA_ERR_BAD_ARG;
+  if ((a->q_segment_ids == nullptr) != (a->kv_segment_ids == nullptr)) return TPA_ERR_BAD_ARG;
+  const bool store = (a->flags & TPA_FLAG_STATE_STORE) != 0;
+  const bool load = (a->flags & TPA_FLAG_STATE_LOAD) != 0;
+  if ((store || load) && (a->state_o == nullptr || a->state_lse == nullptr)) return TPA_ERR_BAD_ARG;
+  if (!store && a->o == nullptr) return TPA_ERR_BAD_ARG;
+  if (a->flags & ~(uint32_t)(TPA_FLAG_CAUSAL | TPA_FLAG_STATE_LOAD | TPA_FLAG_STATE_STORE))
+    return TPA_ERR_BAD_ARG;
+  if (a->kernel < TPA_KERNEL_AUTO || a->kernel > TPA_KERNEL_SM100) return TPA_ERR_BAD_ARG;
+  if (a->heads > 65535 || a->batch > 65535) return TPA_ERR_UNSUPPORTED;
+  if (a->dk > 256 || a->dv > 256) return TPA_ERR_UNSUPPORTED;
+  p->dtype = a->dtype;
+  p->batch = a->batch; p->lq = a->lq; p->lk = a->lk;
+  p->rank_q = a->rank_q; p->rank_k = a->rank_k;
+  p->heads = a->heads; p->dk = a->dk; p->dv = a->dv;
+  p->qa = a->qa; p->qb = a->qb; p->ka = a->ka; p->kb = a->kb; p->va = a->va; p->vb = a->vb;
+  p->q_seg = a->q_segment_ids; p->kv_seg = a->kv_segment_ids;
+  p->q_seg_bstride = a->q_segment_batch_stride; p->kv_seg_bstride = a->kv_segment_batch_stride;
+  p->o = a->o; p->lse = a->lse; p->state_o = a->state_o; p->state_lse = a->state_lse;
+  p->sm_scale = a->sm_scale; p->flags = a->flags;
+  p->q_offset = a->q_offset; p->k_offset = a->k_offset;
+  p->status = nullptr;
+  return TPA_OK;
+}
+
+static int choose(const TpaFwdArgs* a, const Params& p, int* kernel) {
+  const bool tc = sm100_supported(p);
+  if (a->kernel == TPA_KERNEL_SM100 && !tc) return TPA_ERR_KERNEL_FORCED;
+  *kernel = (a->kernel == TPA_KERNEL_SIMT || !tc) ? TPA_KERNEL_SIMT : TPA_KERNEL_SM100;
+  return TPA_OK;
+}
+
+constexpr size_t kStatusBytes = 256;  // status block at the head of every non-empty workspace
+
+}  // namespace tpa
+
+using namespace tpa;
+
+extern "C" {
+
+int tpa_abi_version(void) { return TPA_B200_ABI_VERSION; }
+
+uint64_t tpa_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+const char* tpa_last_cuda_error(void) { return g_cuda_error; }
+
+const char* tpa_status_string(int status) {
+  switch (status) {
+    case TPA_OK: return "ok";
+    case TPA_ERR_BAD_ARG: return "bad argument (null pointer, non-positive size, segment ids given for only one side, or wrong struct_size)";
+    case TPA_ERR_UNSUPPORTED: return "unsupported shape or dtype (dtype must be f32/bf16; dk, dv <= 256; heads, batch <= 65535)";
+    case TPA_ERR_WORKSPACE: return "workspace missing, misaligned or smaller than tpa_fwd_workspace_bytes()";
+    case TPA_ERR_CUDA: return "CUDA runtime error (see tpa_last_cuda_error)";
+    case TPA_ERR_KERNEL_FORCED: return "the forced kernel cannot run this shape";
+    case TPA_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait ran out";
+    default: return "unknown status";
+  }
+}
+
+size_t tpa_fwd_workspace_bytes(const TpaFwdArgs* args) {
+  Params p;
+  int kernel;
+  if (validate(args, &p) != TPA_OK || choose(args, p, &kernel) != TPA_OK) return 0;
+  if (kernel != TPA_KERNEL_SM100) return 0;
+  return kStatusBytes + sm100_workspace_bytes(p);
+}
+
+int tpa_query_kernel(const TpaFwdArgs* args, TpaKernelInfo* info) {
+  if (info == nullptr) return TPA_ERR_BAD_ARG;
+  std::memset(info, 0, sizeof(*info));
+  Params p;
+  int kernel;
+  int st = validate(args, &p);
+  if (st != TPA_OK) return st;
+  st = choose(args, p, &kernel);
+  if (st != TPA_OK) return st;
+  cudaError_t e = (kernel == TPA_KERNEL_SM100) ? launch_sm100(p, nullptr, info, true, nullptr)
+                                               : launch_simt(p, info, true, nullptr);
+  return e == cudaSuccess ? TPA_OK : fail_cuda(e);
+}
+
+int tpa_fwd(const TpaFwdArgs* args, void* workspace, size_t workspace_bytes, void* stream) {
+  Params p;
+  int kernel;
+  int st = validate(args, &p);
+  if (st != TPA_OK) return st;
+  st = choose(args, p, &kernel);
+  if (st != TPA_OK) return st;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t e;
+  if (kernel == TPA_KERNEL_SM100) {
+    const size_t need = kStatusBytes + sm100_workspace_bytes(p);
+    if (workspace == nullptr || workspace_bytes < need ||
+        (reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
+      return TPA_ERR_WORKSPACE;
+    p.status = static_cast<uint32_t*>(workspace);
+    e = cudaMemsetAsync(workspace, 0, kStatusBytes, s);
+    if (e != cudaSuccess) return fail_cuda(e);
+    e = launch_sm100(p, static_cast<char*>(workspace) + kStatusBytes, nullptr, false, s);
+  } else {
+    e = launch_simt(p, nullptr, false, s);
+  }
+  return e == cudaSuccess ? TPA_OK : fail_cuda(e);
+}
+
+int tpa_read_status(const void* workspace, void* stream, uint32_t detail[4]) {
+  uint32_t host[4] = {0, 0, 0, 0};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaStreamSynchronize(s);
+  if (e != cudaSuccess) return fail_cuda(e);
+  if (workspace != nullptr) {
+    e = cudaMemcpy(host, workspace, sizeof(host), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return fail_cuda(e);
+  }
+  if (detail != nullptr) std::memcpy(detail, host, sizeof(host));
+  return host[0] == 0 ? TPA_OK : TPA_ERR_DEVICE_TIMEOUT;
+}
+
+}  // extern "C"

@@ -1,0 +1,46 @@
+// Internal declarations shared by the translation units of libtpa_b200.so.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "tpa_b200.h"
+
+namespace tpa {
+
+// Device-side view of one forward call (validated copy of TpaFwdArgs).
+struct Params {
+  int dtype;
+  int batch, lq, lk, rank_q, rank_k, heads, dk, dv;
+  TpaFactor qa, qb, ka, kb, va, vb;
+  const int32_t* q_seg;
+  const int32_t* kv_seg;
+  int64_t q_seg_bstride, kv_seg_bstride;
+  void* o;
+  float* lse;
+  float* state_o;
+  float* state_lse;
+  float sm_scale;
+  uint32_t flags;
+  int64_t q_offset, k_offset;
+  uint32_t* status;  // device status block {flag, where, block, spins} or nullptr
+};
+
+// Launchers: enqueue on `stream`, return a cudaError_t.  `info` is filled either way.
+cudaError_t launch_simt(const Params& p, TpaKernelInfo* info, bool dry_run, cudaStream_t stream);
+bool sm100_supported(const Params& p);
+size_t sm100_workspace_bytes(const Params& p);
+cudaError_t launch_sm100(const Params& p, void* workspace, TpaKernelInfo* info, bool dry_run,
+                         cudaStream_t stream);
+
+void count_launch(int n);
+
+__device__ __forceinline__ float to_float(float x) { return x; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
+__device__ __forceinline__ void from_float(float& dst, float x) { dst = x; }
+__device__ __forceinline__ void from_float(__nv_bfloat16& dst, float x) {
+  dst = __float2bfloat16_rn(x);
+}
+
+}  // namespace tpa

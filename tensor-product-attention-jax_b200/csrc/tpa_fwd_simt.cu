@@ -1,0 +1,265 @@
+// Generic fp32-math TPA forward (any lq, lk, heads, dk, dv <= 256, any ranks; fp32 or bf16 I/O).
+//
+// Replaces _fwd_kernel (tpa/tpa.py:245-443) for shapes / precisions the tensor-core kernel
+// does not take: one CTA owns 32 query rows of one head of one batch element, walks the
+// key/value rows 64 at a time, rebuilds the K and V tiles of its head from the rank factors
+// (tpa/tpa.py:364,417), and keeps a running (max, sum, accumulator) per query row.  The
+// reference keeps `o` normalised and carries the LSE (tpa/tpa.py:389-424); running
+// max / sum is the same function evaluated with one division at the end.
+//
+// Each warp owns 4 whole query rows, so row reductions are warp shuffles and no two warps
+// ever touch the same row: results are bitwise reproducible run to run.
+#include <math_constants.h>
+
+#include "tpa_common.cuh"
+
+namespace tpa {
+
+constexpr int SIMT_BQ = 32;
+constexpr int SIMT_BK = 64;
+constexpr int SIMT_THREADS = 256;
+constexpr int SIMT_RPW = 4;  // rows per warp
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+template <typename T>
+__device__ __forceinline__ void rebuild_tile(float* dst, int ld, int rows, int row0, int row_end,
+                                             int cols, const T* a, const int64_t* as,
+                                             const T* bfac, const int64_t* bs, int rank, int h,
+                                             float inv_rank, int tid) {
+  // dst[r][t] = inv_rank * sum_rho a[row0+r, rho, h] * b[row0+r, rho, t]; zero past row_end/cols.
+  for (int idx = tid; idx < rows * ld; idx += SIMT_THREADS) {
+    const int r = idx / ld, t = idx - r * ld;
+    const int row = row0 + r;
+    float acc = 0.f;
+    if (row < row_end && t < cols) {
+      const T* ap = a + (int64_t)row * as[1] + h;
+      const T* bp = bfac + (int64_t)row * bs[1] + t;
+      for (int rho = 0; rho < rank; ++rho)
+        acc = fmaf(to_float(ap[rho * as[2]]), to_float(bp[rho * bs[2]]), acc);
+    }
+    dst[idx] = acc * inv_rank;
+  }
+}
+
+template <typename T, int JJ>
+__global__ void __launch_bounds__(SIMT_THREADS)
+tpa_fwd_simt_kernel(const Params p) {
+  extern __shared__ float smem[];
+  const int dk = p.dk, dv = p.dv;
+  const int ldk = dk + 1;       // +1: rows of K land in different banks
+  constexpr int ldv = JJ * 32;  // V rows padded to the lane grid, pad is zero
+  float* Qs = smem;                     // [BQ][ldk]
+  float* Ks = Qs + SIMT_BQ * ldk;       // [BK][ldk]
+  float* Vs = Ks + SIMT_BK * ldk;       // [BK][ldv]
+  float* Ps = Vs + SIMT_BK * ldv;       // [BQ][BK]
+  int* ksegs = reinterpret_cast<int*>(Ps + SIMT_BQ * SIMT_BK);  // [BK]
+
+  const int q0 = blockIdx.x * SIMT_BQ, h = blockIdx.y, b = blockIdx.z;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const bool causal = (p.flags & TPA_FLAG_CAUSAL) != 0;
+  const bool has_seg = p.q_seg != nullptr;
+  const bool load_state = (p.flags & TPA_FLAG_STATE_LOAD) != 0;
+  const bool store_state = (p.flags & TPA_FLAG_STATE_STORE) != 0;
+
+  const T* qa = static_cast<const T*>(p.qa.ptr) + (int64_t)b * p.qa.stride[0];
+  const T* qb = static_cast<const T*>(p.qb.ptr) + (int64_t)b * p.qb.stride[0];
+  const T* ka = static_cast<const T*>(p.ka.ptr) + (int64_t)b * p.ka.stride[0];
+  const T* kb = static_cast<const T*>(p.kb.ptr) + (int64_t)b * p.kb.stride[0];
+  const T* va = static_cast<const T*>(p.va.ptr) + (int64_t)b * p.va.stride[0];
+  const T* vb = static_cast<const T*>(p.vb.ptr) + (int64_t)b * p.vb.stride[0];
+  const int32_t* qseg_g = has_seg ? p.q_seg + (int64_t)b * p.q_seg_bstride : nullptr;
+  const int32_t* kseg_g = has_seg ? p.kv_seg + (int64_t)b * p.kv_seg_bstride : nullptr;
+
+  rebuild_tile<T>(Qs, ldk, SIMT_BQ, q0, p.lq, dk, qa, p.qa.stride, qb, p.qb.stride, p.rank_q, h,
+                  1.f / (float)p.rank_q, tid);
+
+  float m[SIMT_RPW], l[SIMT_RPW], acc[SIMT_RPW][JJ];
+  int qseg[SIMT_RPW];
+  int64_t qpos[SIMT_RPW];
+#pragma unroll
+  for (int i = 0; i < SIMT_RPW; ++i) {
+    const int row = q0 + warp * SIMT_RPW + i;
+    const bool live = row < p.lq;
+    qpos[i] = (int64_t)row + p.q_offset;
+    qseg[i] = (has_seg && live) ? qseg_g[row] : 0;
+    m[i] = -CUDART_INF_F;
+    l[i] = 0.f;
+#pragma unroll
+    for (int jj = 0; jj < JJ; ++jj) acc[i][jj] = 0.f;
+    if (load_state && live) {
+      const int64_t rh = ((int64_t)b * p.lq + row) * p.heads + h;
+      const float prev = p.state_lse[rh];
+      if (prev != -CUDART_INF_F) {
+        m[i] = prev;
+        l[i] = 1.f;
+#pragma unroll
+        for (int jj = 0; jj < JJ; ++jj) {
+          const int j = lane + 32 * jj;
+          if (j < dv) acc[i][jj] = p.state_o[rh * dv + j];
+        }
+      }
+    }
+  }
+
+  // Tiles wholly above the causal diagonal are never visited (tpa/tpa.py:427-428).
+  int n_tiles = (p.lk + SIMT_BK - 1) / SIMT_BK;
+  if (causal) {
+    const int64_t kmax = (int64_t)q0 + SIMT_BQ - 1 + p.q_offset - p.k_offset;  // last visible local key
+    if (kmax < 0) n_tiles = 0;
+    else if (kmax / SIMT_BK + 1 < n_tiles) n_tiles = (int)(kmax / SIMT_BK) + 1;
+  }
+
+  const float inv_rk = 1.f / (float)p.rank_k;
+  for (int tile = 0; tile < n_tiles; ++tile) {
+    const int k0 = tile * SIMT_BK;
+    __syncthreads();  // everyone is done with the previous K/V/P tiles (and Q is written)
+    rebuild_tile<T>(Ks, ldk, SIMT_BK, k0, p.lk, dk, ka, p.ka.stride, kb, p.kb.stride, p.rank_k, h,
+                    inv_rk, tid);
+    rebuild_tile<T>(Vs, ldv, SIMT_BK, k0, p.lk, dv, va, p.va.stride, vb, p.vb.stride, p.rank_k, h,
+                    inv_rk, tid);
+    if (has_seg && tid < SIMT_BK) ksegs[tid] = (k0 + tid < p.lk) ? kseg_g[k0 + tid] : 0;
+    __syncthreads();
+
+    // logits: this lane owns key columns `lane` and `lane + 32` of the 4 rows of its warp
+    float s[SIMT_RPW][2];
+#pragma unroll
+    for (int i = 0; i < SIMT_RPW; ++i) s[i][0] = s[i][1] = 0.f;
+    const float* k0p = Ks + lane * ldk;
+    const float* k1p = Ks + (lane + 32) * ldk;
+    const float* qp = Qs + warp * SIMT_RPW * ldk;
+    for (int t = 0; t < dk; ++t) {
+      const float ka0 = k0p[t], ka1 = k1p[t];
+#pragma unroll
+      for (int i = 0; i < SIMT_RPW; ++i) {
+        const float qv = qp[i * ldk + t];
+        s[i][0] = fmaf(qv, ka0, s[i][0]);
+        s[i][1] = fmaf(qv, ka1, s[i][1]);
+      }
+    }
+
+#pragma unroll
+    for (int i = 0; i < SIMT_RPW; ++i) {
+      float x[2];
+      bool keep[2];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const int kc = k0 + lane + 32 * c;
+        keep[c] = kc < p.lk;
+        if (causal) keep[c] = keep[c] && (qpos[i] >= (int64_t)kc + p.k_offset);
+        if (has_seg) keep[c] = keep[c] && (qseg[i] == ksegs[lane + 32 * c]);
+        x[c] = keep[c] ? s[i][c] * p.sm_scale : -CUDART_INF_F;
+      }
+      const float tmax = warp_max(fmaxf(x[0], x[1]));
+      const float m_new = fmaxf(m[i], tmax);
+      float p0 = 0.f, p1 = 0.f, corr = 1.f;
+      if (m_new != -CUDART_INF_F) {
+        corr = (m[i] == -CUDART_INF_F) ? 0.f : expf(m[i] - m_new);
+        p0 = keep[0] ? expf(x[0] - m_new) : 0.f;
+        p1 = keep[1] ? expf(x[1] - m_new) : 0.f;
+      }
+      const float psum = warp_sum(p0 + p1);
+      l[i] = l[i] * corr + psum;
+      m[i] = m_new;
+#pragma unroll
+      for (int jj = 0; jj < JJ; ++jj) acc[i][jj] *= corr;
+      Ps[(warp * SIMT_RPW + i) * SIMT_BK + lane] = p0;
+      Ps[(warp * SIMT_RPW + i) * SIMT_BK + lane + 32] = p1;
+    }
+    __syncwarp();
+
+    // acc += P V : this lane owns value columns lane + 32*jj
+    const float* pp = Ps + warp * SIMT_RPW * SIMT_BK;
+    for (int c = 0; c < SIMT_BK; ++c) {
+      float vv[JJ];
+#pragma unroll
+      for (int jj = 0; jj < JJ; ++jj) vv[jj] = Vs[c * ldv + lane + 32 * jj];
+#pragma unroll
+      for (int i = 0; i < SIMT_RPW; ++i) {
+        const float pv = pp[i * SIMT_BK + c];
+#pragma unroll
+        for (int jj = 0; jj < JJ; ++jj) acc[i][jj] = fmaf(pv, vv[jj], acc[i][jj]);
+      }
+    }
+  }
+
+#pragma unroll
+  for (int i = 0; i < SIMT_RPW; ++i) {
+    const int row = q0 + warp * SIMT_RPW + i;
+    if (row >= p.lq) continue;
+    const int64_t rh = ((int64_t)b * p.lq + row) * p.heads + h;
+    const bool empty = !(l[i] > 0.f);
+    const float inv = empty ? 0.f : 1.f / l[i];
+    const float lse = empty ? -CUDART_INF_F : m[i] + logf(l[i]);
+    if (store_state) {
+      // partial result for the next ring step: 0 / -inf where nothing was visible yet
+      // (the nan_to_num of tpa/ring_tpa.py:85-89)
+#pragma unroll
+      for (int jj = 0; jj < JJ; ++jj) {
+        const int j = lane + 32 * jj;
+        if (j < dv) p.state_o[rh * dv + j] = acc[i][jj] * inv;
+      }
+      if (lane == 0) p.state_lse[rh] = lse;
+    } else {
+      T* op = static_cast<T*>(p.o) + rh * dv;
+#pragma unroll
+      for (int jj = 0; jj < JJ; ++jj) {
+        const int j = lane + 32 * jj;
+        // rows that saw no key are NaN (tpa/tpa.py:439, tpa/ring_tpa.py:109)
+        if (j < dv) from_float(op[j], empty ? CUDART_NAN_F : acc[i][jj] * inv);
+      }
+      if (lane == 0 && p.lse != nullptr) p.lse[rh] = lse;
+    }
+  }
+}
+
+template <typename T, int JJ>
+static cudaError_t launch_one(const Params& p, TpaKernelInfo* info, bool dry_run,
+                              cudaStream_t stream) {
+  const int ldk = p.dk + 1, ldv = JJ * 32;
+  const size_t smem = sizeof(float) * ((size_t)SIMT_BQ * ldk + (size_t)SIMT_BK * ldk +
+                                       (size_t)SIMT_BK * ldv + SIMT_BQ * SIMT_BK + SIMT_BK);
+  dim3 grid((p.lq + SIMT_BQ - 1) / SIMT_BQ, p.heads, p.batch);
+  if (info) {
+    info->kernel = TPA_KERNEL_SIMT;
+    info->block_q = SIMT_BQ;
+    info->block_kv = SIMT_BK;
+    info->threads = SIMT_THREADS;
+    info->grid[0] = grid.x;
+    info->grid[1] = grid.y;
+    info->grid[2] = grid.z;
+    info->smem_bytes = (int)smem;
+    info->launches = 1;
+  }
+  if (dry_run) return cudaSuccess;
+  auto kern = tpa_fwd_simt_kernel<T, JJ>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  kern<<<grid, SIMT_THREADS, smem, stream>>>(p);
+  count_launch(1);
+  return cudaGetLastError();
+}
+
+template <typename T>
+static cudaError_t launch_t(const Params& p, TpaKernelInfo* info, bool dry, cudaStream_t s) {
+  if (p.dv <= 32) return launch_one<T, 1>(p, info, dry, s);
+  if (p.dv <= 64) return launch_one<T, 2>(p, info, dry, s);
+  if (p.dv <= 128) return launch_one<T, 4>(p, info, dry, s);
+  return launch_one<T, 8>(p, info, dry, s);
+}
+
+cudaError_t launch_simt(const Params& p, TpaKernelInfo* info, bool dry_run, cudaStream_t stream) {
+  if (p.dtype == TPA_DTYPE_F32) return launch_t<float>(p, info, dry_run, stream);
+  return launch_t<__nv_bfloat16>(p, info, dry_run, stream);
+}
+
+}  // namespace tpa

@@ -1,0 +1,139 @@
+"""ctypes binding of libtpa_b200.so (declarations: include/tpa_b200.h).
+
+There is no CPU or PyTorch fallback behind this module: if the shared library is
+missing or a symbol cannot be resolved, importing it raises.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libtpa_b200.so")
+
+TPA_OK = 0
+TPA_ERR_BAD_ARG = -1
+TPA_ERR_UNSUPPORTED = -2
+TPA_ERR_WORKSPACE = -3
+TPA_ERR_CUDA = -4
+TPA_ERR_KERNEL_FORCED = -5
+TPA_ERR_DEVICE_TIMEOUT = -6
+
+DTYPE_F32, DTYPE_BF16 = 0, 1
+KERNEL_AUTO, KERNEL_SIMT, KERNEL_SM100 = 0, 1, 2
+KERNELS = {"auto": KERNEL_AUTO, "simt": KERNEL_SIMT, "sm100": KERNEL_SM100}
+FLAG_CAUSAL, FLAG_STATE_LOAD, FLAG_STATE_STORE = 1, 2, 4
+
+# Every symbol include/tpa_b200.h declares.
+EXPORTS = (
+    "tpa_fwd",
+    "tpa_fwd_workspace_bytes",
+    "tpa_query_kernel",
+    "tpa_read_status",
+    "tpa_status_string",
+    "tpa_last_cuda_error",
+    "tpa_launch_count",
+    "tpa_abi_version",
+)
+
+
+class TpaFactor(C.Structure):
+    _fields_ = [("ptr", C.c_void_p), ("stride", C.c_int64 * 3)]
+
+
+class TpaFwdArgs(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32),
+        ("dtype", C.c_int32),
+        ("batch", C.c_int32),
+        ("lq", C.c_int32),
+        ("lk", C.c_int32),
+        ("rank_q", C.c_int32),
+        ("rank_k", C.c_int32),
+        ("heads", C.c_int32),
+        ("dk", C.c_int32),
+        ("dv", C.c_int32),
+        ("qa", TpaFactor),
+        ("qb", TpaFactor),
+        ("ka", TpaFactor),
+        ("kb", TpaFactor),
+        ("va", TpaFactor),
+        ("vb", TpaFactor),
+        ("q_segment_ids", C.c_void_p),
+        ("kv_segment_ids", C.c_void_p),
+        ("q_segment_batch_stride", C.c_int64),
+        ("kv_segment_batch_stride", C.c_int64),
+        ("o", C.c_void_p),
+        ("lse", C.c_void_p),
+        ("state_o", C.c_void_p),
+        ("state_lse", C.c_void_p),
+        ("sm_scale", C.c_float),
+        ("flags", C.c_uint32),
+        ("q_offset", C.c_int64),
+        ("k_offset", C.c_int64),
+        ("kernel", C.c_int32),
+        ("reserved", C.c_int32),
+    ]
+
+
+class TpaKernelInfo(C.Structure):
+    _fields_ = [
+        ("kernel", C.c_int32),
+        ("block_q", C.c_int32),
+        ("block_kv", C.c_int32),
+        ("threads", C.c_int32),
+        ("grid", C.c_int32 * 3),
+        ("smem_bytes", C.c_int32),
+        ("launches", C.c_int32),
+    ]
+
+
+def _load():
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m tpa_b200.build` "
+            "(there is no fallback implementation)"
+        )
+    lib = C.CDLL(LIB_PATH)
+    for name in EXPORTS:
+        getattr(lib, name)  # AttributeError if the library does not export it
+    lib.tpa_fwd.argtypes = [C.POINTER(TpaFwdArgs), C.c_void_p, C.c_size_t, C.c_void_p]
+    lib.tpa_fwd.restype = C.c_int
+    lib.tpa_fwd_workspace_bytes.argtypes = [C.POINTER(TpaFwdArgs)]
+    lib.tpa_fwd_workspace_bytes.restype = C.c_size_t
+    lib.tpa_query_kernel.argtypes = [C.POINTER(TpaFwdArgs), C.POINTER(TpaKernelInfo)]
+    lib.tpa_query_kernel.restype = C.c_int
+    lib.tpa_read_status.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_uint32 * 4)]
+    lib.tpa_read_status.restype = C.c_int
+    lib.tpa_status_string.argtypes = [C.c_int]
+    lib.tpa_status_string.restype = C.c_char_p
+    lib.tpa_last_cuda_error.argtypes = []
+    lib.tpa_last_cuda_error.restype = C.c_char_p
+    lib.tpa_launch_count.argtypes = []
+    lib.tpa_launch_count.restype = C.c_uint64
+    lib.tpa_abi_version.argtypes = []
+    lib.tpa_abi_version.restype = C.c_int
+    return lib
+
+
+lib = _load()
+
+
+def status_string(status: int) -> str:
+    s = lib.tpa_status_string(status).decode()
+    if status == TPA_ERR_CUDA:
+        s += ": " + lib.tpa_last_cuda_error().decode()
+    return s
+
+
+def check(status: int):
+    """Raise the Python exception that corresponds to a negative status."""
+    if status == TPA_OK:
+        return
+    msg = f"libtpa_b200: {status_string(status)} (status {status})"
+    if status in (TPA_ERR_BAD_ARG, TPA_ERR_KERNEL_FORCED):
+        raise ValueError(msg)
+    if status == TPA_ERR_UNSUPPORTED:
+        raise NotImplementedError(msg)
+    raise RuntimeError(msg)

@@ -1,0 +1,339 @@
+"""Tensor Product Attention forward: the reference's call signatures over libtpa_b200.so.
+
+Mirrors tpa/tpa.py of jondeaton/tensor-product-attention-jax for the forward path:
+
+    BlockSizes   tpa/tpa.py:35-70
+    tpa()        tpa/tpa.py:73-121
+    _tpa_fwd()   tpa/tpa.py:124-165
+    _fwd()       tpa/tpa.py:446-543   (the custom call this library replaces)
+
+Arrays are torch tensors.  CUDA tensors are used in place (zero copy: the head factor
+A = x[..., :h] and the dim factor B = x[..., h:] are passed as pointer + strides).  Host
+arrays (numpy arrays or CPU torch tensors) are copied to the current CUDA device, run
+there, and the result is copied back — there is no CPU implementation.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import dataclasses
+
+import numpy as np
+import torch
+
+from . import _capi
+
+__all__ = ["BlockSizes", "tpa", "fwd_device"]
+
+
+@dataclasses.dataclass
+class BlockSizes:
+    """Tile-size request, kept for signature compatibility (tpa/tpa.py:35-70).
+
+    The divisibility rule of the reference launcher is enforced with these values
+    (tpa/tpa.py:485-490); the kernels choose their own tiles.
+    """
+
+    block_q: int = 128
+    block_kv: int = 128
+    block_h: int = 4
+
+
+_DTYPES = {torch.float32: _capi.DTYPE_F32, torch.bfloat16: _capi.DTYPE_BF16}
+_workspaces: dict = {}
+
+
+def _workspace(device, nbytes):
+    """Per-(device, stream) scratch buffer, grown on demand and reused across calls."""
+    if nbytes == 0:
+        return None
+    key = (device, torch.cuda.current_stream(device).cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def _factor(x, col0):
+    f = _capi.TpaFactor()
+    f.ptr = x.data_ptr() + col0 * x.element_size()
+    f.stride[0], f.stride[1], f.stride[2] = x.stride(0), x.stride(1), x.stride(2)
+    return f
+
+
+def _check_shapes(q, k, v, num_heads):
+    if q.ndim != 4 or k.ndim != 4 or v.ndim != 4:
+        raise AssertionError(f"expected [b, l, r, h+d] factors, got {q.shape}, {k.shape}, {v.shape}")
+    b, lq, rank_q, h_dk = q.shape
+    _, lk, rank_k, h_dv = v.shape
+    # tpa/tpa.py:474-475: rank is read from v and k must match it
+    if tuple(k.shape) != (b, lk, rank_k, h_dk):
+        raise AssertionError(tuple(k.shape))
+    if v.shape[0] != b:
+        raise AssertionError(tuple(v.shape))
+    dk, dv = h_dk - num_heads, h_dv - num_heads
+    if dk <= 0 or dv <= 0:
+        raise AssertionError((h_dk, h_dv, num_heads))
+    return b, lq, lk, rank_q, rank_k, dk, dv
+
+
+def fwd_device(
+    q,
+    k,
+    v,
+    num_heads,
+    q_segment_ids=None,
+    kv_segment_ids=None,
+    sm_scale=1.0,
+    causal=False,
+    *,
+    q_offset=0,
+    k_offset=0,
+    state=None,
+    load_state=False,
+    store_state=False,
+    out=None,
+    lse=None,
+    want_lse=True,
+    kernel="auto",
+):
+    """One tpa_fwd call on CUDA tensors; returns (o, lse_fp32).
+
+    `state = (state_o fp32 [b,lq,h,dv], state_lse fp32 [b,lq,h])` with `load_state` /
+    `store_state` is the carry of the ring scan (tpa/ring_tpa.py:69-91): a call with
+    `store_state=True` writes the merged partial into `state` and returns (None, None).
+    Work is enqueued on the current stream of q's device.
+    """
+    if not q.is_cuda:
+        raise RuntimeError("tpa_b200 needs a CUDA device: there is no CPU implementation")
+    b, lq, lk, rank_q, rank_k, dk, dv = _check_shapes(q, k, v, num_heads)
+    if q.dtype not in _DTYPES or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise NotImplementedError(f"dtype {q.dtype}/{k.dtype}/{v.dtype}: float32 or bfloat16 factors only")
+    for x in (q, k, v):
+        if x.stride(3) != 1:
+            raise ValueError("the last (h+d) axis of the factors must be contiguous")
+    if (q_segment_ids is None) != (kv_segment_ids is None):
+        raise AssertionError("segment ids must be given for both sides or neither")  # tpa/tpa.py:369-371
+
+    a = _capi.TpaFwdArgs()
+    a.struct_size = C.sizeof(_capi.TpaFwdArgs)
+    a.dtype = _DTYPES[q.dtype]
+    a.batch, a.lq, a.lk = b, lq, lk
+    a.rank_q, a.rank_k = rank_q, rank_k
+    a.heads, a.dk, a.dv = num_heads, dk, dv
+    a.qa, a.qb = _factor(q, 0), _factor(q, num_heads)
+    a.ka, a.kb = _factor(k, 0), _factor(k, num_heads)
+    a.va, a.vb = _factor(v, 0), _factor(v, num_heads)
+    keep = []
+    if q_segment_ids is not None:
+        qs = q_segment_ids.to(device=q.device, dtype=torch.int32)
+        ks = kv_segment_ids.to(device=q.device, dtype=torch.int32)
+        # a 1-D id row is shared by the whole batch (vmap in_axes None, tpa/tpa.py:155-161)
+        qs = qs.contiguous()
+        ks = ks.contiguous()
+        if qs.shape[-1] != lq or ks.shape[-1] != lk:
+            raise AssertionError((tuple(qs.shape), tuple(ks.shape)))
+        a.q_segment_ids, a.kv_segment_ids = qs.data_ptr(), ks.data_ptr()
+        a.q_segment_batch_stride = lq if qs.ndim == 2 else 0
+        a.kv_segment_batch_stride = lk if ks.ndim == 2 else 0
+        keep += [qs, ks]
+    flags = _capi.FLAG_CAUSAL if causal else 0
+    if load_state:
+        flags |= _capi.FLAG_STATE_LOAD
+    if store_state:
+        flags |= _capi.FLAG_STATE_STORE
+    if load_state or store_state:
+        so, sl = state
+        assert so.dtype == torch.float32 and sl.dtype == torch.float32
+        assert so.is_contiguous() and sl.is_contiguous()
+        assert tuple(so.shape) == (b, lq, num_heads, dv) and tuple(sl.shape) == (b, lq, num_heads)
+        a.state_o, a.state_lse = so.data_ptr(), sl.data_ptr()
+    if not store_state:
+        if out is None:
+            out = torch.empty((b, lq, num_heads, dv), dtype=q.dtype, device=q.device)
+        assert out.is_contiguous() and out.dtype == q.dtype
+        a.o = out.data_ptr()
+        if lse is None and want_lse:
+            lse = torch.empty((b, lq, num_heads), dtype=torch.float32, device=q.device)
+        if lse is not None:
+            assert lse.is_contiguous() and lse.dtype == torch.float32
+            a.lse = lse.data_ptr()
+    a.sm_scale = float(sm_scale)
+    a.flags = flags
+    a.q_offset, a.k_offset = int(q_offset), int(k_offset)
+    a.kernel = _capi.KERNELS[kernel]
+
+    with torch.cuda.device(q.device):
+        nbytes = _capi.lib.tpa_fwd_workspace_bytes(C.byref(a))
+        ws = _workspace(q.device, nbytes)
+        stream = torch.cuda.current_stream(q.device).cuda_stream
+        st = _capi.lib.tpa_fwd(
+            C.byref(a), ws.data_ptr() if ws is not None else None, nbytes, C.c_void_p(stream)
+        )
+    _capi.check(st)
+    del keep
+    if store_state:
+        return None, None
+    return out, lse
+
+
+def query_kernel(q, k, v, num_heads, kernel="auto", causal=False, segments=False):
+    """Which kernel / tiles / grid a call with these operands would use (tpa_query_kernel)."""
+    b, lq, lk, rank_q, rank_k, dk, dv = _check_shapes(q, k, v, num_heads)
+    a = _capi.TpaFwdArgs()
+    a.struct_size = C.sizeof(_capi.TpaFwdArgs)
+    a.dtype = _DTYPES[q.dtype]
+    a.batch, a.lq, a.lk, a.rank_q, a.rank_k = b, lq, lk, rank_q, rank_k
+    a.heads, a.dk, a.dv = num_heads, dk, dv
+    a.qa, a.qb = _factor(q, 0), _factor(q, num_heads)
+    a.ka, a.kb = _factor(k, 0), _factor(k, num_heads)
+    a.va, a.vb = _factor(v, 0), _factor(v, num_heads)
+    a.o = 1  # any non-null value: nothing is dereferenced by the query
+    if segments:
+        a.q_segment_ids = a.kv_segment_ids = 1
+    a.flags = _capi.FLAG_CAUSAL if causal else 0
+    a.kernel = _capi.KERNELS[kernel]
+    info = _capi.TpaKernelInfo()
+    _capi.check(_capi.lib.tpa_query_kernel(C.byref(a), C.byref(info)))
+    return {
+        "kernel": {1: "simt", 2: "sm100"}[info.kernel],
+        "block_q": info.block_q,
+        "block_kv": info.block_kv,
+        "threads": info.threads,
+        "grid": tuple(info.grid),
+        "smem_bytes": info.smem_bytes,
+        "launches": info.launches,
+    }
+
+
+def _to_device(x, device):
+    """Host array -> CUDA tensor (through pinned memory when the source is pinned)."""
+    if x is None:
+        return None
+    if isinstance(x, np.ndarray):
+        x = torch.from_numpy(x)
+    return x.to(device, non_blocking=x.is_pinned() if not x.is_cuda else False)
+
+
+def _tpa_fwd(
+    q,
+    k,
+    v,
+    num_heads,
+    q_segment_ids,
+    kv_segment_ids,
+    sm_scale,
+    causal,
+    block_sizes,
+    nomat,
+    debug,
+    interpret,
+):
+    """Batch forward returning (o, residuals) as tpa/tpa.py:124-165 does.
+
+    residuals = (q, k, v, q_segment_ids, kv_segment_ids, o, l) with l[b, lq, h] the LSE
+    in q's dtype.  `nomat`, `debug` and `interpret` are accepted and have no effect: the
+    non-materialising strategy (tpa/tpa.py:333-359) gives the same result by construction
+    and the other two are Pallas debugging switches.
+    """
+    del nomat, debug, interpret
+    if block_sizes is None:
+        block_sizes = BlockSizes()
+    lq, lk = q.shape[1], k.shape[1]
+    block_q = min(block_sizes.block_q, lq)  # tpa/tpa.py:485-490
+    block_kv = min(block_sizes.block_kv, lk)
+    if lq % block_q != 0:
+        raise AssertionError((lq, block_q))
+    if lk % block_kv != 0:
+        raise AssertionError((lk, block_kv))
+    o, l = fwd_device(q, k, v, num_heads, q_segment_ids, kv_segment_ids, sm_scale, causal)
+    l = l.to(q.dtype)
+    return o, (q, k, v, q_segment_ids, kv_segment_ids, o, l)
+
+
+def tpa(
+    q,
+    k,
+    v,
+    num_heads: int,
+    q_segment_ids=None,
+    kv_segment_ids=None,
+    sm_scale: float = 1.0,
+    causal: bool = False,
+    block_sizes: BlockSizes | None = None,
+    nomat: bool = False,
+    debug: bool = False,
+    interpret: bool = False,
+):
+    """Tensor Product Attention forward; same arguments as tpa/tpa.py:73-121.
+
+    q[b, lq, rq, h+dk], k[b, lk, rk, h+dk], v[b, lk, rk, h+dv] hold the head factor in
+    [..., :h] and the dim factor in [..., h:]; Q, K, V are rank means of their outer
+    products.  Returns o[b, lq, h, dv] in q's dtype; rows whose every key is masked are NaN.
+    Host inputs (numpy / CPU tensors) are copied to the current CUDA device and the
+    result comes back as the same kind of host array.
+    """
+    host_kind = None
+    if isinstance(q, np.ndarray):
+        host_kind = "numpy"
+    elif not q.is_cuda:
+        host_kind = "torch"
+    if host_kind is not None:
+        if not torch.cuda.is_available():
+            raise RuntimeError("tpa_b200 needs a CUDA device: there is no CPU implementation")
+        dev = torch.device("cuda", torch.cuda.current_device())
+        q, k, v = (_to_device(x, dev) for x in (q, k, v))
+        q_segment_ids = _to_device(q_segment_ids, dev)
+        kv_segment_ids = _to_device(kv_segment_ids, dev)
+    o, _ = _tpa_fwd(
+        q,
+        k,
+        v,
+        num_heads=num_heads,
+        q_segment_ids=q_segment_ids,
+        kv_segment_ids=kv_segment_ids,
+        sm_scale=sm_scale,
+        causal=causal,
+        block_sizes=block_sizes,
+        nomat=nomat,
+        debug=debug,
+        interpret=interpret,
+    )
+    if host_kind == "numpy":
+        return o.float().cpu().numpy() if o.dtype == torch.bfloat16 else o.cpu().numpy()
+    if host_kind == "torch":
+        return o.cpu()
+    return o
+
+
+def _fwd(
+    q,
+    k,
+    v,
+    q_segment_ids,
+    kv_segment_ids,
+    num_heads,
+    sm_scale,
+    causal,
+    block_sizes,
+    nomat=False,
+    debug=False,
+    interpret=False,
+):
+    """Per-batch-element forward (o[lq,h,dv], lse[lq,h]) as tpa/tpa.py:446-543."""
+    o, res = _tpa_fwd(
+        q[None],
+        k[None],
+        v[None],
+        num_heads,
+        None if q_segment_ids is None else q_segment_ids[None],
+        None if kv_segment_ids is None else kv_segment_ids[None],
+        sm_scale,
+        causal,
+        block_sizes,
+        nomat,
+        debug,
+        interpret,
+    )
+    return o[0], res[-1][0]

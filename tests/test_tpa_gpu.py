@@ -1,0 +1,178 @@
+"""GPU parity: the CUDA path, called through the C ABI, against the golden fixtures and the oracle.
+
+Tolerances: fp32 max-abs <= 1e-5 on the benchmark's fp32 configuration and
+rtol = atol = 1e-3 (tpa/tpa_test.py:125) on the reference's own test matrix, where the
+tighter 2e-5 bound is also asserted; bf16 max-abs <= 2e-2 and mean-abs <= 5e-3.
+"""
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import load_golden
+from oracle import tpa_oracle as orc
+
+import tpa_b200
+from tpa_b200 import _capi
+
+pytestmark = pytest.mark.gpu
+
+FWD = load_golden("fwd_matrix")
+RING = load_golden("ring_matrix")
+EXTRA = load_golden("extra")
+
+
+def dev(x, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(x)).cuda()
+    return t.to(dtype) if dtype is not None else t
+
+
+def assert_close(a, b, tight=2e-5):
+    np.testing.assert_allclose(a, b, rtol=1e-3, atol=1e-3, equal_nan=True)
+    assert np.array_equal(np.isnan(a), np.isnan(b))
+    assert np.nanmax(np.abs(a - b)) <= tight
+
+
+def test_extension_loaded_and_counts_launches():
+    n0 = _capi.lib.tpa_launch_count()
+    q, k, v = orc.make_factors(1, 1, 8, 8, 1, 1, 1, 4, 6)
+    tpa_b200.tpa.tpa(dev(q), dev(k), dev(v), num_heads=1)
+    torch.cuda.synchronize()
+    assert _capi.lib.tpa_launch_count() == n0 + 1
+
+
+@pytest.mark.parametrize("nomat", [False, True])
+@pytest.mark.parametrize("case", sorted(FWD))
+def test_reference_forward_matrix(case, nomat):
+    """The 48 cases of tpa/tpa_test.py:60-125 against outputs of the reference's kernel."""
+    g = FWD[case]
+    seed, b, lq, lk, rq, rk, h, dk, dv, seg = (int(x) for x in g["meta"])
+    q, k, v = orc.make_factors(seed, b, lq, lk, rq, rk, h, dk, dv, dist="uniform")
+    qs = dev(orc.segment_ids(b, lq, seg)) if seg else None
+    ks = dev(orc.segment_ids(b, lk, seg)) if seg else None
+    o, res = tpa_b200.tpa._tpa_fwd(dev(q), dev(k), dev(v), h, qs, ks, 1.0, False, None, nomat, False, True)
+    assert o.shape == (b, lq, h, dv)
+    assert_close(o.cpu().numpy(), g["o"])
+    assert_close(res[-1].cpu().numpy(), g["lse"])
+
+
+@pytest.mark.parametrize("case", ["c0_causal", "causal_seg", "peaky", "empty_rows"])
+def test_causal_scale_and_empty_rows(case):
+    g = EXTRA[case]
+    seed, b, lq, lk, rq, rk, h, dk, dv, sq, sk, causal, dist = (int(x) for x in g["meta"])
+    sm = float(g["sm_scale"])
+    q, k, v = orc.make_factors(seed, b, lq, lk, rq, rk, h, dk, dv, dist=["normal", "uniform"][dist])
+    qs = dev(orc.segment_ids(b, lq, sq)) if sq else None
+    ks = dev(orc.segment_ids(b, lk, sk)) if sk else None
+    o, res = tpa_b200.tpa._tpa_fwd(dev(q), dev(k), dev(v), h, qs, ks, sm, bool(causal), None, False, False, False)
+    o = o.cpu().numpy()
+    # fp32 bound of the benchmark: max-abs <= 1e-5 against the reference's output
+    assert np.nanmax(np.abs(o - g["o"])) <= 1e-5
+    assert np.array_equal(np.isnan(o), np.isnan(g["o"]))
+    assert_close(res[-1].cpu().numpy(), g["lse"])
+    # against the fp64 oracle as well
+    ref = orc.tpa_reference(q, k, v, h, None if qs is None else qs.cpu().numpy(),
+                            None if ks is None else ks.cpu().numpy(), sm_scale=sm, causal=bool(causal))
+    assert np.nanmax(np.abs(o - ref)) <= 1e-5
+
+
+def test_host_arrays_round_trip():
+    """numpy in -> numpy out through the public call (copies inside the call)."""
+    q, k, v = orc.make_factors(5, 2, 128, 128, 2, 2, 4, 16, 16)
+    o = tpa_b200.tpa.tpa(q, k, v, num_heads=4, sm_scale=0.25, causal=True)
+    assert isinstance(o, np.ndarray)
+    assert np.max(np.abs(o - orc.tpa_reference(q, k, v, 4, sm_scale=0.25, causal=True))) <= 1e-5
+
+
+@pytest.mark.parametrize("shape", [(1, 100, 77, 3, 2, 3, 7, 9), (2, 33, 200, 1, 5, 5, 20, 130), (1, 64, 64, 2, 2, 2, 256, 256)])
+@pytest.mark.parametrize("causal", [False, True])
+def test_ragged_shapes_low_level(shape, causal):
+    """Lengths that are not multiples of any tile, dv > 128, offsets: the C entry point itself."""
+    b, lq, lk, rq, rk, h, dk, dv = shape
+    q, k, v = orc.make_factors(31, b, lq, lk, rq, rk, h, dk, dv)
+    qo, ko = (37, 5) if causal else (0, 0)
+    o, l = tpa_b200.tpa.fwd_device(dev(q), dev(k), dev(v), h, None, None, 0.4, causal, q_offset=qo, k_offset=ko)
+    ref, lref = orc.tpa_reference(q, k, v, h, sm_scale=0.4, causal=causal, q_offset=qo, k_offset=ko, return_lse=True)
+    assert_close(o.cpu().numpy(), ref)
+    assert_close(l.cpu().numpy(), lref)
+
+
+@pytest.mark.parametrize("dtype,kernel", [(torch.float32, "simt"), (torch.bfloat16, "simt"), (torch.bfloat16, "auto")])
+@pytest.mark.parametrize("mode", ["reference_local", "global"])
+def test_state_chaining_equals_ring_oracle(dtype, kernel, mode):
+    """N ring steps emulated on one GPU through TPA_FLAG_STATE_LOAD/STORE vs the ring oracle."""
+    n, b, l, rq, rk, h, d = 4, 1, 1024, 3, 2, 8, 64
+    q, k, v = orc.make_factors(41, b, l, l, rq, rk, h, d, d)
+    tq, tk, tv = dev(q, dtype), dev(k, dtype), dev(v, dtype)
+    q, k, v = (t.float().cpu().numpy() for t in (tq, tk, tv))
+    ids = np.zeros((b, l), np.int32)
+    ref = orc.ring_tpa_reference(q, k, v, ids, ids, h, n, sm_scale=d**-0.5, causal=True, mask_mode=mode)
+    per = l // n
+    out = torch.empty(b, l, h, d, dtype=dtype, device="cuda")
+    for r in range(n):
+        sl = slice(r * per, (r + 1) * per)
+        state = (torch.empty(b, per, h, d, device="cuda"), torch.empty(b, per, h, device="cuda"))
+        steps = [s for s in range(n) if not (mode == "global" and (r - s) % n > r)]
+        for i, s in enumerate(steps):
+            src = (r - s) % n
+            ks = slice(src * per, (src + 1) * per)
+            off = (r * per, src * per) if mode == "global" else (0, 0)
+            o_r = torch.empty(b, per, h, d, dtype=dtype, device="cuda")
+            tpa_b200.tpa.fwd_device(tq[:, sl], tk[:, ks], tv[:, ks], h, None, None, d**-0.5, True,
+                                    q_offset=off[0], k_offset=off[1], state=state, load_state=i > 0,
+                                    store_state=i < len(steps) - 1, out=o_r, kernel=kernel)
+        out[:, sl] = o_r
+    diff = np.abs(out.float().cpu().numpy() - ref)
+    if dtype == torch.float32:
+        assert diff.max() <= 1e-5
+    else:
+        assert diff.max() <= 2e-2 and diff.mean() <= 5e-3
+
+
+def test_bitwise_reproducible():
+    q, k, v = orc.make_factors(3, 2, 256, 256, 6, 2, 8, 64, 64)
+    a = tpa_b200.tpa.tpa(dev(q), dev(k), dev(v), num_heads=8, sm_scale=0.125, causal=True)
+    b = tpa_b200.tpa.tpa(dev(q), dev(k), dev(v), num_heads=8, sm_scale=0.125, causal=True)
+    assert torch.equal(a, b)
+
+
+# --------------------------------------------------------------------------- bf16 configurations
+
+
+def bf16_case(seed, b, t, h, d, rq, rk, causal, kernel="auto", rows=None, segs=None, scale=1.0):
+    q, k, v = orc.make_factors(seed, b, t, t, rq, rk, h, d, d)
+    tq, tk, tv = dev(q * scale, torch.bfloat16), dev(k, torch.bfloat16), dev(v, torch.bfloat16)
+    ids = None if segs is None else dev(orc.segment_ids(b, t, segs))
+    o, lse = tpa_b200.tpa.fwd_device(tq, tk, tv, h, ids, ids, d**-0.5, causal, kernel=kernel)
+    ref, lref = orc.tpa_reference_torch(tq.float().cpu(), tk.float().cpu(), tv.float().cpu(), h,
+                                        None if ids is None else ids.cpu(), None if ids is None else ids.cpu(),
+                                        sm_scale=d**-0.5, causal=causal, rows=rows, return_lse=True)
+    o = o.float().cpu()
+    lse = lse.cpu()
+    if rows is not None:
+        o, lse = o[:, rows], lse[:, rows]
+    diff = (o - ref).abs()
+    return float(diff.max()), float(diff.mean()), float((lse - lref).abs().max()), float(ref.abs().max())
+
+
+@pytest.mark.parametrize("kernel", ["simt", "auto"])
+def test_bf16_config1_shape_reduced_batch(kernel):
+    """Configuration 1 (bf16 causal T=4096 h=32 d=128 R 6/2/2) at batch 1, sampled rows."""
+    rows = torch.cat([torch.arange(0, 4), torch.arange(4092, 4096), torch.randperm(4096, generator=torch.Generator().manual_seed(0))[:120]])
+    mx, mean, lerr, _ = bf16_case(1, 1, 4096, 32, 128, 6, 2, True, kernel, rows=rows)
+    assert mx <= 2e-2 and mean <= 5e-3 and lerr <= 1e-2, (mx, mean, lerr)
+
+
+@pytest.mark.parametrize("kernel", ["simt", "auto"])
+def test_bf16_config4_noncausal_high_rank(kernel):
+    """Configuration 4 (bf16 non-causal T=2048 h=16 d=64 R 8/8/8) at batch 1, with the dense
+    attention cross-check: the oracle materialises Q, K, V and runs plain softmax attention."""
+    mx, mean, lerr, _ = bf16_case(4, 1, 2048, 16, 64, 8, 8, False, kernel)
+    assert mx <= 2e-2 and mean <= 5e-3 and lerr <= 1e-2, (mx, mean, lerr)
+
+
+@pytest.mark.parametrize("kernel", ["simt", "auto"])
+def test_bf16_peaky_and_segments(kernel):
+    """Large logits (online-softmax rescaling really happens) and packed segments."""
+    mx, mean, lerr, refmax = bf16_case(6, 2, 512, 8, 128, 4, 4, True, kernel, segs=200, scale=24.0)
+    assert mx <= 2e-2 * max(1.0, refmax) and mean <= 5e-3, (mx, mean, lerr, refmax)
