@@ -189,6 +189,8 @@ def main():
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
     ap.add_argument("--mask-mode", default="reference_local", choices=["reference_local", "global"])
     ap.add_argument("--kernel", default="auto", choices=["auto", "simt", "sm100"])
+    ap.add_argument("--seq-len", type=int, default=None,
+                    help="override T of the workload (profiling on a small case; not a headline number)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
@@ -198,6 +200,11 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     name = args.workload or ("c2" if world == 1 else "c3")
+    if args.seq_len is not None:
+        w = list(WORKLOADS[name])
+        w[2] = args.seq_len
+        name = f"{name}@T{args.seq_len}"
+        WORKLOADS[name] = tuple(w)
     if args.impl == "reference":
         return reference_arm(args, name)
 

@@ -1,10 +1,543 @@
-// Placeholder until the tcgen05 kernel lands: nothing is routed here.
+// Tensor-core TPA forward for sm_100a: bf16 factors, head_dim 64 or 128, lengths that are
+// multiples of 128.  Replaces _fwd_kernel (tpa/tpa.py:245-443) for those shapes.
+//
+// One CTA owns 256 query rows (two 128-row units) of one head of one batch element and
+// walks the key/value rows 128 at a time.  Roles, by warp:
+//
+//   warps 0-3 / 4-7   online softmax of unit 0 / unit 1 (one thread per query row: TMEM lane)
+//   warps 8-11        rebuild the K tile of this head from the rank factors into shared memory
+//   warps 12-15       rebuild the V tile likewise (all eight rebuild Q once at the start)
+//   warp 16           issues tcgen05.mma: S_u = Q_u K^T (fp32 in TMEM), O_u += P_u V
+//
+// Q, K, V are sums over rank of a[row, r, head] * b[row, r, :] (tpa/tpa.py:317,364,417).  The
+// 1/R_q, 1/R_k means and sm_scale * log2(e) are folded into Q once; the 1/R_k of V is applied
+// with the final 1/l.  K and V tiles are double buffered; the rebuilt tiles are written in
+// the 128-byte-swizzled layout the tcgen05 shared-memory descriptors describe.  P (bf16)
+// overwrites S in TMEM and feeds the second MMA from there.  The two units alternate on the
+// tensor pipe, so the softmax of one overlaps the MMAs of the other.
+//
+// The running maximum is only raised when the new tile exceeds it by more than 2^8 (the
+// accumulator and row sum are then rescaled); the final 1/l division makes the result
+// independent of which maximum was subtracted.
+//
+// Every mbarrier wait is bounded: after ~2^28 cycles the waiter records where it gave up in
+// the status block, raises a CTA-wide abort flag that makes all later waits fall through,
+// and the CTA runs to its normal end (TMEM is freed).
+#include <math_constants.h>
+
+#include "sm100_ptx.cuh"
 #include "tpa_common.cuh"
 
 namespace tpa {
-bool sm100_supported(const Params&) { return false; }
-size_t sm100_workspace_bytes(const Params&) { return 0; }
-cudaError_t launch_sm100(const Params&, void*, TpaKernelInfo*, bool, cudaStream_t) {
-  return cudaErrorNotSupported;
+namespace {
+
+using namespace ptx;
+
+constexpr int kSoftmaxWarps = 8;
+constexpr int kRebuildWarps = 8;
+constexpr int kMmaWarp = kSoftmaxWarps + kRebuildWarps;
+constexpr int kThreads = (kMmaWarp + 1) * 32;  // 544
+constexpr int kUnitRows = 128;
+constexpr int kTileKv = 128;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+constexpr float kRescaleThreshold = 8.0f;  // log2 units
+constexpr long long kWaitCycles = 1ll << 28;
+
+struct Barriers {
+  uint64_t q_full;
+  uint64_t k_full[2], k_empty[2];
+  uint64_t v_full[2], v_empty[2];
+  uint64_t s_full[2], p_ready[2], o_done[2];
+  uint32_t tmem_base;
+  volatile uint32_t abort;
+};
+
+struct Waiter {
+  Barriers* bars;
+  uint32_t* status;
+  // Returns when the phase with this parity has completed, or after the cycle budget.
+  __device__ __forceinline__ void operator()(uint64_t* bar, uint32_t parity, uint32_t where) const {
+    if (mbar_try_wait(bar, parity)) return;
+    const long long t0 = clock64();
+    uint32_t spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+      if (bars->abort) return;
+      if ((++spins & 63u) == 0 && clock64() - t0 > kWaitCycles) {
+        bars->abort = 1;
+        if (status != nullptr && atomicCAS(status, 0u, 1u) == 0u) {
+          status[1] = where;
+          status[2] = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+          status[3] = spins;
+        }
+        return;
+      }
+    }
+  }
+};
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
+
+// dst tile rows [0,128): dst[row][:] = scale * sum_r a[row0+row, r] * b[row0+row, r, :], bf16,
+// in 64-column sub-tiles of 16 KB with the 128-byte swizzle.  `nthreads` threads cooperate.
+template <int D>
+__device__ __forceinline__ void rebuild_tile(uint8_t* dst, const __nv_bfloat16* a,
+                                             int64_t a_row, int64_t a_rank,
+                                             const __nv_bfloat16* b, int64_t b_row, int64_t b_rank,
+                                             int rank, int64_t row0, float scale, int tid,
+                                             int nthreads) {
+  constexpr int CH = D / 8;  // 16-byte chunks per row
+  const int chunk = tid % CH;
+  const int rows_per_pass = nthreads / CH;
+  const int r_in = tid / CH;
+  const __nv_bfloat16* bcol = b + chunk * 8;
+  uint8_t* dsub = dst + (chunk >> 3) * (kUnitRows * 128);
+#pragma unroll 2
+  for (int row = r_in; row < kUnitRows; row += rows_per_pass) {
+    const int64_t g = row0 + row;
+    const __nv_bfloat16* ap = a + g * a_row;
+    const __nv_bfloat16* bp = bcol + g * b_row;
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+#pragma unroll 4
+    for (int r = 0; r < rank; ++r) {
+      const uint4 bv = __ldg(reinterpret_cast<const uint4*>(bp + r * b_rank));
+      const float av = __bfloat162float(ap[r * a_rank]);
+      const uint32_t w[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        acc[2 * e] = fmaf(av, __uint_as_float(w[e] << 16), acc[2 * e]);
+        acc[2 * e + 1] = fmaf(av, __uint_as_float(w[e] & 0xffff0000u), acc[2 * e + 1]);
+      }
+    }
+    uint4 out;
+    out.x = pack_bf16(acc[0] * scale, acc[1] * scale);
+    out.y = pack_bf16(acc[2] * scale, acc[3] * scale);
+    out.z = pack_bf16(acc[4] * scale, acc[5] * scale);
+    out.w = pack_bf16(acc[6] * scale, acc[7] * scale);
+    *reinterpret_cast<uint4*>(dsub + sw128_offset(row, chunk & 7)) = out;
+  }
+}
+
+template <int D>
+__global__ void __launch_bounds__(kThreads, 1) tpa_fwd_sm100_kernel(const Params p) {
+  constexpr int kTileBytes = kUnitRows * D * 2;  // one Q unit, one K stage or one V stage
+  constexpr uint32_t kIdescS = make_idesc(128, kTileKv, false, false);
+  constexpr uint32_t kIdescPV = make_idesc(128, D, false, true);
+  constexpr int kOCol = 256;  // TMEM: S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [256+D,256+2D)
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = smem + 2 * kTileBytes;
+  uint8_t* sV = smem + 4 * kTileBytes;
+  Barriers* bars = reinterpret_cast<Barriers*>(smem + 6 * kTileBytes);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int head = blockIdx.x;
+  const int pair = gridDim.y - 1 - blockIdx.y;  // longest causal rows first
+  const int batch = blockIdx.z;
+  const int q0 = pair * 2 * kUnitRows;
+  const bool causal = (p.flags & TPA_FLAG_CAUSAL) != 0;
+  const bool has_seg = p.q_seg != nullptr;
+  const bool load_state = (p.flags & TPA_FLAG_STATE_LOAD) != 0;
+  const bool store_state = (p.flags & TPA_FLAG_STATE_STORE) != 0;
+
+  // number of key tiles each unit can see (tpa/tpa.py:427-431, with global offsets)
+  const int n_kv = p.lk / kTileKv;
+  int n_vis[2];
+#pragma unroll
+  for (int u = 0; u < 2; ++u) {
+    const int q0u = q0 + u * kUnitRows;
+    if (q0u >= p.lq) {
+      n_vis[u] = 0;
+    } else if (causal) {
+      const int64_t last = (int64_t)q0u + kUnitRows - 1 + p.q_offset - p.k_offset;
+      n_vis[u] = last < 0 ? 0 : (int)min((int64_t)n_kv, last / kTileKv + 1);
+    } else {
+      n_vis[u] = n_kv;
+    }
+  }
+  const int n_tiles = max(n_vis[0], n_vis[1]);
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->q_full, kRebuildWarps * 32);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bars->k_full[s], kRebuildWarps * 16);
+      mbar_init(&bars->v_full[s], kRebuildWarps * 16);
+      mbar_init(&bars->k_empty[s], 1);
+      mbar_init(&bars->v_empty[s], 1);
+      mbar_init(&bars->s_full[s], 1);
+      mbar_init(&bars->p_ready[s], kUnitRows);
+      mbar_init(&bars->o_done[s], 1);
+    }
+    bars->abort = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(&bars->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_base;
+  const Waiter wait{bars, p.status};
+
+  const __nv_bfloat16* qa = static_cast<const __nv_bfloat16*>(p.qa.ptr) + batch * p.qa.stride[0] + head;
+  const __nv_bfloat16* qb = static_cast<const __nv_bfloat16*>(p.qb.ptr) + batch * p.qb.stride[0];
+  const __nv_bfloat16* ka = static_cast<const __nv_bfloat16*>(p.ka.ptr) + batch * p.ka.stride[0] + head;
+  const __nv_bfloat16* kb = static_cast<const __nv_bfloat16*>(p.kb.ptr) + batch * p.kb.stride[0];
+  const __nv_bfloat16* va = static_cast<const __nv_bfloat16*>(p.va.ptr) + batch * p.va.stride[0] + head;
+  const __nv_bfloat16* vb = static_cast<const __nv_bfloat16*>(p.vb.ptr) + batch * p.vb.stride[0];
+
+  if (warp < kSoftmaxWarps) {
+    // ------------------------------------------------------------------ softmax + epilogue
+    const int u = warp >> 2;
+    const int row = (warp & 3) * 32 + lane;
+    const int n_u = n_vis[u];
+    const int q0u = q0 + u * kUnitRows;
+    const int grow = q0u + row;
+    const bool live = q0u < p.lq;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t tS = tmem + lane_base + u * 128;
+    const uint32_t tO = tmem + lane_base + kOCol + u * D;
+    const int64_t rh = live ? ((int64_t)batch * p.lq + grow) * p.heads + head : 0;
+    const int64_t qpos = (int64_t)grow + p.q_offset;
+    const int qseg = (has_seg && live) ? p.q_seg[(int64_t)batch * p.q_seg_bstride + grow] : 0;
+    const int32_t* kseg = has_seg ? p.kv_seg + (int64_t)batch * p.kv_seg_bstride : nullptr;
+    const float rk = (float)p.rank_k;
+
+    float m = -CUDART_INF_F, l = 0.f;
+    bool loaded = false;
+    if (load_state && live && n_u > 0) {
+      // carried partial (tpa/ring_tpa.py:69-71): accumulator = o_prev (times R_k, see header),
+      // row sum 1, maximum = previous LSE
+      const float prev = p.state_lse[rh];
+      const bool has = prev != -CUDART_INF_F;
+      if (has) {
+        m = prev * kLog2e;
+        l = 1.f;
+      }
+      const float* so = p.state_o + rh * D;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t r[32];
+#pragma unroll
+        for (int e = 0; e < 32; e += 4) {
+          float4 v = has ? *reinterpret_cast<const float4*>(so + c * 32 + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+          r[e] = __float_as_uint(v.x * rk);
+          r[e + 1] = __float_as_uint(v.y * rk);
+          r[e + 2] = __float_as_uint(v.z * rk);
+          r[e + 3] = __float_as_uint(v.w * rk);
+        }
+        tmem_st32(tO + c * 32, r);
+      }
+      tmem_st_wait();
+      loaded = true;
+    }
+
+    for (int j = 0; j < n_u; ++j) {
+      wait(&bars->s_full[u], j & 1, 0x100 + u);
+      tc_fence_after();
+      const int k0 = j * kTileKv;
+      const bool diag = causal && ((int64_t)k0 + kTileKv - 1 + p.k_offset > (int64_t)q0u + p.q_offset);
+      const bool masked = diag || has_seg;
+
+      // pass 1: row maximum of the (masked) logits; they are already in log2 units
+      float tmax = -CUDART_INF_F;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tS + c * 32, r);
+        tmem_ld_wait();
+        if (masked) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const int kc = k0 + c * 32 + e;
+            bool keep = true;
+            if (diag) keep = qpos >= (int64_t)kc + p.k_offset;
+            if (has_seg) keep = keep && (qseg == kseg[kc]);
+            if (keep) tmax = fmaxf(tmax, __uint_as_float(r[e]));
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) tmax = fmaxf(tmax, __uint_as_float(r[e]));
+        }
+      }
+      const float m_new = fmaxf(m, tmax);
+      float factor = 1.f;
+      if (m == -CUDART_INF_F) {
+        m = m_new;  // nothing accumulated for this row yet (l = 0, accumulator row is 0)
+      } else if (m_new - m > kRescaleThreshold) {
+        factor = fast_exp2(m - m_new);
+        m = m_new;
+      }
+      if (__any_sync(0xffffffffu, factor != 1.f) && (j > 0 || loaded)) {
+        if (j > 0) {
+          wait(&bars->o_done[u], (j - 1) & 1, 0x200 + u);
+          tc_fence_after();
+        }
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(tO + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * factor);
+          tmem_st32(tO + c * 32, r);
+        }
+        tmem_st_wait();
+      }
+      l *= factor;
+      const float m_sub = (m == -CUDART_INF_F) ? 0.f : m;
+
+      // pass 2: p = 2^(s - m), row sum, bf16 P over the first 64 columns of S
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t pk[32];
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+          const int c = half * 2 + cc;
+          uint32_t r[32];
+          tmem_ld32(tS + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            float s0 = __uint_as_float(r[e]), s1 = __uint_as_float(r[e + 1]);
+            if (masked) {
+              const int kc = k0 + c * 32 + e;
+              bool keep0 = true, keep1 = true;
+              if (diag) {
+                keep0 = qpos >= (int64_t)kc + p.k_offset;
+                keep1 = qpos >= (int64_t)kc + 1 + p.k_offset;
+              }
+              if (has_seg) {
+                keep0 = keep0 && (qseg == kseg[kc]);
+                keep1 = keep1 && (qseg == kseg[kc + 1]);
+              }
+              if (!keep0) s0 = -CUDART_INF_F;
+              if (!keep1) s1 = -CUDART_INF_F;
+            }
+            const float p0 = fast_exp2(s0 - m_sub), p1 = fast_exp2(s1 - m_sub);
+            l += p0 + p1;
+            pk[cc * 16 + e / 2] = pack_bf16(p0, p1);
+          }
+        }
+        tmem_st32(tS + half * 32, pk);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&bars->p_ready[u]);
+    }
+
+    // ---- epilogue: o = acc / (l * R_k), lse = ln2 * (m + log2 l); NaN / -inf for empty rows
+    if (live) {
+      if (n_u > 0) {
+        wait(&bars->o_done[u], (n_u - 1) & 1, 0x300 + u);
+        tc_fence_after();
+      }
+      const bool empty = !(l > 0.f);
+      float inv = empty ? 0.f : 1.f / (l * rk);
+      float lse = empty ? -CUDART_INF_F : (m + log2f(l)) * kLn2;
+      const bool passthrough = (n_u == 0) && load_state;  // nothing visible: carry the state over
+      if (passthrough) {
+        lse = p.state_lse[rh];
+        inv = 1.f;
+      }
+      const bool none = passthrough ? (lse == -CUDART_INF_F) : empty;
+      __nv_bfloat16* orow = store_state ? nullptr : static_cast<__nv_bfloat16*>(p.o) + rh * D;
+      float* srow = (store_state || passthrough) ? p.state_o + rh * D : nullptr;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t r[32];
+        if (n_u > 0) {
+          tmem_ld32(tO + c * 32, r);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e)
+            r[e] = (passthrough && !none) ? __float_as_uint(srow[c * 32 + e]) : 0u;
+        }
+        if (store_state) {
+          if (!passthrough) {
+#pragma unroll
+            for (int e = 0; e < 32; e += 4) {
+              float4 v = make_float4(__uint_as_float(r[e]) * inv, __uint_as_float(r[e + 1]) * inv,
+                                     __uint_as_float(r[e + 2]) * inv, __uint_as_float(r[e + 3]) * inv);
+              *reinterpret_cast<float4*>(srow + c * 32 + e) = v;
+            }
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; e += 8) {
+            uint32_t w[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const float x0 = none ? CUDART_NAN_F : __uint_as_float(r[e + 2 * k]) * inv;
+              const float x1 = none ? CUDART_NAN_F : __uint_as_float(r[e + 2 * k + 1]) * inv;
+              w[k] = pack_bf16(x0, x1);
+            }
+            *reinterpret_cast<uint4*>(orow + c * 32 + e) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+      }
+      if (store_state) {
+        if (!passthrough) p.state_lse[rh] = lse;
+      } else if (p.lse != nullptr) {
+        p.lse[rh] = lse;
+      }
+    }
+  } else if (warp < kMmaWarp) {
+    // ------------------------------------------------------------------ rebuild Q, then K or V tiles
+    const int rt = threadIdx.x - kSoftmaxWarps * 32;  // 0..255
+    const float qscale = p.sm_scale * kLog2e / ((float)p.rank_q * (float)p.rank_k);
+    for (int u = 0; u < 2; ++u) {
+      if (q0 + u * kUnitRows < p.lq)
+        rebuild_tile<D>(sQ + u * kTileBytes, qa, p.qa.stride[1], p.qa.stride[2], qb, p.qb.stride[1],
+                        p.qb.stride[2], p.rank_q, q0 + u * kUnitRows, qscale, rt, kRebuildWarps * 32);
+    }
+    fence_async_smem();
+    mbar_arrive(&bars->q_full);
+
+    const bool is_k = rt < kRebuildWarps * 16;
+    const int t = is_k ? rt : rt - kRebuildWarps * 16;
+    const __nv_bfloat16* fa = is_k ? ka : va;
+    const __nv_bfloat16* fb = is_k ? kb : vb;
+    const TpaFactor& sa = is_k ? p.ka : p.va;
+    const TpaFactor& sb = is_k ? p.kb : p.vb;
+    uint8_t* stages = is_k ? sK : sV;
+    uint64_t* full = is_k ? bars->k_full : bars->v_full;
+    uint64_t* empty = is_k ? bars->k_empty : bars->v_empty;
+    for (int j = 0; j < n_tiles; ++j) {
+      const int s = j & 1;
+      if (j >= 2) wait(&empty[s], ((j >> 1) - 1) & 1, is_k ? 0x400 : 0x500);
+      rebuild_tile<D>(stages + s * kTileBytes, fa, sa.stride[1], sa.stride[2], fb, sb.stride[1],
+                      sb.stride[2], p.rank_k, (int64_t)j * kTileKv, 1.f, t, kRebuildWarps * 16);
+      fence_async_smem();
+      mbar_arrive(&full[s]);
+    }
+  } else {
+    // ------------------------------------------------------------------ MMA issue (one thread)
+    if (lane == 0 && n_tiles > 0) {
+      const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), aV = smem_u32(sV);
+      auto issue_s = [&](int u, int j) {
+        const uint32_t qbase = aQ + u * kTileBytes, kbase = aK + (j & 1) * kTileBytes;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t off = (ks >> 2) * (kUnitRows * 128) + (ks & 3) * 32;
+          mma_ss(tmem + u * 128, make_desc(qbase + off, 16, 1024), make_desc(kbase + off, 16, 1024),
+                 kIdescS, ks > 0);
+        }
+        tc_commit(&bars->s_full[u]);
+      };
+      auto issue_pv = [&](int u, int j, bool acc) {
+        const uint32_t vbase = aV + (j & 1) * kTileBytes;
+#pragma unroll
+        for (int ks = 0; ks < kTileKv / 16; ++ks) {
+          mma_ts(tmem + kOCol + u * D, tmem + u * 128 + ks * 8,
+                 make_desc(vbase + ks * 2048, kTileKv * 128, 1024), kIdescPV, (acc || ks > 0) ? 1u : 0u);
+        }
+        tc_commit(&bars->o_done[u]);
+      };
+      const bool acc0 = load_state;
+
+      wait(&bars->q_full, 0, 0x600);
+      wait(&bars->k_full[0], 0, 0x601);
+      tc_fence_after();
+      for (int u = 0; u < 2; ++u)
+        if (n_vis[u] > 0) issue_s(u, 0);
+      tc_commit(&bars->k_empty[0]);
+      for (int j = 0; j < n_tiles; ++j) {
+        wait(&bars->v_full[j & 1], (j >> 1) & 1, 0x602);
+        tc_fence_after();
+        bool k_waited = false;
+        for (int u = 0; u < 2; ++u) {
+          if (j < n_vis[u]) {
+            wait(&bars->p_ready[u], j & 1, 0x610 + u);
+            tc_fence_after();
+            issue_pv(u, j, acc0 || j > 0);
+          }
+          if (j + 1 < n_vis[u]) {
+            if (!k_waited) {
+              wait(&bars->k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, 0x603);
+              tc_fence_after();
+              k_waited = true;
+            }
+            issue_s(u, j + 1);
+          }
+        }
+        tc_commit(&bars->v_empty[j & 1]);
+        if (j + 1 < n_tiles) tc_commit(&bars->k_empty[(j + 1) & 1]);
+      }
+    }
+    __syncwarp();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 512);
+}
+
+template <int D>
+constexpr size_t smem_bytes() {
+  return 6 * (size_t)kUnitRows * D * 2 + sizeof(Barriers) + 1024;
+}
+
+inline bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; }
+inline bool factor_vec_ok(const TpaFactor& f) {
+  return aligned16(f.ptr) && f.stride[0] % 8 == 0 && f.stride[1] % 8 == 0 && f.stride[2] % 8 == 0;
+}
+
+}  // namespace
+
+bool sm100_supported(const Params& p) {
+  if (p.dtype != TPA_DTYPE_BF16) return false;
+  if (p.dk != p.dv || (p.dk != 64 && p.dk != 128)) return false;
+  if (p.lq % kUnitRows != 0 || p.lk % kTileKv != 0) return false;
+  // the dim factors are read with 16-byte loads; the output rows are written with them
+  if (!factor_vec_ok(p.qb) || !factor_vec_ok(p.kb) || !factor_vec_ok(p.vb)) return false;
+  if (!(p.flags & TPA_FLAG_STATE_STORE) && !aligned16(p.o)) return false;
+  if ((p.flags & (TPA_FLAG_STATE_STORE | TPA_FLAG_STATE_LOAD)) && !aligned16(p.state_o)) return false;
+  return true;
+}
+
+size_t sm100_workspace_bytes(const Params&) { return 0; }
+
+cudaError_t launch_sm100(const Params& p, void* /*workspace*/, TpaKernelInfo* info, bool dry_run,
+                         cudaStream_t stream) {
+  const size_t smem = p.dk == 128 ? smem_bytes<128>() : smem_bytes<64>();
+  dim3 grid(p.heads, (p.lq + 2 * kUnitRows - 1) / (2 * kUnitRows), p.batch);
+  if (info) {
+    info->kernel = TPA_KERNEL_SM100;
+    info->block_q = 2 * kUnitRows;
+    info->block_kv = kTileKv;
+    info->threads = kThreads;
+    info->grid[0] = grid.x;
+    info->grid[1] = grid.y;
+    info->grid[2] = grid.z;
+    info->smem_bytes = (int)smem;
+    info->launches = 1;
+  }
+  if (dry_run) return cudaSuccess;
+  cudaError_t e;
+  if (p.dk == 128) {
+    e = cudaFuncSetAttribute(tpa_fwd_sm100_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    tpa_fwd_sm100_kernel<128><<<grid, kThreads, smem, stream>>>(p);
+  } else {
+    e = cudaFuncSetAttribute(tpa_fwd_sm100_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    tpa_fwd_sm100_kernel<64><<<grid, kThreads, smem, stream>>>(p);
+  }
+  count_launch(1);
+  return cudaGetLastError();
+}
+
 }  // namespace tpa

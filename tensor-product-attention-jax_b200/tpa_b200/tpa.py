@@ -55,6 +55,17 @@ def _workspace(device, nbytes):
     return ws
 
 
+def device_status(device=None):
+    """Synchronise and read the status block of the last tensor-core launch on the current
+    stream of `device`: (status code, [flag, where, block, spins])."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+    stream = torch.cuda.current_stream(device).cuda_stream
+    ws = _workspaces.get((device, stream))
+    detail = (C.c_uint32 * 4)()
+    st = _capi.lib.tpa_read_status(ws.data_ptr() if ws is not None else None, C.c_void_p(stream), C.byref(detail))
+    return st, list(detail)
+
+
 def _factor(x, col0):
     f = _capi.TpaFactor()
     f.ptr = x.data_ptr() + col0 * x.element_size()
@@ -189,9 +200,9 @@ def query_kernel(q, k, v, num_heads, kernel="auto", causal=False, segments=False
     a.qa, a.qb = _factor(q, 0), _factor(q, num_heads)
     a.ka, a.kb = _factor(k, 0), _factor(k, num_heads)
     a.va, a.vb = _factor(v, 0), _factor(v, num_heads)
-    a.o = 1  # any non-null value: nothing is dereferenced by the query
+    a.o = 4096  # any aligned non-null value: nothing is dereferenced by the query
     if segments:
-        a.q_segment_ids = a.kv_segment_ids = 1
+        a.q_segment_ids = a.kv_segment_ids = 4096
     a.flags = _capi.FLAG_CAUSAL if causal else 0
     a.kernel = _capi.KERNELS[kernel]
     info = _capi.TpaKernelInfo()

@@ -139,6 +139,30 @@ def test_bitwise_reproducible():
 # --------------------------------------------------------------------------- bf16 configurations
 
 
+@pytest.fixture(autouse=True)
+def no_device_timeout():
+    """After every test: no bounded device-side wait may have run out."""
+    yield
+    st, detail = tpa_b200.tpa.device_status()
+    assert st == 0, (st, [hex(x) for x in detail])
+
+
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("t", [128, 256, 384, 1024])
+@pytest.mark.parametrize("causal", [False, True])
+def test_sm100_small(d, t, causal):
+    """The tensor-core kernel on one to a few tiles, all rows checked, LSE included."""
+    q, k, v = orc.make_factors(50 + t + d, 2, t, t, 3, 2, 8, d, d)
+    tq, tk, tv = dev(q, torch.bfloat16), dev(k, torch.bfloat16), dev(v, torch.bfloat16)
+    assert tpa_b200.tpa.query_kernel(tq, tk, tv, 8, causal=causal)["kernel"] == "sm100"
+    o, lse = tpa_b200.tpa.fwd_device(tq, tk, tv, 8, None, None, d**-0.5, causal, kernel="sm100")
+    ref, lref = orc.tpa_reference_torch(tq.float().cpu(), tk.float().cpu(), tv.float().cpu(), 8,
+                                        sm_scale=d**-0.5, causal=causal, return_lse=True)
+    diff = (o.float().cpu() - ref).abs()
+    assert diff.max() <= 2e-2 and diff.mean() <= 5e-3, (float(diff.max()), float(diff.mean()))
+    assert (lse.cpu() - lref).abs().max() <= 1e-2
+
+
 def bf16_case(seed, b, t, h, d, rq, rk, causal, kernel="auto", rows=None, segs=None, scale=1.0):
     q, k, v = orc.make_factors(seed, b, t, t, rq, rk, h, d, d)
     tq, tk, tv = dev(q * scale, torch.bfloat16), dev(k, torch.bfloat16), dev(v, torch.bfloat16)
