@@ -38,8 +38,17 @@ enum {
 
 enum { TPA_DTYPE_F32 = 0, TPA_DTYPE_BF16 = 1 };
 
-/* Which kernel runs.  AUTO picks SM100 when the shape allows, else SIMT. */
-enum { TPA_KERNEL_AUTO = 0, TPA_KERNEL_SIMT = 1, TPA_KERNEL_SM100 = 2 };
+/* Which kernel runs.  AUTO picks a tensor-core variant when the shape allows, else SIMT.
+ * SM100 = tensor cores, variant chosen by the library; FUSED rebuilds Q/K/V from the factors
+ * inside the attention kernel (no scratch); STAGED rebuilds every tile once into the
+ * workspace with a staging kernel and then runs the attention kernel on those tiles. */
+enum {
+  TPA_KERNEL_AUTO = 0,
+  TPA_KERNEL_SIMT = 1,
+  TPA_KERNEL_SM100 = 2,
+  TPA_KERNEL_SM100_FUSED = 3,
+  TPA_KERNEL_SM100_STAGED = 4
+};
 
 /* flags */
 enum {
@@ -88,7 +97,7 @@ typedef struct TpaFwdArgs {
 } TpaFwdArgs;
 
 typedef struct TpaKernelInfo {
-  int32_t kernel;       /* TPA_KERNEL_SIMT or TPA_KERNEL_SM100                             */
+  int32_t kernel;       /* TPA_KERNEL_SIMT, TPA_KERNEL_SM100_FUSED or TPA_KERNEL_SM100_STAGED */
   int32_t block_q, block_kv; /* tile sizes the kernel will use                             */
   int32_t threads;      /* threads per CTA                                                 */
   int32_t grid[3];

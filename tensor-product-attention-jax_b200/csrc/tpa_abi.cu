@@ -41,7 +41,7 @@ static int validate(const TpaFwdArgs* a, Params* p) {
   if (!store && a->o == nullptr) return TPA_ERR_BAD_ARG;
   if (a->flags & ~(uint32_t)(TPA_FLAG_CAUSAL | TPA_FLAG_STATE_LOAD | TPA_FLAG_STATE_STORE))
     return TPA_ERR_BAD_ARG;
-  if (a->kernel < TPA_KERNEL_AUTO || a->kernel > TPA_KERNEL_SM100) return TPA_ERR_BAD_ARG;
+  if (a->kernel < TPA_KERNEL_AUTO || a->kernel > TPA_KERNEL_SM100_STAGED) return TPA_ERR_BAD_ARG;
   if (a->heads > 65535 || a->batch > 65535) return TPA_ERR_UNSUPPORTED;
   if (a->dk > 256 || a->dv > 256) return TPA_ERR_UNSUPPORTED;
   p->dtype = a->dtype;
@@ -60,8 +60,10 @@ static int validate(const TpaFwdArgs* a, Params* p) {
 
 static int choose(const TpaFwdArgs* a, const Params& p, int* kernel) {
   const bool tc = sm100_supported(p);
-  if (a->kernel == TPA_KERNEL_SM100 && !tc) return TPA_ERR_KERNEL_FORCED;
-  *kernel = (a->kernel == TPA_KERNEL_SIMT || !tc) ? TPA_KERNEL_SIMT : TPA_KERNEL_SM100;
+  if (a->kernel >= TPA_KERNEL_SM100 && !tc) return TPA_ERR_KERNEL_FORCED;
+  if (a->kernel == TPA_KERNEL_SIMT || !tc) *kernel = TPA_KERNEL_SIMT;
+  else if (a->kernel == TPA_KERNEL_SM100_FUSED || a->kernel == TPA_KERNEL_SM100_STAGED) *kernel = a->kernel;
+  else *kernel = sm100_pick_variant(p);
   return TPA_OK;
 }
 
@@ -96,8 +98,8 @@ size_t tpa_fwd_workspace_bytes(const TpaFwdArgs* args) {
   Params p;
   int kernel;
   if (validate(args, &p) != TPA_OK || choose(args, p, &kernel) != TPA_OK) return 0;
-  if (kernel != TPA_KERNEL_SM100) return 0;
-  return kStatusBytes + sm100_workspace_bytes(p);
+  if (kernel == TPA_KERNEL_SIMT) return 0;
+  return kStatusBytes + sm100_workspace_bytes(p, kernel);
 }
 
 int tpa_query_kernel(const TpaFwdArgs* args, TpaKernelInfo* info) {
@@ -109,8 +111,8 @@ int tpa_query_kernel(const TpaFwdArgs* args, TpaKernelInfo* info) {
   if (st != TPA_OK) return st;
   st = choose(args, p, &kernel);
   if (st != TPA_OK) return st;
-  cudaError_t e = (kernel == TPA_KERNEL_SM100) ? launch_sm100(p, nullptr, info, true, nullptr)
-                                               : launch_simt(p, info, true, nullptr);
+  cudaError_t e = (kernel != TPA_KERNEL_SIMT) ? launch_sm100(p, kernel, nullptr, info, true, nullptr)
+                                              : launch_simt(p, info, true, nullptr);
   return e == cudaSuccess ? TPA_OK : fail_cuda(e);
 }
 
@@ -123,15 +125,15 @@ int tpa_fwd(const TpaFwdArgs* args, void* workspace, size_t workspace_bytes, voi
   if (st != TPA_OK) return st;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   cudaError_t e;
-  if (kernel == TPA_KERNEL_SM100) {
-    const size_t need = kStatusBytes + sm100_workspace_bytes(p);
+  if (kernel != TPA_KERNEL_SIMT) {
+    const size_t need = kStatusBytes + sm100_workspace_bytes(p, kernel);
     if (workspace == nullptr || workspace_bytes < need ||
         (reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
       return TPA_ERR_WORKSPACE;
     p.status = static_cast<uint32_t*>(workspace);
     e = cudaMemsetAsync(workspace, 0, kStatusBytes, s);
     if (e != cudaSuccess) return fail_cuda(e);
-    e = launch_sm100(p, static_cast<char*>(workspace) + kStatusBytes, nullptr, false, s);
+    e = launch_sm100(p, kernel, static_cast<char*>(workspace) + kStatusBytes, nullptr, false, s);
   } else {
     e = launch_simt(p, nullptr, false, s);
   }

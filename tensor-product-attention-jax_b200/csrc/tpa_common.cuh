@@ -30,9 +30,10 @@ struct Params {
 // Launchers: enqueue on `stream`, return a cudaError_t.  `info` is filled either way.
 cudaError_t launch_simt(const Params& p, TpaKernelInfo* info, bool dry_run, cudaStream_t stream);
 bool sm100_supported(const Params& p);
-size_t sm100_workspace_bytes(const Params& p);
-cudaError_t launch_sm100(const Params& p, void* workspace, TpaKernelInfo* info, bool dry_run,
-                         cudaStream_t stream);
+int sm100_pick_variant(const Params& p);  // TPA_KERNEL_SM100_FUSED or TPA_KERNEL_SM100_STAGED
+size_t sm100_workspace_bytes(const Params& p, int variant);
+cudaError_t launch_sm100(const Params& p, int variant, void* workspace, TpaKernelInfo* info,
+                         bool dry_run, cudaStream_t stream);
 
 void count_launch(int n);
 

@@ -2,19 +2,31 @@
 // multiples of 128.  Replaces _fwd_kernel (tpa/tpa.py:245-443) for those shapes.
 //
 // One CTA owns 256 query rows (two 128-row units) of one head of one batch element and
-// walks the key/value rows 128 at a time.  Roles, by warp:
+// walks the key/value rows 128 at a time.  Two variants share the softmax and MMA roles and
+// differ in where the per-head Q, K, V tiles are rebuilt from the rank factors
+// (Q, K, V = sums over rank of a[row, r, head] * b[row, r, :], tpa/tpa.py:317,364,417):
 //
+//   FUSED   the attention kernel rebuilds them itself: 8 warps turn factor rows into
+//           shared-memory tiles while the tensor pipe works.  No scratch memory.  Every CTA
+//           of a head rebuilds the K/V tiles it visits, so this is the choice when there is
+//           one CTA per head (lq <= 256) and the rebuild is not repeated.
+//   STAGED  a staging kernel rebuilds every 128-row tile of Q, K and V once, already in the
+//           swizzled shared-memory image, into caller scratch; the attention kernel then
+//           only moves 16/32 KB tiles with cp.async.bulk.  For long sequences this removes
+//           the lq/256-fold repetition of the rebuild (64x on average at T = 32768).
+//
+// Roles, by warp:
 //   warps 0-3 / 4-7   online softmax of unit 0 / unit 1 (one thread per query row: TMEM lane)
-//   warps 8-11        rebuild the K tile of this head from the rank factors into shared memory
-//   warps 12-15       rebuild the V tile likewise (all eight rebuild Q once at the start)
-//   warp 16           issues tcgen05.mma: S_u = Q_u K^T (fp32 in TMEM), O_u += P_u V
+//   FUSED  warps 8-11 / 12-15  rebuild the K / V tile (all eight rebuild Q once at the start)
+//          warp 16             issues tcgen05.mma: S_u = Q_u K^T (fp32 in TMEM), O_u += P_u V
+//   STAGED warp 8              one thread issues the bulk copies of the staged tiles
+//          warp 9              issues tcgen05.mma
 //
-// Q, K, V are sums over rank of a[row, r, head] * b[row, r, :] (tpa/tpa.py:317,364,417).  The
-// 1/R_q, 1/R_k means and sm_scale * log2(e) are folded into Q once; the 1/R_k of V is applied
-// with the final 1/l.  K and V tiles are double buffered; the rebuilt tiles are written in
-// the 128-byte-swizzled layout the tcgen05 shared-memory descriptors describe.  P (bf16)
-// overwrites S in TMEM and feeds the second MMA from there.  The two units alternate on the
-// tensor pipe, so the softmax of one overlaps the MMAs of the other.
+// The 1/R_q, 1/R_k means and sm_scale * log2(e) are folded into Q once; the 1/R_k of V is
+// applied with the final 1/l.  K and V tiles are double buffered, in the 128-byte-swizzled
+// layout the tcgen05 shared-memory descriptors describe.  P (bf16) overwrites S in TMEM and
+// feeds the second MMA from there.  The two units alternate on the tensor pipe, so the
+// softmax of one overlaps the MMAs of the other.
 //
 // The running maximum is only raised when the new tile exceeds it by more than 2^8 (the
 // accumulator and row sum are then rescaled); the final 1/l division makes the result
@@ -35,8 +47,12 @@ using namespace ptx;
 
 constexpr int kSoftmaxWarps = 8;
 constexpr int kRebuildWarps = 8;
-constexpr int kMmaWarp = kSoftmaxWarps + kRebuildWarps;
-constexpr int kThreads = (kMmaWarp + 1) * 32;  // 544
+template <bool STAGED>
+struct Roles {
+  static constexpr int kProducerWarps = STAGED ? 1 : kRebuildWarps;
+  static constexpr int kMmaWarp = kSoftmaxWarps + kProducerWarps;
+  static constexpr int kThreads = (kMmaWarp + 1) * 32;  // 320 staged, 544 fused
+};
 constexpr int kUnitRows = 128;
 constexpr int kTileKv = 128;
 constexpr float kLog2e = 1.4426950408889634f;
@@ -124,8 +140,82 @@ __device__ __forceinline__ void rebuild_tile(uint8_t* dst, const __nv_bfloat16* 
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Staging kernel: one CTA rebuilds one 128-row tile of Q, K or V for 8 heads and writes each
+// head's tile as the exact shared-memory image (64-column sub-tiles of 16 KB, 128-byte swizzle)
+// at ws[((batch * heads + head) * tiles + tile) * tile_bytes].
+// grid = (lq/128 + 2 * lk/128, heads/8, batch), 256 threads.
 template <int D>
-__global__ void __launch_bounds__(kThreads, 1) tpa_fwd_sm100_kernel(const Params p) {
+__global__ void __launch_bounds__(256) tpa_stage_tiles_kernel(const Params p, uint8_t* ws_q,
+                                                              uint8_t* ws_k, uint8_t* ws_v,
+                                                              float qscale) {
+  constexpr int CH = D / 8;
+  constexpr int kTileBytes = kUnitRows * D * 2;
+  const int nq = p.lq / kUnitRows, nk = p.lk / kTileKv;
+  int tile = blockIdx.x;
+  const TpaFactor *fa, *fb;
+  uint8_t* ws;
+  int rank, ntiles;
+  float scale;
+  if (tile < nq) {
+    fa = &p.qa; fb = &p.qb; ws = ws_q; rank = p.rank_q; ntiles = nq; scale = qscale;
+  } else if (tile < nq + nk) {
+    tile -= nq;
+    fa = &p.ka; fb = &p.kb; ws = ws_k; rank = p.rank_k; ntiles = nk; scale = 1.f;
+  } else {
+    tile -= nq + nk;
+    fa = &p.va; fb = &p.vb; ws = ws_v; rank = p.rank_k; ntiles = nk; scale = 1.f;
+  }
+  const int hg = blockIdx.y, batch = blockIdx.z;
+  const __nv_bfloat16* a = static_cast<const __nv_bfloat16*>(fa->ptr) + batch * fa->stride[0] + hg * 8;
+  const __nv_bfloat16* b = static_cast<const __nv_bfloat16*>(fb->ptr) + batch * fb->stride[0];
+  const int chunk = threadIdx.x % CH, r_in = threadIdx.x / CH;
+  uint8_t* out0 = ws + (((int64_t)batch * p.heads + hg * 8) * ntiles + tile) * kTileBytes +
+                  (chunk >> 3) * (kUnitRows * 128);
+  for (int row = r_in; row < kUnitRows; row += 256 / CH) {
+    const int64_t g = (int64_t)tile * kUnitRows + row;
+    const __nv_bfloat16* ap = a + g * fa->stride[1];
+    const __nv_bfloat16* bp = b + g * fb->stride[1] + chunk * 8;
+    float acc[8][8];
+#pragma unroll
+    for (int h = 0; h < 8; ++h)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[h][e] = 0.f;
+#pragma unroll 2
+    for (int r = 0; r < rank; ++r) {
+      const uint4 bv = __ldg(reinterpret_cast<const uint4*>(bp + r * fb->stride[2]));
+      const uint4 av = __ldg(reinterpret_cast<const uint4*>(ap + r * fa->stride[2]));
+      const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w}, aw[4] = {av.x, av.y, av.z, av.w};
+      float bf[8];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        bf[2 * e] = __uint_as_float(bw[e] << 16);
+        bf[2 * e + 1] = __uint_as_float(bw[e] & 0xffff0000u);
+      }
+#pragma unroll
+      for (int h = 0; h < 8; ++h) {
+        const float ah = __uint_as_float((h & 1) ? (aw[h >> 1] & 0xffff0000u) : (aw[h >> 1] << 16));
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[h][e] = fmaf(ah, bf[e], acc[h][e]);
+      }
+    }
+    const uint32_t off = sw128_offset(row, chunk & 7);
+#pragma unroll
+    for (int h = 0; h < 8; ++h) {
+      uint4 o;
+      o.x = pack_bf16(acc[h][0] * scale, acc[h][1] * scale);
+      o.y = pack_bf16(acc[h][2] * scale, acc[h][3] * scale);
+      o.z = pack_bf16(acc[h][4] * scale, acc[h][5] * scale);
+      o.w = pack_bf16(acc[h][6] * scale, acc[h][7] * scale);
+      *reinterpret_cast<uint4*>(out0 + (int64_t)h * ntiles * kTileBytes + off) = o;
+    }
+  }
+}
+
+template <int D, bool STAGED>
+__global__ void __launch_bounds__(Roles<STAGED>::kThreads, 1)
+tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, const uint8_t* ws_v) {
+  constexpr int kMmaWarp = Roles<STAGED>::kMmaWarp;
   constexpr int kTileBytes = kUnitRows * D * 2;  // one Q unit, one K stage or one V stage
   constexpr uint32_t kIdescS = make_idesc(128, kTileKv, false, false);
   constexpr uint32_t kIdescPV = make_idesc(128, D, false, true);
@@ -167,10 +257,10 @@ __global__ void __launch_bounds__(kThreads, 1) tpa_fwd_sm100_kernel(const Params
   const int n_tiles = max(n_vis[0], n_vis[1]);
 
   if (threadIdx.x == 0) {
-    mbar_init(&bars->q_full, kRebuildWarps * 32);
+    mbar_init(&bars->q_full, STAGED ? 1 : kRebuildWarps * 32);
     for (int s = 0; s < 2; ++s) {
-      mbar_init(&bars->k_full[s], kRebuildWarps * 16);
-      mbar_init(&bars->v_full[s], kRebuildWarps * 16);
+      mbar_init(&bars->k_full[s], STAGED ? 1 : kRebuildWarps * 16);
+      mbar_init(&bars->v_full[s], STAGED ? 1 : kRebuildWarps * 16);
       mbar_init(&bars->k_empty[s], 1);
       mbar_init(&bars->v_empty[s], 1);
       mbar_init(&bars->s_full[s], 1);
@@ -395,6 +485,28 @@ __global__ void __launch_bounds__(kThreads, 1) tpa_fwd_sm100_kernel(const Params
       }
     }
   } else if (warp < kMmaWarp) {
+   if constexpr (STAGED) {
+    // ------------------------------------------------------------------ bulk copies of staged tiles
+    if (lane == 0) {
+      const int64_t bh = (int64_t)batch * p.heads + head;
+      const uint8_t* gq = ws_q + (bh * (p.lq / kUnitRows) + pair * 2) * kTileBytes;
+      const uint8_t* gk = ws_k + bh * n_kv * kTileBytes;
+      const uint8_t* gv = ws_v + bh * n_kv * kTileBytes;
+      const int units = (q0 + kUnitRows < p.lq) ? 2 : 1;
+      mbar_arrive_expect_tx(&bars->q_full, units * kTileBytes);
+      bulk_g2s(sQ, gq, units * kTileBytes, &bars->q_full);
+      for (int j = 0; j < n_tiles; ++j) {
+        const int s = j & 1;
+        if (j >= 2) wait(&bars->k_empty[s], ((j >> 1) - 1) & 1, 0x400);
+        mbar_arrive_expect_tx(&bars->k_full[s], kTileBytes);
+        bulk_g2s(sK + s * kTileBytes, gk + (int64_t)j * kTileBytes, kTileBytes, &bars->k_full[s]);
+        if (j >= 2) wait(&bars->v_empty[s], ((j >> 1) - 1) & 1, 0x500);
+        mbar_arrive_expect_tx(&bars->v_full[s], kTileBytes);
+        bulk_g2s(sV + s * kTileBytes, gv + (int64_t)j * kTileBytes, kTileBytes, &bars->v_full[s]);
+      }
+    }
+    __syncwarp();
+   } else {
     // ------------------------------------------------------------------ rebuild Q, then K or V tiles
     const int rt = threadIdx.x - kSoftmaxWarps * 32;  // 0..255
     const float qscale = p.sm_scale * kLog2e / ((float)p.rank_q * (float)p.rank_k);
@@ -423,6 +535,7 @@ __global__ void __launch_bounds__(kThreads, 1) tpa_fwd_sm100_kernel(const Params
       fence_async_smem();
       mbar_arrive(&full[s]);
     }
+   }
   } else {
     // ------------------------------------------------------------------ MMA issue (one thread)
     if (lane == 0 && n_tiles > 0) {
@@ -494,6 +607,19 @@ inline bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr
 inline bool factor_vec_ok(const TpaFactor& f) {
   return aligned16(f.ptr) && f.stride[0] % 8 == 0 && f.stride[1] % 8 == 0 && f.stride[2] % 8 == 0;
 }
+inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
+inline size_t staged_q_bytes(const Params& p) { return align256((size_t)p.batch * p.heads * p.lq * p.dk * 2); }
+inline size_t staged_kv_bytes(const Params& p) { return align256((size_t)p.batch * p.heads * p.lk * p.dk * 2); }
+
+template <int D, bool STAGED>
+cudaError_t launch_attn(const Params& p, const uint8_t* wq, const uint8_t* wk, const uint8_t* wv,
+                        dim3 grid, size_t smem, cudaStream_t stream) {
+  auto kern = tpa_fwd_sm100_kernel<D, STAGED>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  kern<<<grid, Roles<STAGED>::kThreads, smem, stream>>>(p, wq, wk, wv);
+  return cudaGetLastError();
+}
 
 }  // namespace
 
@@ -501,43 +627,63 @@ bool sm100_supported(const Params& p) {
   if (p.dtype != TPA_DTYPE_BF16) return false;
   if (p.dk != p.dv || (p.dk != 64 && p.dk != 128)) return false;
   if (p.lq % kUnitRows != 0 || p.lk % kTileKv != 0) return false;
-  // the dim factors are read with 16-byte loads; the output rows are written with them
+  if (p.heads % 8 != 0) return false;
+  // factors are read with 16-byte loads; output rows are written with them
+  if (!factor_vec_ok(p.qa) || !factor_vec_ok(p.ka) || !factor_vec_ok(p.va)) return false;
   if (!factor_vec_ok(p.qb) || !factor_vec_ok(p.kb) || !factor_vec_ok(p.vb)) return false;
   if (!(p.flags & TPA_FLAG_STATE_STORE) && !aligned16(p.o)) return false;
   if ((p.flags & (TPA_FLAG_STATE_STORE | TPA_FLAG_STATE_LOAD)) && !aligned16(p.state_o)) return false;
   return true;
 }
 
-size_t sm100_workspace_bytes(const Params&) { return 0; }
+// The staged variant pays for itself once more than one CTA per head walks the K/V tiles.
+int sm100_pick_variant(const Params& p) {
+  return p.lq > 2 * kUnitRows ? TPA_KERNEL_SM100_STAGED : TPA_KERNEL_SM100_FUSED;
+}
 
-cudaError_t launch_sm100(const Params& p, void* /*workspace*/, TpaKernelInfo* info, bool dry_run,
-                         cudaStream_t stream) {
+size_t sm100_workspace_bytes(const Params& p, int variant) {
+  if (variant != TPA_KERNEL_SM100_STAGED) return 0;
+  return staged_q_bytes(p) + 2 * staged_kv_bytes(p);
+}
+
+cudaError_t launch_sm100(const Params& p, int variant, void* workspace, TpaKernelInfo* info,
+                         bool dry_run, cudaStream_t stream) {
+  const bool staged = variant == TPA_KERNEL_SM100_STAGED;
   const size_t smem = p.dk == 128 ? smem_bytes<128>() : smem_bytes<64>();
   dim3 grid(p.heads, (p.lq + 2 * kUnitRows - 1) / (2 * kUnitRows), p.batch);
   if (info) {
-    info->kernel = TPA_KERNEL_SM100;
+    info->kernel = variant;
     info->block_q = 2 * kUnitRows;
     info->block_kv = kTileKv;
-    info->threads = kThreads;
+    info->threads = staged ? Roles<true>::kThreads : Roles<false>::kThreads;
     info->grid[0] = grid.x;
     info->grid[1] = grid.y;
     info->grid[2] = grid.z;
     info->smem_bytes = (int)smem;
-    info->launches = 1;
+    info->launches = staged ? 2 : 1;
   }
   if (dry_run) return cudaSuccess;
   cudaError_t e;
-  if (p.dk == 128) {
-    e = cudaFuncSetAttribute(tpa_fwd_sm100_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  uint8_t *wq = nullptr, *wk = nullptr, *wv = nullptr;
+  if (staged) {
+    wq = static_cast<uint8_t*>(workspace);
+    wk = wq + staged_q_bytes(p);
+    wv = wk + staged_kv_bytes(p);
+    const float qscale = p.sm_scale * kLog2e / ((float)p.rank_q * (float)p.rank_k);
+    dim3 sgrid(p.lq / kUnitRows + 2 * (p.lk / kTileKv), p.heads / 8, p.batch);
+    if (p.dk == 128) tpa_stage_tiles_kernel<128><<<sgrid, 256, 0, stream>>>(p, wq, wk, wv, qscale);
+    else tpa_stage_tiles_kernel<64><<<sgrid, 256, 0, stream>>>(p, wq, wk, wv, qscale);
+    e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-    tpa_fwd_sm100_kernel<128><<<grid, kThreads, smem, stream>>>(p);
+    count_launch(1);
+    e = p.dk == 128 ? launch_attn<128, true>(p, wq, wk, wv, grid, smem, stream)
+                    : launch_attn<64, true>(p, wq, wk, wv, grid, smem, stream);
   } else {
-    e = cudaFuncSetAttribute(tpa_fwd_sm100_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
-    tpa_fwd_sm100_kernel<64><<<grid, kThreads, smem, stream>>>(p);
+    e = p.dk == 128 ? launch_attn<128, false>(p, wq, wk, wv, grid, smem, stream)
+                    : launch_attn<64, false>(p, wq, wk, wv, grid, smem, stream);
   }
-  count_launch(1);
-  return cudaGetLastError();
+  if (e == cudaSuccess) count_launch(1);
+  return e;
 }
 
 }  // namespace tpa

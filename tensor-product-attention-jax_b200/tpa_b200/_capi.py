@@ -21,8 +21,10 @@ TPA_ERR_KERNEL_FORCED = -5
 TPA_ERR_DEVICE_TIMEOUT = -6
 
 DTYPE_F32, DTYPE_BF16 = 0, 1
-KERNEL_AUTO, KERNEL_SIMT, KERNEL_SM100 = 0, 1, 2
-KERNELS = {"auto": KERNEL_AUTO, "simt": KERNEL_SIMT, "sm100": KERNEL_SM100}
+KERNEL_AUTO, KERNEL_SIMT, KERNEL_SM100, KERNEL_SM100_FUSED, KERNEL_SM100_STAGED = 0, 1, 2, 3, 4
+KERNELS = {"auto": KERNEL_AUTO, "simt": KERNEL_SIMT, "sm100": KERNEL_SM100,
+           "sm100_fused": KERNEL_SM100_FUSED, "sm100_staged": KERNEL_SM100_STAGED}
+KERNEL_NAMES = {KERNEL_SIMT: "simt", KERNEL_SM100_FUSED: "sm100_fused", KERNEL_SM100_STAGED: "sm100_staged"}
 FLAG_CAUSAL, FLAG_STATE_LOAD, FLAG_STATE_STORE = 1, 2, 4
 
 # Every symbol include/tpa_b200.h declares.

@@ -208,7 +208,7 @@ def query_kernel(q, k, v, num_heads, kernel="auto", causal=False, segments=False
     info = _capi.TpaKernelInfo()
     _capi.check(_capi.lib.tpa_query_kernel(C.byref(a), C.byref(info)))
     return {
-        "kernel": {1: "simt", 2: "sm100"}[info.kernel],
+        "kernel": _capi.KERNEL_NAMES[info.kernel],
         "block_q": info.block_q,
         "block_kv": info.block_kv,
         "threads": info.threads,

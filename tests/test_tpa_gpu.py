@@ -97,7 +97,8 @@ def test_ragged_shapes_low_level(shape, causal):
     assert_close(l.cpu().numpy(), lref)
 
 
-@pytest.mark.parametrize("dtype,kernel", [(torch.float32, "simt"), (torch.bfloat16, "simt"), (torch.bfloat16, "auto")])
+@pytest.mark.parametrize("dtype,kernel", [(torch.float32, "simt"), (torch.bfloat16, "simt"),
+                                          (torch.bfloat16, "sm100_fused"), (torch.bfloat16, "sm100_staged")])
 @pytest.mark.parametrize("mode", ["reference_local", "global"])
 def test_state_chaining_equals_ring_oracle(dtype, kernel, mode):
     """N ring steps emulated on one GPU through TPA_FLAG_STATE_LOAD/STORE vs the ring oracle."""
@@ -147,15 +148,17 @@ def no_device_timeout():
     assert st == 0, (st, [hex(x) for x in detail])
 
 
+@pytest.mark.parametrize("kernel", ["sm100_fused", "sm100_staged"])
 @pytest.mark.parametrize("d", [64, 128])
 @pytest.mark.parametrize("t", [128, 256, 384, 1024])
 @pytest.mark.parametrize("causal", [False, True])
-def test_sm100_small(d, t, causal):
-    """The tensor-core kernel on one to a few tiles, all rows checked, LSE included."""
+def test_sm100_small(d, t, causal, kernel):
+    """Both tensor-core variants on one to a few tiles, all rows checked, LSE included."""
     q, k, v = orc.make_factors(50 + t + d, 2, t, t, 3, 2, 8, d, d)
     tq, tk, tv = dev(q, torch.bfloat16), dev(k, torch.bfloat16), dev(v, torch.bfloat16)
-    assert tpa_b200.tpa.query_kernel(tq, tk, tv, 8, causal=causal)["kernel"] == "sm100"
-    o, lse = tpa_b200.tpa.fwd_device(tq, tk, tv, 8, None, None, d**-0.5, causal, kernel="sm100")
+    assert tpa_b200.tpa.query_kernel(tq, tk, tv, 8, causal=causal)["kernel"] == (
+        "sm100_staged" if t > 256 else "sm100_fused")
+    o, lse = tpa_b200.tpa.fwd_device(tq, tk, tv, 8, None, None, d**-0.5, causal, kernel=kernel)
     ref, lref = orc.tpa_reference_torch(tq.float().cpu(), tk.float().cpu(), tv.float().cpu(), 8,
                                         sm_scale=d**-0.5, causal=causal, return_lse=True)
     diff = (o.float().cpu() - ref).abs()
@@ -179,7 +182,7 @@ def bf16_case(seed, b, t, h, d, rq, rk, causal, kernel="auto", rows=None, segs=N
     return float(diff.max()), float(diff.mean()), float((lse - lref).abs().max()), float(ref.abs().max())
 
 
-@pytest.mark.parametrize("kernel", ["simt", "auto"])
+@pytest.mark.parametrize("kernel", ["simt", "sm100_fused", "auto"])
 def test_bf16_config1_shape_reduced_batch(kernel):
     """Configuration 1 (bf16 causal T=4096 h=32 d=128 R 6/2/2) at batch 1, sampled rows."""
     rows = torch.cat([torch.arange(0, 4), torch.arange(4092, 4096), torch.randperm(4096, generator=torch.Generator().manual_seed(0))[:120]])
@@ -187,7 +190,7 @@ def test_bf16_config1_shape_reduced_batch(kernel):
     assert mx <= 2e-2 and mean <= 5e-3 and lerr <= 1e-2, (mx, mean, lerr)
 
 
-@pytest.mark.parametrize("kernel", ["simt", "auto"])
+@pytest.mark.parametrize("kernel", ["simt", "sm100_fused", "auto"])
 def test_bf16_config4_noncausal_high_rank(kernel):
     """Configuration 4 (bf16 non-causal T=2048 h=16 d=64 R 8/8/8) at batch 1, with the dense
     attention cross-check: the oracle materialises Q, K, V and runs plain softmax attention."""
@@ -195,7 +198,7 @@ def test_bf16_config4_noncausal_high_rank(kernel):
     assert mx <= 2e-2 and mean <= 5e-3 and lerr <= 1e-2, (mx, mean, lerr)
 
 
-@pytest.mark.parametrize("kernel", ["simt", "auto"])
+@pytest.mark.parametrize("kernel", ["simt", "sm100_fused", "sm100_staged"])
 def test_bf16_peaky_and_segments(kernel):
     """Large logits (online-softmax rescaling really happens) and packed segments."""
     mx, mean, lerr, refmax = bf16_case(6, 2, 512, 8, 128, 4, 4, True, kernel, segs=200, scale=24.0)
