@@ -92,6 +92,25 @@ struct Waiter {
   }
 };
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// two fp32 values in one 64-bit register, for the packed add below
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -340,87 +359,187 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
       const bool diag = causal && ((int64_t)k0 + kTileKv - 1 + p.k_offset > (int64_t)q0u + p.q_offset);
       const bool masked = diag || has_seg;
 
-      // pass 1: row maximum of the (masked) logits; they are already in log2 units
-      float tmax = -CUDART_INF_F;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tS + c * 32, r);
-        tmem_ld_wait();
-        if (masked) {
+      if constexpr (STAGED) {
+        // Pass 1: all four 32-column chunks are fetched at once for the row maximum.  Pass 2
+        // re-reads them two at a time (TMEM reads are cheap; 128 live logits would spill),
+        // the second pair in flight while the first is exponentiated.  Packed fp32 sub / add.
+        auto mask_chunk = [&](uint32_t(&r)[32], int c) {
 #pragma unroll
           for (int e = 0; e < 32; ++e) {
             const int kc = k0 + c * 32 + e;
             bool keep = true;
             if (diag) keep = qpos >= (int64_t)kc + p.k_offset;
             if (has_seg) keep = keep && (qseg == kseg[kc]);
-            if (keep) tmax = fmaxf(tmax, __uint_as_float(r[e]));
+            if (!keep) r[e] = 0xff800000u;  // -inf
           }
-        } else {
+        };
+        float tmax;
+        {
+          uint32_t sc[4][32];
 #pragma unroll
-          for (int e = 0; e < 32; ++e) tmax = fmaxf(tmax, __uint_as_float(r[e]));
-        }
-      }
-      const float m_new = fmaxf(m, tmax);
-      float factor = 1.f;
-      if (m == -CUDART_INF_F) {
-        m = m_new;  // nothing accumulated for this row yet (l = 0, accumulator row is 0)
-      } else if (m_new - m > kRescaleThreshold) {
-        factor = fast_exp2(m - m_new);
-        m = m_new;
-      }
-      if (__any_sync(0xffffffffu, factor != 1.f) && (j > 0 || loaded)) {
-        if (j > 0) {
-          wait(&bars->o_done[u], (j - 1) & 1, 0x200 + u);
-          tc_fence_after();
-        }
-#pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld32(tO + c * 32, r);
+          for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, sc[c]);
           tmem_ld_wait();
+          if (masked) {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * factor);
-          tmem_st32(tO + c * 32, r);
+            for (int c = 0; c < 4; ++c) mask_chunk(sc[c], c);
+          }
+          float cm[4];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            cm[c] = fmaxf(__uint_as_float(sc[c][0]), __uint_as_float(sc[c][1]));
+#pragma unroll
+            for (int e = 2; e < 32; e += 2)
+              cm[c] = max3(cm[c], __uint_as_float(sc[c][e]), __uint_as_float(sc[c][e + 1]));
+          }
+          tmax = fmaxf(fmaxf(cm[0], cm[1]), fmaxf(cm[2], cm[3]));
         }
-        tmem_st_wait();
-      }
-      l *= factor;
-      const float m_sub = (m == -CUDART_INF_F) ? 0.f : m;
-
-      // pass 2: p = 2^(s - m), row sum, bf16 P over the first 64 columns of S
+        uint32_t ra[32], rb[32];
+        tmem_ld32(tS, ra);
+        tmem_ld32(tS + 32, rb);
+        const float m_new = fmaxf(m, tmax);
+        float factor = 1.f;
+        if (m == -CUDART_INF_F) {
+          m = m_new;  // nothing accumulated for this row yet (l = 0, accumulator row is 0)
+        } else if (m_new - m > kRescaleThreshold) {
+          factor = fast_exp2(m - m_new);
+          m = m_new;
+        }
+        if (__any_sync(0xffffffffu, factor != 1.f) && (j > 0 || loaded)) {
+          if (j > 0) {
+            wait(&bars->o_done[u], (j - 1) & 1, 0x200 + u);
+            tc_fence_after();
+          }
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld32(tO + c * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * factor);
+            tmem_st32(tO + c * 32, r);
+          }
+          tmem_st_wait();
+        }
+        l *= factor;
+        const float neg_m = (m == -CUDART_INF_F) ? 0.f : -m;
+        const uint64_t neg_m2 = pack2(neg_m, neg_m);
+        uint64_t lsum[4] = {0ull, 0ull, 0ull, 0ull};
+        auto exp_chunk = [&](const uint32_t(&r)[32], uint32_t* pk) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            float x0, x1;
+            unpack2(add2(pack2(__uint_as_float(r[e]), __uint_as_float(r[e + 1])), neg_m2), x0, x1);
+            const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+            lsum[(e >> 1) & 3] = add2(lsum[(e >> 1) & 3], pack2(p0, p1));
+            pk[e / 2] = pack_bf16(p0, p1);
+          }
+        };
         uint32_t pk[32];
-#pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
-          const int c = half * 2 + cc;
+        tmem_ld_wait();
+        if (masked) {
+          mask_chunk(ra, 0);
+          mask_chunk(rb, 1);
+        }
+        exp_chunk(ra, pk);
+        tmem_ld32(tS + 64, ra);
+        exp_chunk(rb, pk + 16);
+        tmem_ld32(tS + 96, rb);
+        tmem_ld_wait();  // P below overwrites columns [0,32): both re-reads must have landed
+        tmem_st32(tS, pk);
+        if (masked) {
+          mask_chunk(ra, 2);
+          mask_chunk(rb, 3);
+        }
+        exp_chunk(ra, pk);
+        exp_chunk(rb, pk + 16);
+        tmem_st32(tS + 32, pk);
+        float a0, a1, a2, a3;
+        unpack2(add2(lsum[0], lsum[1]), a0, a1);
+        unpack2(add2(lsum[2], lsum[3]), a2, a3);
+        l += (a0 + a1) + (a2 + a3);
+      } else {
+        // pass 1: row maximum of the (masked) logits; they are already in log2 units
+        float tmax = -CUDART_INF_F;
+  #pragma unroll
+        for (int c = 0; c < 4; ++c) {
           uint32_t r[32];
           tmem_ld32(tS + c * 32, r);
           tmem_ld_wait();
-#pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            float s0 = __uint_as_float(r[e]), s1 = __uint_as_float(r[e + 1]);
-            if (masked) {
+          if (masked) {
+  #pragma unroll
+            for (int e = 0; e < 32; ++e) {
               const int kc = k0 + c * 32 + e;
-              bool keep0 = true, keep1 = true;
-              if (diag) {
-                keep0 = qpos >= (int64_t)kc + p.k_offset;
-                keep1 = qpos >= (int64_t)kc + 1 + p.k_offset;
-              }
-              if (has_seg) {
-                keep0 = keep0 && (qseg == kseg[kc]);
-                keep1 = keep1 && (qseg == kseg[kc + 1]);
-              }
-              if (!keep0) s0 = -CUDART_INF_F;
-              if (!keep1) s1 = -CUDART_INF_F;
+              bool keep = true;
+              if (diag) keep = qpos >= (int64_t)kc + p.k_offset;
+              if (has_seg) keep = keep && (qseg == kseg[kc]);
+              if (keep) tmax = fmaxf(tmax, __uint_as_float(r[e]));
             }
-            const float p0 = fast_exp2(s0 - m_sub), p1 = fast_exp2(s1 - m_sub);
-            l += p0 + p1;
-            pk[cc * 16 + e / 2] = pack_bf16(p0, p1);
+          } else {
+  #pragma unroll
+            for (int e = 0; e < 32; ++e) tmax = fmaxf(tmax, __uint_as_float(r[e]));
           }
         }
-        tmem_st32(tS + half * 32, pk);
+        const float m_new = fmaxf(m, tmax);
+        float factor = 1.f;
+        if (m == -CUDART_INF_F) {
+          m = m_new;  // nothing accumulated for this row yet (l = 0, accumulator row is 0)
+        } else if (m_new - m > kRescaleThreshold) {
+          factor = fast_exp2(m - m_new);
+          m = m_new;
+        }
+        if (__any_sync(0xffffffffu, factor != 1.f) && (j > 0 || loaded)) {
+          if (j > 0) {
+            wait(&bars->o_done[u], (j - 1) & 1, 0x200 + u);
+            tc_fence_after();
+          }
+  #pragma unroll
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld32(tO + c * 32, r);
+            tmem_ld_wait();
+  #pragma unroll
+            for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * factor);
+            tmem_st32(tO + c * 32, r);
+          }
+          tmem_st_wait();
+        }
+        l *= factor;
+        const float m_sub = (m == -CUDART_INF_F) ? 0.f : m;
+
+        // pass 2: p = 2^(s - m), row sum, bf16 P over the first 64 columns of S
+  #pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t pk[32];
+  #pragma unroll
+          for (int cc = 0; cc < 2; ++cc) {
+            const int c = half * 2 + cc;
+            uint32_t r[32];
+            tmem_ld32(tS + c * 32, r);
+            tmem_ld_wait();
+  #pragma unroll
+            for (int e = 0; e < 32; e += 2) {
+              float s0 = __uint_as_float(r[e]), s1 = __uint_as_float(r[e + 1]);
+              if (masked) {
+                const int kc = k0 + c * 32 + e;
+                bool keep0 = true, keep1 = true;
+                if (diag) {
+                  keep0 = qpos >= (int64_t)kc + p.k_offset;
+                  keep1 = qpos >= (int64_t)kc + 1 + p.k_offset;
+                }
+                if (has_seg) {
+                  keep0 = keep0 && (qseg == kseg[kc]);
+                  keep1 = keep1 && (qseg == kseg[kc + 1]);
+                }
+                if (!keep0) s0 = -CUDART_INF_F;
+                if (!keep1) s1 = -CUDART_INF_F;
+              }
+              const float p0 = fast_exp2(s0 - m_sub), p1 = fast_exp2(s1 - m_sub);
+              l += p0 + p1;
+              pk[cc * 16 + e / 2] = pack_bf16(p0, p1);
+            }
+          }
+          tmem_st32(tS + half * 32, pk);
+        }
       }
       tmem_st_wait();
       tc_fence_before();
