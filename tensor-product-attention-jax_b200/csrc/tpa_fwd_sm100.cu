@@ -67,6 +67,8 @@ struct Barriers {
   uint64_t s_full[2], p_ready[2], o_done[2];
   uint32_t tmem_base;
   volatile uint32_t abort;
+  // key segment ids of the tile in each V stage (filled and released together with it)
+  alignas(16) int32_t kseg[2][kTileKv];
 };
 
 struct Waiter {
@@ -233,7 +235,8 @@ __global__ void __launch_bounds__(256) tpa_stage_tiles_kernel(const Params p, ui
 
 template <int D, bool STAGED>
 __global__ void __launch_bounds__(Roles<STAGED>::kThreads, 1)
-tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, const uint8_t* ws_v) {
+tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, const uint8_t* ws_v,
+                     const bool head_major) {
   constexpr int kMmaWarp = Roles<STAGED>::kMmaWarp;
   constexpr int kTileBytes = kUnitRows * D * 2;  // one Q unit, one K stage or one V stage
   constexpr uint32_t kIdescS = make_idesc(128, kTileKv, false, false);
@@ -249,8 +252,11 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
   Barriers* bars = reinterpret_cast<Barriers*>(smem + 6 * kTileBytes);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int head = blockIdx.x;
-  const int pair = gridDim.y - 1 - blockIdx.y;  // longest causal rows first
+  // Launch order (x fastest) decides what shares L2 (see launch_sm100): head-major runs the
+  // CTAs of one head together, row-major runs the heads of one row block together.  Either
+  // way the longest causal rows go first.
+  const int head = head_major ? blockIdx.y : blockIdx.x;
+  const int pair = head_major ? gridDim.x - 1 - blockIdx.x : gridDim.y - 1 - blockIdx.y;
   const int batch = blockIdx.z;
   const int q0 = pair * 2 * kUnitRows;
   const bool causal = (p.flags & TPA_FLAG_CAUSAL) != 0;
@@ -320,7 +326,6 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
     const int64_t rh = live ? ((int64_t)batch * p.lq + grow) * p.heads + head : 0;
     const int64_t qpos = (int64_t)grow + p.q_offset;
     const int qseg = (has_seg && live) ? p.q_seg[(int64_t)batch * p.q_seg_bstride + grow] : 0;
-    const int32_t* kseg = has_seg ? p.kv_seg + (int64_t)batch * p.kv_seg_bstride : nullptr;
     const float rk = (float)p.rank_k;
 
     float m = -CUDART_INF_F, l = 0.f;
@@ -357,7 +362,18 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
       tc_fence_after();
       const int k0 = j * kTileKv;
       const bool diag = causal && ((int64_t)k0 + kTileKv - 1 + p.k_offset > (int64_t)q0u + p.q_offset);
-      const bool masked = diag || has_seg;
+      // Segment ids: when every key of the tile and every row of this warp carry the same
+      // id, nothing is masked and the element-wise test is skipped (warp-uniform decision).
+      const int32_t* ks = bars->kseg[j & 1];
+      bool seg_mask = false;
+      if (has_seg) {
+        wait(&bars->v_full[j & 1], (j >> 1) & 1, 0x700 + u);
+        const int4 k4 = *reinterpret_cast<const int4*>(ks + lane * 4);
+        const int kmin = __reduce_min_sync(0xffffffffu, min(min(k4.x, k4.y), min(k4.z, k4.w)));
+        const int kmax = __reduce_max_sync(0xffffffffu, max(max(k4.x, k4.y), max(k4.z, k4.w)));
+        seg_mask = !__all_sync(0xffffffffu, kmin == kmax && qseg == kmin);
+      }
+      const bool masked = diag || seg_mask;
 
       if constexpr (STAGED) {
         // Pass 1: all four 32-column chunks are fetched at once for the row maximum.  Pass 2
@@ -369,7 +385,7 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
             const int kc = k0 + c * 32 + e;
             bool keep = true;
             if (diag) keep = qpos >= (int64_t)kc + p.k_offset;
-            if (has_seg) keep = keep && (qseg == kseg[kc]);
+            if (seg_mask) keep = keep && (qseg == ks[c * 32 + e]);
             if (!keep) r[e] = 0xff800000u;  // -inf
           }
         };
@@ -471,7 +487,7 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
               const int kc = k0 + c * 32 + e;
               bool keep = true;
               if (diag) keep = qpos >= (int64_t)kc + p.k_offset;
-              if (has_seg) keep = keep && (qseg == kseg[kc]);
+              if (seg_mask) keep = keep && (qseg == ks[c * 32 + e]);
               if (keep) tmax = fmaxf(tmax, __uint_as_float(r[e]));
             }
           } else {
@@ -526,9 +542,9 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
                   keep0 = qpos >= (int64_t)kc + p.k_offset;
                   keep1 = qpos >= (int64_t)kc + 1 + p.k_offset;
                 }
-                if (has_seg) {
-                  keep0 = keep0 && (qseg == kseg[kc]);
-                  keep1 = keep1 && (qseg == kseg[kc + 1]);
+                if (seg_mask) {
+                  keep0 = keep0 && (qseg == ks[c * 32 + e]);
+                  keep1 = keep1 && (qseg == ks[c * 32 + e + 1]);
                 }
                 if (!keep0) s0 = -CUDART_INF_F;
                 if (!keep1) s1 = -CUDART_INF_F;
@@ -620,8 +636,11 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
         mbar_arrive_expect_tx(&bars->k_full[s], kTileBytes);
         bulk_g2s(sK + s * kTileBytes, gk + (int64_t)j * kTileBytes, kTileBytes, &bars->k_full[s]);
         if (j >= 2) wait(&bars->v_empty[s], ((j >> 1) - 1) & 1, 0x500);
-        mbar_arrive_expect_tx(&bars->v_full[s], kTileBytes);
+        mbar_arrive_expect_tx(&bars->v_full[s], kTileBytes + (has_seg ? kTileKv * 4 : 0));
         bulk_g2s(sV + s * kTileBytes, gv + (int64_t)j * kTileBytes, kTileBytes, &bars->v_full[s]);
+        if (has_seg)
+          bulk_g2s(bars->kseg[s], p.kv_seg + (int64_t)batch * p.kv_seg_bstride + (int64_t)j * kTileKv,
+                   kTileKv * 4, &bars->v_full[s]);
       }
     }
     __syncwarp();
@@ -651,6 +670,8 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
       if (j >= 2) wait(&empty[s], ((j >> 1) - 1) & 1, is_k ? 0x400 : 0x500);
       rebuild_tile<D>(stages + s * kTileBytes, fa, sa.stride[1], sa.stride[2], fb, sb.stride[1],
                       sb.stride[2], p.rank_k, (int64_t)j * kTileKv, 1.f, t, kRebuildWarps * 16);
+      if (!is_k && has_seg)
+        bars->kseg[s][t] = p.kv_seg[(int64_t)batch * p.kv_seg_bstride + (int64_t)j * kTileKv + t];
       fence_async_smem();
       mbar_arrive(&full[s]);
     }
@@ -732,11 +753,11 @@ inline size_t staged_kv_bytes(const Params& p) { return align256((size_t)p.batch
 
 template <int D, bool STAGED>
 cudaError_t launch_attn(const Params& p, const uint8_t* wq, const uint8_t* wk, const uint8_t* wv,
-                        dim3 grid, size_t smem, cudaStream_t stream) {
+                        dim3 grid, bool head_major, size_t smem, cudaStream_t stream) {
   auto kern = tpa_fwd_sm100_kernel<D, STAGED>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
-  kern<<<grid, Roles<STAGED>::kThreads, smem, stream>>>(p, wq, wk, wv);
+  kern<<<grid, Roles<STAGED>::kThreads, smem, stream>>>(p, wq, wk, wv, head_major);
   return cudaGetLastError();
 }
 
@@ -752,6 +773,8 @@ bool sm100_supported(const Params& p) {
   if (!factor_vec_ok(p.qb) || !factor_vec_ok(p.kb) || !factor_vec_ok(p.vb)) return false;
   if (!(p.flags & TPA_FLAG_STATE_STORE) && !aligned16(p.o)) return false;
   if ((p.flags & (TPA_FLAG_STATE_STORE | TPA_FLAG_STATE_LOAD)) && !aligned16(p.state_o)) return false;
+  // key segment ids travel to shared memory as 512-byte bulk copies
+  if (p.kv_seg != nullptr && (!aligned16(p.kv_seg) || p.kv_seg_bstride % 4 != 0)) return false;
   return true;
 }
 
@@ -769,7 +792,12 @@ cudaError_t launch_sm100(const Params& p, int variant, void* workspace, TpaKerne
                          bool dry_run, cudaStream_t stream) {
   const bool staged = variant == TPA_KERNEL_SM100_STAGED;
   const size_t smem = p.dk == 128 ? smem_bytes<128>() : smem_bytes<64>();
-  dim3 grid(p.heads, (p.lq + 2 * kUnitRows - 1) / (2 * kUnitRows), p.batch);
+  const int pairs = (p.lq + 2 * kUnitRows - 1) / (2 * kUnitRows);
+  // Row-major order (all heads of the longest rows first) balances best, but its concurrent
+  // CTAs touch the staged K/V of every head; once that exceeds what L2 holds, run one head's
+  // CTAs together instead so they share the tiles they stream.
+  const bool head_major = staged && (size_t)p.heads * p.lk * p.dk * 4 > (size_t)96 << 20;
+  dim3 grid = head_major ? dim3(pairs, p.heads, p.batch) : dim3(p.heads, pairs, p.batch);
   if (info) {
     info->kernel = variant;
     info->block_q = 2 * kUnitRows;
@@ -795,11 +823,11 @@ cudaError_t launch_sm100(const Params& p, int variant, void* workspace, TpaKerne
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     count_launch(1);
-    e = p.dk == 128 ? launch_attn<128, true>(p, wq, wk, wv, grid, smem, stream)
-                    : launch_attn<64, true>(p, wq, wk, wv, grid, smem, stream);
+    e = p.dk == 128 ? launch_attn<128, true>(p, wq, wk, wv, grid, head_major, smem, stream)
+                    : launch_attn<64, true>(p, wq, wk, wv, grid, head_major, smem, stream);
   } else {
-    e = p.dk == 128 ? launch_attn<128, false>(p, wq, wk, wv, grid, smem, stream)
-                    : launch_attn<64, false>(p, wq, wk, wv, grid, smem, stream);
+    e = p.dk == 128 ? launch_attn<128, false>(p, wq, wk, wv, grid, head_major, smem, stream)
+                    : launch_attn<64, false>(p, wq, wk, wv, grid, head_major, smem, stream);
   }
   if (e == cudaSuccess) count_launch(1);
   return e;

@@ -1,0 +1,75 @@
+"""Ring TPA on real GPUs (needs >= 2 devices; skipped otherwise): one process per GPU over NCCL,
+every rank's output against the ring oracle (shard-local causal mask, as the reference computes
+it) and against the unsharded forward for the global mask."""
+
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from conftest import ROOT
+
+pytestmark = pytest.mark.gpu
+
+WORKER = r"""
+import os, sys
+import numpy as np, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["TPA_ROOT"]); sys.path.insert(0, os.path.join(os.environ["TPA_ROOT"], "tensor-product-attention-jax_b200"))
+import tpa_b200
+from oracle import tpa_oracle as orc
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ["LOCAL_RANK"])))
+fails = []
+for (dtype, b, l, h, d, rq, rk, seg, mode, causal) in [
+    ("f32", 2, 256 * world, 4, 32, 3, 2, 100, "reference_local", True),
+    ("f32", 1, 256 * world, 4, 32, 3, 2, 0, "global", True),
+    ("bf16", 1, 1024 * world, 8, 128, 6, 2, 0, "reference_local", True),
+    ("bf16", 1, 1024 * world, 8, 128, 6, 2, 0, "global", True),
+    ("bf16", 1, 512 * world, 8, 64, 4, 4, 300, "reference_local", False),
+]:
+    q, k, v = orc.make_factors(77, b, l, l, rq, rk, h, d, d)
+    ids = orc.segment_ids(b, l, seg) if seg else np.zeros((b, l), np.int32)
+    td = torch.float32 if dtype == "f32" else torch.bfloat16
+    tq, tk, tv = (torch.from_numpy(x).cuda().to(td) for x in (q, k, v))
+    tid = torch.from_numpy(ids).cuda()
+    o = tpa_b200.ring_tpa.ring_tp_self_attention(tq, tk, tv, tid, tid, mesh=None, pspec=(None, "sp", None, None),
+                                                 num_heads=h, sm_scale=d ** -0.5, causal=causal, mask_mode=mode,
+                                                 gather_output=True)
+    st, detail = tpa_b200.tpa.device_status()
+    ref = orc.ring_tpa_reference(tq.float().cpu().numpy(), tk.float().cpu().numpy(), tv.float().cpu().numpy(),
+                                 ids, ids, h, world, sm_scale=d ** -0.5, causal=causal, mask_mode=mode)
+    diff = np.abs(o.float().cpu().numpy() - ref)
+    ok = (diff.max() <= 1e-5) if dtype == "f32" else (diff.max() <= 2e-2 and diff.mean() <= 5e-3)
+    ok = ok and st == 0 and np.array_equal(np.isnan(o.float().cpu().numpy()), np.isnan(ref))
+    if rank == 0:
+        print(f"ring {dtype} l={l} d={d} {mode} causal={causal}: max {np.nanmax(diff):.2e} mean {np.nanmean(diff):.2e} status {st} {'OK' if ok else 'FAIL'}", flush=True)
+    if not ok:
+        fails.append((dtype, l, mode))
+dist.barrier()
+dist.destroy_process_group()
+sys.exit(1 if fails else 0)
+"""
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
+def test_ring_nccl_all_gpus(tmp_path):
+    n = min(torch.cuda.device_count(), 8)
+    script = tmp_path / "ring_worker.py"
+    script.write_text(WORKER)
+    env = dict(os.environ, TPA_ROOT=ROOT, NCCL_NVLS_ENABLE="0")
+    res = subprocess.run(
+        [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
+         "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), str(script)],
+        env=env, capture_output=True, text=True, timeout=600)
+    print(res.stdout[-3000:], res.stderr[-3000:])
+    assert res.returncode == 0
