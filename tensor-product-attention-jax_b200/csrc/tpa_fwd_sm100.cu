@@ -37,6 +37,8 @@
 // and the CTA runs to its normal end (TMEM is freed).
 #include <math_constants.h>
 
+#include <type_traits>
+
 #include "sm100_ptx.cuh"
 #include "tpa_common.cuh"
 
@@ -51,14 +53,25 @@ template <bool STAGED>
 struct Roles {
   static constexpr int kProducerWarps = STAGED ? 1 : kRebuildWarps;
   static constexpr int kMmaWarp = kSoftmaxWarps + kProducerWarps;
-  static constexpr int kThreads = (kMmaWarp + 1) * 32;  // 320 staged, 544 fused
+  // STAGED: 12 warps = 3 warpgroups (producer, MMA and two idle warps form the third), so
+  // that registers can be moved from the third warpgroup to the softmax ones.  FUSED: 17.
+  static constexpr int kThreads = STAGED ? 384 : (kMmaWarp + 1) * 32;
 };
+constexpr int kSoftmaxRegs = 224, kOtherRegs = 56;  // 8*32*224 + 4*32*56 = 64512 <= 65536
 constexpr int kUnitRows = 128;
 constexpr int kTileKv = 128;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 constexpr long long kWaitCycles = 1ll << 28;
+// polynomial 2^x: which of every 8 column pairs leave the MUFU pipe (bit i = pair i mod 8)
+#ifndef TPA_POLY_PAIRS
+#define TPA_POLY_PAIRS 0x00
+#endif
+constexpr uint32_t kPolyPairs = TPA_POLY_PAIRS;
+constexpr float kExpMagic = 12582912.f;  // 1.5 * 2^23: adding it rounds to the nearest integer
+constexpr float kExpC0 = 0.9999280571937561f, kExpC1 = 0.6932609677314758f,
+                kExpC2 = 0.2426111251115799f, kExpC3 = 0.0551716648042202f;
 
 struct Barriers {
   uint64_t q_full;
@@ -113,10 +126,19 @@ __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
   asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
   return r;
 }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
 __device__ __forceinline__ float fast_exp2(float x) {
+#if defined(TPA_EXPERIMENT) && TPA_EXPERIMENT == 1
+  return x;
+#else
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+#endif
 }
 
 // dst tile rows [0,128): dst[row][:] = scale * sum_r a[row0+row, r] * b[row0+row, r, :], bf16,
@@ -304,6 +326,12 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
   tc_fence_after();
   const uint32_t tmem = bars->tmem_base;
   const Waiter wait{bars, p.status};
+  if constexpr (STAGED) {
+    // whole-warpgroup register reallocation: the softmax threads keep 64 packed P words and
+    // two 32-column chunks of S live at once
+    if (warp < kSoftmaxWarps) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kSoftmaxRegs));
+    else asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kOtherRegs));
+  }
 
   const __nv_bfloat16* qa = static_cast<const __nv_bfloat16*>(p.qa.ptr) + batch * p.qa.stride[0] + head;
   const __nv_bfloat16* qb = static_cast<const __nv_bfloat16*>(p.qb.ptr) + batch * p.qb.stride[0];
@@ -375,10 +403,11 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
       }
       const bool masked = diag || seg_mask;
 
+#if defined(TPA_EXPERIMENT) && TPA_EXPERIMENT == 3
+      if (true) {
+      } else
+#endif
       if constexpr (STAGED) {
-        // Pass 1: all four 32-column chunks are fetched at once for the row maximum.  Pass 2
-        // re-reads them two at a time (TMEM reads are cheap; 128 live logits would spill),
-        // the second pair in flight while the first is exponentiated.  Packed fp32 sub / add.
         auto mask_chunk = [&](uint32_t(&r)[32], int c) {
 #pragma unroll
           for (int e = 0; e < 32; ++e) {
@@ -389,90 +418,170 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
             if (!keep) r[e] = 0xff800000u;  // -inf
           }
         };
-        float tmax;
-        {
-          uint32_t sc[4][32];
-#pragma unroll
-          for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, sc[c]);
-          tmem_ld_wait();
-          if (masked) {
-#pragma unroll
-            for (int c = 0; c < 4; ++c) mask_chunk(sc[c], c);
-          }
-          float cm[4];
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            cm[c] = fmaxf(__uint_as_float(sc[c][0]), __uint_as_float(sc[c][1]));
-#pragma unroll
-            for (int e = 2; e < 32; e += 2)
-              cm[c] = max3(cm[c], __uint_as_float(sc[c][e]), __uint_as_float(sc[c][e + 1]));
-          }
-          tmax = fmaxf(fmaxf(cm[0], cm[1]), fmaxf(cm[2], cm[3]));
-        }
-        uint32_t ra[32], rb[32];
-        tmem_ld32(tS, ra);
-        tmem_ld32(tS + 32, rb);
-        const float m_new = fmaxf(m, tmax);
-        float factor = 1.f;
-        if (m == -CUDART_INF_F) {
-          m = m_new;  // nothing accumulated for this row yet (l = 0, accumulator row is 0)
-        } else if (m_new - m > kRescaleThreshold) {
-          factor = fast_exp2(m - m_new);
-          m = m_new;
-        }
-        if (__any_sync(0xffffffffu, factor != 1.f) && (j > 0 || loaded)) {
-          if (j > 0) {
-            wait(&bars->o_done[u], (j - 1) & 1, 0x200 + u);
-            tc_fence_after();
-          }
-#pragma unroll
-          for (int c = 0; c < D / 32; ++c) {
-            uint32_t r[32];
-            tmem_ld32(tO + c * 32, r);
-            tmem_ld_wait();
-#pragma unroll
-            for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * factor);
-            tmem_st32(tO + c * 32, r);
-          }
-          tmem_st_wait();
-        }
-        l *= factor;
-        const float neg_m = (m == -CUDART_INF_F) ? 0.f : -m;
-        const uint64_t neg_m2 = pack2(neg_m, neg_m);
-        uint64_t lsum[4] = {0ull, 0ull, 0ull, 0ull};
-        auto exp_chunk = [&](const uint32_t(&r)[32], uint32_t* pk) {
+        // p = 2^(s - reference maximum) for one 32-column chunk, packed to bf16, with the
+        // row sum (four packed partial sums) and, optionally, the running maximum of s.
+        // On unmasked tiles the pairs selected by kPolyPairs are evaluated on the FMA pipe
+        // (round-to-nearest split x = n + f, degree-3 minimax polynomial for 2^f on
+        // [-1/2, 1/2], relative error 7.5e-5, n added to the exponent field) to take load
+        // off the MUFU pipe.  Masked tiles need exact zeros for -inf and use ex2 throughout.
+        uint64_t neg_m2 = 0, lsum[4];
+        float x_floor = 0.f, cmx[2];
+        auto set_reference = [&](float mm) {
+          const float neg_m = (mm == -CUDART_INF_F) ? 0.f : -mm;
+          neg_m2 = pack2(neg_m, neg_m);
+          x_floor = -126.f - neg_m;
+          lsum[0] = lsum[1] = lsum[2] = lsum[3] = 0ull;
+          cmx[0] = cmx[1] = -CUDART_INF_F;
+        };
+        auto exp_chunk = [&](const uint32_t(&r)[32], uint32_t* pk, auto poly_tag, auto track_tag) {
+          constexpr bool kPoly = decltype(poly_tag)::value;
+          constexpr bool kTrack = decltype(track_tag)::value;
 #pragma unroll
           for (int e = 0; e < 32; e += 2) {
-            float x0, x1;
-            unpack2(add2(pack2(__uint_as_float(r[e]), __uint_as_float(r[e + 1])), neg_m2), x0, x1);
-            const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+            const float s0 = __uint_as_float(r[e]), s1 = __uint_as_float(r[e + 1]);
+            if (kTrack) cmx[(e >> 1) & 1] = max3(cmx[(e >> 1) & 1], s0, s1);
+            float p0, p1;
+            if (kPoly && ((kPolyPairs >> ((e >> 1) & 7)) & 1)) {
+              const uint64_t x = add2(pack2(fmaxf(s0, x_floor), fmaxf(s1, x_floor)), neg_m2);
+              const uint64_t t = add2(x, pack2(kExpMagic, kExpMagic));
+              const uint64_t n = add2(t, pack2(-kExpMagic, -kExpMagic));
+              const uint64_t f = fma2(n, pack2(-1.f, -1.f), x);
+              uint64_t q = fma2(f, pack2(kExpC3, kExpC3), pack2(kExpC2, kExpC2));
+              q = fma2(q, f, pack2(kExpC1, kExpC1));
+              q = fma2(q, f, pack2(kExpC0, kExpC0));
+              float t0, t1, q0, q1;
+              unpack2(t, t0, t1);
+              unpack2(q, q0, q1);
+              p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(t0) << 23));
+              p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(t1) << 23));
+            } else {
+              float x0, x1;
+              unpack2(add2(pack2(s0, s1), neg_m2), x0, x1);
+              p0 = fast_exp2(x0);
+              p1 = fast_exp2(x1);
+            }
             lsum[(e >> 1) & 3] = add2(lsum[(e >> 1) & 3], pack2(p0, p1));
             pk[e / 2] = pack_bf16(p0, p1);
           }
         };
-        uint32_t pk[32];
-        tmem_ld_wait();
-        if (masked) {
-          mask_chunk(ra, 0);
-          mask_chunk(rb, 1);
+        auto row_sum = [&]() {
+          float a0, a1, a2, a3;
+          unpack2(add2(lsum[0], lsum[1]), a0, a1);
+          unpack2(add2(lsum[2], lsum[3]), a2, a3);
+          return (a0 + a1) + (a2 + a3);
+        };
+
+        // Optimistic single pass: exponentiate against the maximum carried from earlier
+        // tiles while tracking this tile's maximum; P stays in registers until the check.
+        // If some row of the warp grew by more than the threshold (or has no maximum yet),
+        // nothing has been stored and the exact two-pass path below runs instead.
+        bool done = false;
+        if (__all_sync(0xffffffffu, m != -CUDART_INF_F)) {
+          set_reference(m);
+          uint32_t ra[32], rb[32], pk[64];
+          tmem_ld32(tS, ra);
+          tmem_ld32(tS + 32, rb);
+          tmem_ld_wait();
+          auto single = [&](auto poly_tag) {
+            if (masked) {
+              mask_chunk(ra, 0);
+              mask_chunk(rb, 1);
+            }
+            exp_chunk(ra, pk, poly_tag, std::true_type{});
+            tmem_ld32(tS + 64, ra);
+            exp_chunk(rb, pk + 16, poly_tag, std::true_type{});
+            tmem_ld32(tS + 96, rb);
+            tmem_ld_wait();
+            if (masked) {
+              mask_chunk(ra, 2);
+              mask_chunk(rb, 3);
+            }
+            exp_chunk(ra, pk + 32, poly_tag, std::true_type{});
+            exp_chunk(rb, pk + 48, poly_tag, std::true_type{});
+          };
+          if (masked) single(std::false_type{});
+          else single(std::true_type{});
+          const float tmax = fmaxf(cmx[0], cmx[1]);
+          if (!__any_sync(0xffffffffu, tmax - m > kRescaleThreshold)) {
+            tmem_st32(tS, *reinterpret_cast<uint32_t(*)[32]>(pk));
+            tmem_st32(tS + 32, *reinterpret_cast<uint32_t(*)[32]>(pk + 32));
+            l += row_sum();
+            done = true;
+          }
         }
-        exp_chunk(ra, pk);
-        tmem_ld32(tS + 64, ra);
-        exp_chunk(rb, pk + 16);
-        tmem_ld32(tS + 96, rb);
-        tmem_ld_wait();  // P below overwrites columns [0,32): both re-reads must have landed
-        tmem_st32(tS, pk);
-        if (masked) {
-          mask_chunk(ra, 2);
-          mask_chunk(rb, 3);
+        if (!done) {
+          // Exact path.  Pass 1: all four chunks at once for the row maximum.  Pass 2 re-reads
+          // them two at a time, the second pair in flight while the first is exponentiated.
+          float tmax;
+          {
+            uint32_t sc[4][32];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, sc[c]);
+            tmem_ld_wait();
+            if (masked) {
+#pragma unroll
+              for (int c = 0; c < 4; ++c) mask_chunk(sc[c], c);
+            }
+            float cm[4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              cm[c] = fmaxf(__uint_as_float(sc[c][0]), __uint_as_float(sc[c][1]));
+#pragma unroll
+              for (int e = 2; e < 32; e += 2)
+                cm[c] = max3(cm[c], __uint_as_float(sc[c][e]), __uint_as_float(sc[c][e + 1]));
+            }
+            tmax = fmaxf(fmaxf(cm[0], cm[1]), fmaxf(cm[2], cm[3]));
+          }
+          uint32_t ra[32], rb[32];
+          tmem_ld32(tS, ra);
+          tmem_ld32(tS + 32, rb);
+          const float m_new = fmaxf(m, tmax);
+          float factor = 1.f;
+          if (m == -CUDART_INF_F) {
+            m = m_new;  // nothing accumulated for this row yet (l = 0, accumulator row is 0)
+          } else if (m_new - m > kRescaleThreshold) {
+            factor = fast_exp2(m - m_new);
+            m = m_new;
+          }
+          if (__any_sync(0xffffffffu, factor != 1.f) && (j > 0 || loaded)) {
+            if (j > 0) {
+              wait(&bars->o_done[u], (j - 1) & 1, 0x200 + u);
+              tc_fence_after();
+            }
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+              uint32_t r[32];
+              tmem_ld32(tO + c * 32, r);
+              tmem_ld_wait();
+#pragma unroll
+              for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * factor);
+              tmem_st32(tO + c * 32, r);
+            }
+            tmem_st_wait();
+          }
+          l *= factor;
+          set_reference(m);
+          uint32_t pk[32];
+          tmem_ld_wait();
+          if (masked) {
+            mask_chunk(ra, 0);
+            mask_chunk(rb, 1);
+          }
+          exp_chunk(ra, pk, std::false_type{}, std::false_type{});
+          tmem_ld32(tS + 64, ra);
+          exp_chunk(rb, pk + 16, std::false_type{}, std::false_type{});
+          tmem_ld32(tS + 96, rb);
+          tmem_ld_wait();  // P below overwrites columns [0,32): both re-reads must have landed
+          tmem_st32(tS, pk);
+          if (masked) {
+            mask_chunk(ra, 2);
+            mask_chunk(rb, 3);
+          }
+          exp_chunk(ra, pk, std::false_type{}, std::false_type{});
+          exp_chunk(rb, pk + 16, std::false_type{}, std::false_type{});
+          tmem_st32(tS + 32, pk);
+          l += row_sum();
         }
-        exp_chunk(ra, pk);
-        exp_chunk(rb, pk + 16);
-        tmem_st32(tS + 32, pk);
-        float a0, a1, a2, a3;
-        unpack2(add2(lsum[0], lsum[1]), a0, a1);
-        unpack2(add2(lsum[2], lsum[3]), a2, a3);
-        l += (a0 + a1) + (a2 + a3);
       } else {
         // pass 1: row maximum of the (masked) logits; they are already in log2 units
         float tmax = -CUDART_INF_F;
@@ -678,7 +787,7 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
    }
   } else {
     // ------------------------------------------------------------------ MMA issue (one thread)
-    if (lane == 0 && n_tiles > 0) {
+    if (warp == kMmaWarp && lane == 0 && n_tiles > 0) {
       const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), aV = smem_u32(sV);
       auto issue_s = [&](int u, int j) {
         const uint32_t qbase = aQ + u * kTileBytes, kbase = aK + (j & 1) * kTileBytes;

@@ -10,7 +10,8 @@ import ctypes as C
 import os
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "libtpa_b200.so")
+# TPA_B200_LIB points at another build of the same library (tuning builds); default: in-tree.
+LIB_PATH = os.environ.get("TPA_B200_LIB") or os.path.join(_PKG, "libtpa_b200.so")
 
 TPA_OK = 0
 TPA_ERR_BAD_ARG = -1

@@ -39,7 +39,8 @@ def build(force=False, verbose=False):
     if not force and not needs_build():
         return LIB
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
-    cmd = [nvcc, *NVCC_FLAGS, "-I", INCLUDE, "-I", CSRC, "-o", LIB, *sources()]
+    extra = os.environ.get("TPA_NVCC_EXTRA", "").split()  # e.g. -DTPA_POLY_PAIRS=0x88 for tuning builds
+    cmd = [nvcc, *NVCC_FLAGS, *extra, "-I", INCLUDE, "-I", CSRC, "-o", LIB, *sources()]
     res = subprocess.run(cmd, capture_output=True, text=True)
     log = res.stdout + res.stderr
     with open(os.path.join(PKG, "build.log"), "w") as f:
