@@ -94,10 +94,19 @@ class ClockSampler:
                 self.proc.kill()
             self.thread.join(timeout=2)
 
-    def summary(self):
+    def wait_first(self, timeout=5.0):
+        """Block until nvidia-smi has delivered its first sample (it takes a moment to start)."""
+        t0 = time.perf_counter()
+        while not self.rows and time.perf_counter() - t0 < timeout and self.proc is not None:
+            time.sleep(0.02)
+
+    def mark(self):
+        return len(self.rows)
+
+    def summary(self, start=0, end=None):
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
+        for r in self.rows[start:end]:
             try:
                 sm.append(float(r[0]))
                 mx.append(float(r[1]))
@@ -183,7 +192,7 @@ def reference_arm(args, name):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
@@ -235,19 +244,34 @@ def main():
             dist.barrier()
             torch.cuda.synchronize(device)
 
-    for _ in range(args.warmup):
-        step()
-    sync()
-    n0 = _capi.lib.tpa_launch_count()
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
     with ClockSampler(local_rank) as clocks:
+        clocks.wait_first()
+        # the sampler ticks every 100 ms: keep the GPU under this load for at least 0.5 s before
+        # the timed steps so that the clocks reported are the ones the kernel runs at
+        c_start = clocks.mark()
         sync()
+        t0 = time.perf_counter()
+        step()
+        sync()
+        t1 = torch.tensor([time.perf_counter() - t0], device=device)
+        if ring:
+            dist.all_reduce(t1, op=dist.ReduceOp.MAX)  # every rank must run the same number of steps
+        n_warm = max(args.warmup - 1, min(200, int(0.5 / max(float(t1.item()), 1e-4)) + 1))
+        for i in range(n_warm):
+            step()
+            if i % 4 == 3:
+                torch.cuda.synchronize(device)
+        sync()
+        n0 = _capi.lib.tpa_launch_count()
         ev[0].record()
         for i in range(args.steps):
             step()
             ev[i + 1].record()
         sync()
-    launches = _capi.lib.tpa_launch_count() - n0
+        launches = _capi.lib.tpa_launch_count() - n0
+        time.sleep(0.12)  # let the sample that covers the end of the timed region arrive
+        clock_summary = clocks.summary(c_start)
     total_ms = ev[0].elapsed_time(ev[-1])
     per_step = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
     if ring:
@@ -325,7 +349,7 @@ def main():
                    "parallelism": f"ring sp{world} ({args.mask_mode} causal mask)" if ring else "single GPU",
                    "l2": "inputs + outputs larger than L2 (no flush needed)" if name in ("c1", "c2", "c3") else "smaller than L2, not flushed",
                    "kernel": info},
-        "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks.summary(),
+        "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clock_summary,
     }
     print(json.dumps(line), flush=True)
     if ring:
