@@ -33,7 +33,9 @@ enum {
   TPA_ERR_WORKSPACE = -3,    /* workspace missing or smaller than tpa_fwd_workspace_bytes()    */
   TPA_ERR_CUDA = -4,         /* a CUDA runtime call failed (see tpa_last_cuda_error)           */
   TPA_ERR_KERNEL_FORCED = -5,/* args->kernel forces a kernel that cannot run this shape        */
-  TPA_ERR_DEVICE_TIMEOUT = -6/* a bounded device-side wait ran out (read via tpa_read_status)  */
+  TPA_ERR_DEVICE_TIMEOUT = -6,/* a bounded device-side wait ran out (read via tpa_read_status) */
+  TPA_ERR_STATIC_SCRATCH = -7 /* tpa_fwd_static_scratch: the problem needs more scratch than
+                                 TPA_STATIC_SCRATCH_BYTES                                       */
 };
 
 enum { TPA_DTYPE_F32 = 0, TPA_DTYPE_BF16 = 1 };
@@ -111,7 +113,20 @@ typedef struct TpaKernelInfo {
  * (see tpa_read_status). */
 int tpa_fwd(const TpaFwdArgs* args, void* workspace, size_t workspace_bytes, void* stream);
 
-/* Bytes of scratch the call above needs for these arguments (0 is possible). */
+/* Same forward pass for callers that cannot allocate the workspace: an XLA custom-call
+ * handler (device memory is owned, and mostly pre-reserved, by XLA's allocator) or an embedder
+ * with a fixed device-memory budget.  No counterpart in the reference.  Runs the STAGED
+ * tensor-core variant (bf16, head_dim 64/128, lengths % 128 == 0; other shapes return
+ * TPA_ERR_KERNEL_FORCED) with its scratch in a static device array inside the library:
+ * 256 + (lq + 2*lk) * batch * heads * dk * 2 bytes must fit TPA_STATIC_SCRATCH_BYTES, else
+ * TPA_ERR_STATIC_SCRATCH and nothing is launched.  Allocates nothing.  The first call on each
+ * device (with that device current) looks the array's address up once: make it at start-up,
+ * before any stream capture begins.  Calls on one GPU share the array: do not let two of
+ * them overlap.  Every GPU that loads the library holds TPA_STATIC_SCRATCH_BYTES until exit. */
+#define TPA_STATIC_SCRATCH_BYTES (64u << 20)
+int tpa_fwd_static_scratch(const TpaFwdArgs* args, void* stream);
+
+/* Bytes of scratch tpa_fwd needs for these arguments (0 is possible). */
 size_t tpa_fwd_workspace_bytes(const TpaFwdArgs* args);
 
 /* Which kernel, tiles and grid tpa_fwd would use; TPA_OK or the error tpa_fwd would return. */

@@ -90,6 +90,7 @@ const char* tpa_status_string(int status) {
     case TPA_ERR_CUDA: return "CUDA runtime error (see tpa_last_cuda_error)";
     case TPA_ERR_KERNEL_FORCED: return "the forced kernel cannot run this shape";
     case TPA_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait ran out";
+    case TPA_ERR_STATIC_SCRATCH: return "the problem needs more scratch than the library's static buffer (TPA_STATIC_SCRATCH_BYTES) holds; use tpa_fwd with a caller workspace";
     default: return "unknown status";
   }
 }

@@ -20,6 +20,8 @@ TPA_ERR_WORKSPACE = -3
 TPA_ERR_CUDA = -4
 TPA_ERR_KERNEL_FORCED = -5
 TPA_ERR_DEVICE_TIMEOUT = -6
+TPA_ERR_STATIC_SCRATCH = -7
+STATIC_SCRATCH_BYTES = 64 << 20
 
 DTYPE_F32, DTYPE_BF16 = 0, 1
 KERNEL_AUTO, KERNEL_SIMT, KERNEL_SM100, KERNEL_SM100_FUSED, KERNEL_SM100_STAGED = 0, 1, 2, 3, 4
@@ -31,6 +33,7 @@ FLAG_CAUSAL, FLAG_STATE_LOAD, FLAG_STATE_STORE = 1, 2, 4
 # Every symbol include/tpa_b200.h declares.
 EXPORTS = (
     "tpa_fwd",
+    "tpa_fwd_static_scratch",
     "tpa_fwd_workspace_bytes",
     "tpa_query_kernel",
     "tpa_read_status",
@@ -103,6 +106,8 @@ def _load():
         getattr(lib, name)  # AttributeError if the library does not export it
     lib.tpa_fwd.argtypes = [C.POINTER(TpaFwdArgs), C.c_void_p, C.c_size_t, C.c_void_p]
     lib.tpa_fwd.restype = C.c_int
+    lib.tpa_fwd_static_scratch.argtypes = [C.POINTER(TpaFwdArgs), C.c_void_p]
+    lib.tpa_fwd_static_scratch.restype = C.c_int
     lib.tpa_fwd_workspace_bytes.argtypes = [C.POINTER(TpaFwdArgs)]
     lib.tpa_fwd_workspace_bytes.restype = C.c_size_t
     lib.tpa_query_kernel.argtypes = [C.POINTER(TpaFwdArgs), C.POINTER(TpaKernelInfo)]

@@ -63,7 +63,7 @@ def test_query_kernel_and_validation_without_gpu():
     for a, want in bad:
         assert _capi.lib.tpa_query_kernel(C.byref(a), C.byref(info)) == want
         assert _capi.lib.tpa_fwd(C.byref(a), None, 0, None) == want  # returns before any CUDA call
-    for st in range(-6, 1):
+    for st in range(-7, 1):
         assert _capi.lib.tpa_status_string(st)
     with pytest.raises(ValueError):
         _capi.check(_capi.TPA_ERR_BAD_ARG)
