@@ -63,6 +63,7 @@ constexpr int kTileKv = 128;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
+constexpr float kOptimisticSumLimit = 32768.f;  // 2^15, see the softmax role
 constexpr long long kWaitCycles = 1ll << 28;
 // polynomial 2^x: which of every 8 column pairs leave the MUFU pipe (bit i = pair i mod 8)
 #ifndef TPA_POLY_PAIRS
@@ -426,9 +427,16 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
         // off the MUFU pipe.  Masked tiles need exact zeros for -inf and use ex2 throughout.
         uint64_t neg_m2 = 0, lsum[4];
         float x_floor = 0.f, cmx[2];
+#ifdef TPA_SCALAR_SOFTMAX
+        float neg_m_s = 0.f, fsum[8];
+#endif
         auto set_reference = [&](float mm) {
           const float neg_m = (mm == -CUDART_INF_F) ? 0.f : -mm;
           neg_m2 = pack2(neg_m, neg_m);
+#ifdef TPA_SCALAR_SOFTMAX
+          neg_m_s = neg_m;
+          for (int i = 0; i < 8; ++i) fsum[i] = 0.f;
+#endif
           x_floor = -126.f - neg_m;
           lsum[0] = lsum[1] = lsum[2] = lsum[3] = 0ull;
           cmx[0] = cmx[1] = -CUDART_INF_F;
@@ -455,16 +463,29 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
               p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(t0) << 23));
               p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(t1) << 23));
             } else {
+#ifdef TPA_SCALAR_SOFTMAX
+              p0 = fast_exp2(s0 + neg_m_s);
+              p1 = fast_exp2(s1 + neg_m_s);
+#else
               float x0, x1;
               unpack2(add2(pack2(s0, s1), neg_m2), x0, x1);
               p0 = fast_exp2(x0);
               p1 = fast_exp2(x1);
+#endif
             }
+#ifdef TPA_SCALAR_SOFTMAX
+            fsum[(e >> 1) & 3] += p0;
+            fsum[4 + ((e >> 1) & 3)] += p1;
+#else
             lsum[(e >> 1) & 3] = add2(lsum[(e >> 1) & 3], pack2(p0, p1));
+#endif
             pk[e / 2] = pack_bf16(p0, p1);
           }
         };
         auto row_sum = [&]() {
+#ifdef TPA_SCALAR_SOFTMAX
+          return ((fsum[0] + fsum[1]) + (fsum[2] + fsum[3])) + ((fsum[4] + fsum[5]) + (fsum[6] + fsum[7]));
+#endif
           float a0, a1, a2, a3;
           unpack2(add2(lsum[0], lsum[1]), a0, a1);
           unpack2(add2(lsum[2], lsum[3]), a2, a3);
@@ -472,9 +493,11 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
         };
 
         // Optimistic single pass: exponentiate against the maximum carried from earlier
-        // tiles while tracking this tile's maximum; P stays in registers until the check.
-        // If some row of the warp grew by more than the threshold (or has no maximum yet),
-        // nothing has been stored and the exact two-pass path below runs instead.
+        // tiles; P stays in registers until the row sums are known.  A row sum of at most
+        // 2^15 proves every p of the row is at most 2^15 (no overflow anywhere, bf16 keeps its
+        // relative precision), so the carried maximum can stay although it may be stale.
+        // Otherwise (or when a row has no maximum yet) nothing has been stored and the exact
+        // two-pass path below runs instead and raises the maximum.
         bool done = false;
         if (__all_sync(0xffffffffu, m != -CUDART_INF_F)) {
           set_reference(m);
@@ -487,25 +510,25 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
               mask_chunk(ra, 0);
               mask_chunk(rb, 1);
             }
-            exp_chunk(ra, pk, poly_tag, std::true_type{});
+            exp_chunk(ra, pk, poly_tag, std::false_type{});
             tmem_ld32(tS + 64, ra);
-            exp_chunk(rb, pk + 16, poly_tag, std::true_type{});
+            exp_chunk(rb, pk + 16, poly_tag, std::false_type{});
             tmem_ld32(tS + 96, rb);
             tmem_ld_wait();
             if (masked) {
               mask_chunk(ra, 2);
               mask_chunk(rb, 3);
             }
-            exp_chunk(ra, pk + 32, poly_tag, std::true_type{});
-            exp_chunk(rb, pk + 48, poly_tag, std::true_type{});
+            exp_chunk(ra, pk + 32, poly_tag, std::false_type{});
+            exp_chunk(rb, pk + 48, poly_tag, std::false_type{});
           };
           if (masked) single(std::false_type{});
           else single(std::true_type{});
-          const float tmax = fmaxf(cmx[0], cmx[1]);
-          if (!__any_sync(0xffffffffu, tmax - m > kRescaleThreshold)) {
+          const float tsum = row_sum();
+          if (!__any_sync(0xffffffffu, !(tsum <= kOptimisticSumLimit))) {  // also catches inf / NaN
             tmem_st32(tS, *reinterpret_cast<uint32_t(*)[32]>(pk));
             tmem_st32(tS + 32, *reinterpret_cast<uint32_t(*)[32]>(pk + 32));
-            l += row_sum();
+            l += tsum;
             done = true;
           }
         }
