@@ -831,35 +831,60 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
         }
         tc_commit(&bars->o_done[u]);
       };
-      const bool acc0 = load_state;
-
+      // Per unit the order is fixed: S(j), O += P V of tile j, S(j+1) (which overwrites P), ...
+      // Across the two units the thread issues whichever next operation has its operands
+      // ready (non-blocking barrier tests), so a unit whose softmax is late never holds back
+      // the other, and no wake-up latency of a blocking wait sits between softmax and MMA.
       wait(&bars->q_full, 0, 0x600);
-      wait(&bars->k_full[0], 0, 0x601);
       tc_fence_after();
-      for (int u = 0; u < 2; ++u)
-        if (n_vis[u] > 0) issue_s(u, 0);
-      tc_commit(&bars->k_empty[0]);
-      for (int j = 0; j < n_tiles; ++j) {
-        wait(&bars->v_full[j & 1], (j >> 1) & 1, 0x602);
-        tc_fence_after();
-        bool k_waited = false;
+      int s_next[2] = {0, 0}, pv_next[2] = {0, 0};  // next tile whose S / P V each unit issues
+      int k_users[2] = {0, 0}, v_users[2] = {0, 0};
+      long long t_idle = clock64();
+      while (pv_next[0] < n_vis[0] || pv_next[1] < n_vis[1]) {
+        bool progress = false;
+#pragma unroll
         for (int u = 0; u < 2; ++u) {
-          if (j < n_vis[u]) {
-            wait(&bars->p_ready[u], j & 1, 0x610 + u);
-            tc_fence_after();
-            issue_pv(u, j, acc0 || j > 0);
-          }
-          if (j + 1 < n_vis[u]) {
-            if (!k_waited) {
-              wait(&bars->k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, 0x603);
+          if (pv_next[u] < n_vis[u]) {
+            const int j = pv_next[u];
+            if (s_next[u] > j && mbar_test(&bars->p_ready[u], j & 1) &&
+                mbar_test(&bars->v_full[j & 1], (j >> 1) & 1)) {
               tc_fence_after();
-              k_waited = true;
+              issue_pv(u, j, load_state || j > 0);
+              ++pv_next[u];
+              if (++v_users[j & 1] == (j < n_vis[0]) + (j < n_vis[1])) {
+                tc_commit(&bars->v_empty[j & 1]);
+                v_users[j & 1] = 0;
+              }
+              progress = true;
             }
-            issue_s(u, j + 1);
+          }
+          if (s_next[u] < n_vis[u]) {
+            const int j = s_next[u];
+            if (pv_next[u] >= j && mbar_test(&bars->k_full[j & 1], (j >> 1) & 1)) {
+              tc_fence_after();
+              issue_s(u, j);
+              ++s_next[u];
+              if (++k_users[j & 1] == (j < n_vis[0]) + (j < n_vis[1])) {
+                tc_commit(&bars->k_empty[j & 1]);
+                k_users[j & 1] = 0;
+              }
+              progress = true;
+            }
           }
         }
-        tc_commit(&bars->v_empty[j & 1]);
-        if (j + 1 < n_tiles) tc_commit(&bars->k_empty[(j + 1) & 1]);
+        if (progress) {
+          t_idle = clock64();
+        } else if (bars->abort || clock64() - t_idle > kWaitCycles) {
+          if (!bars->abort) {
+            bars->abort = 1;
+            if (p.status != nullptr && atomicCAS(p.status, 0u, 1u) == 0u) {
+              p.status[1] = 0x610;
+              p.status[2] = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+              p.status[3] = (uint32_t)(pv_next[0] | (pv_next[1] << 16));
+            }
+          }
+          break;
+        }
       }
     }
     __syncwarp();
