@@ -90,6 +90,10 @@ struct Waiter {
   uint32_t* status;
   // Returns when the phase with this parity has completed, or after the cycle budget.
   __device__ __forceinline__ void operator()(uint64_t* bar, uint32_t parity, uint32_t where) const {
+#ifdef TPA_POLL_FIRST
+    for (int i = 0; i < TPA_POLL_FIRST; ++i)
+      if (mbar_test(bar, parity)) return;
+#endif
     if (mbar_try_wait(bar, parity)) return;
     const long long t0 = clock64();
     uint32_t spins = 0;
@@ -305,14 +309,15 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
   const int n_tiles = max(n_vis[0], n_vis[1]);
 
   if (threadIdx.x == 0) {
-    mbar_init(&bars->q_full, STAGED ? 1 : kRebuildWarps * 32);
+    // producers: one expect_tx arrival (STAGED) or one arrival per rebuild warp (FUSED)
+    mbar_init(&bars->q_full, STAGED ? 1 : kRebuildWarps);
     for (int s = 0; s < 2; ++s) {
-      mbar_init(&bars->k_full[s], STAGED ? 1 : kRebuildWarps * 16);
-      mbar_init(&bars->v_full[s], STAGED ? 1 : kRebuildWarps * 16);
+      mbar_init(&bars->k_full[s], STAGED ? 1 : kRebuildWarps / 2);
+      mbar_init(&bars->v_full[s], STAGED ? 1 : kRebuildWarps / 2);
       mbar_init(&bars->k_empty[s], 1);
       mbar_init(&bars->v_empty[s], 1);
       mbar_init(&bars->s_full[s], 1);
-      mbar_init(&bars->p_ready[s], kUnitRows);
+      mbar_init(&bars->p_ready[s], kUnitRows / 32);  // one arrival per softmax warp
       mbar_init(&bars->o_done[s], 1);
     }
     bars->abort = 0;
@@ -689,9 +694,10 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
           tmem_st32(tS + half * 32, pk);
         }
       }
-      tmem_st_wait();
+      tmem_st_wait();  // warp-wide: every lane's P has landed in TMEM
       tc_fence_before();
-      mbar_arrive(&bars->p_ready[u]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->p_ready[u]);
     }
 
     // ---- epilogue: o = acc / (l * R_k), lse = ln2 * (m + log2 l); NaN / -inf for empty rows
@@ -786,7 +792,8 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
                         p.qb.stride[2], p.rank_q, q0 + u * kUnitRows, qscale, rt, kRebuildWarps * 32);
     }
     fence_async_smem();
-    mbar_arrive(&bars->q_full);
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&bars->q_full);
 
     const bool is_k = rt < kRebuildWarps * 16;
     const int t = is_k ? rt : rt - kRebuildWarps * 16;
@@ -805,7 +812,8 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
       if (!is_k && has_seg)
         bars->kseg[s][t] = p.kv_seg[(int64_t)batch * p.kv_seg_bstride + (int64_t)j * kTileKv + t];
       fence_async_smem();
-      mbar_arrive(&full[s]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&full[s]);
     }
    }
   } else {
