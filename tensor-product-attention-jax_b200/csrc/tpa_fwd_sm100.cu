@@ -413,6 +413,25 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
       if (true) {
       } else
 #endif
+#if defined(TPA_EXPERIMENT) && (TPA_EXPERIMENT == 4 || TPA_EXPERIMENT == 5)
+      if (true) {  // perf ablation (numerics invalid): TMEM traffic and barriers only, no math
+        uint32_t xa[32], xb[32];
+#if TPA_EXPERIMENT == 4
+        tmem_ld32(tS, xa);
+        tmem_ld32(tS + 32, xb);
+        tmem_ld_wait();
+        tmem_ld32(tS + 64, xa);
+        tmem_ld32(tS + 96, xb);
+        tmem_ld_wait();
+#else
+        for (int e = 0; e < 32; ++e) xa[e] = xb[e] = 0x3c003c00u;
+#endif
+        tmem_st32(tS, xa);
+        tmem_st32(tS + 32, xb);
+        l += 1.f;
+        if (m == -CUDART_INF_F) m = 0.f;
+      } else
+#endif
       if constexpr (STAGED) {
         auto mask_chunk = [&](uint32_t(&r)[32], int c) {
 #pragma unroll
