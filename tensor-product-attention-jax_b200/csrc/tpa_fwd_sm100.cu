@@ -263,7 +263,7 @@ __global__ void __launch_bounds__(256) tpa_stage_tiles_kernel(const Params p, ui
 template <int D, bool STAGED>
 __global__ void __launch_bounds__(Roles<STAGED>::kThreads, 1)
 tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, const uint8_t* ws_v,
-                     const bool head_major) {
+                     const bool head_major, const bool poll_issue) {
   constexpr int kMmaWarp = Roles<STAGED>::kMmaWarp;
   constexpr int kTileBytes = kUnitRows * D * 2;  // one Q unit, one K stage or one V stage
   constexpr uint32_t kIdescS = make_idesc(128, kTileKv, false, false);
@@ -859,12 +859,44 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
         tc_commit(&bars->o_done[u]);
       };
       // Per unit the order is fixed: S(j), O += P V of tile j, S(j+1) (which overwrites P), ...
-      // Across the two units the thread issues whichever next operation has its operands
-      // ready (non-blocking barrier tests), so a unit whose softmax is late never holds back
-      // the other, and no wake-up latency of a blocking wait sits between softmax and MMA.
+      // Two ways to interleave the units (chosen per launch, see launch_sm100):
+      //  - fixed order PV0(j) S0(j+1) PV1(j) S1(j+1) with blocking waits: least issue
+      //    overhead, best once a CTA walks many key tiles;
+      //  - polling: issue whichever unit's next operation has its operands ready, so a unit
+      //    whose softmax is late never holds back the other: best for short CTAs.
       wait(&bars->q_full, 0, 0x600);
       tc_fence_after();
+      if (!poll_issue) {
+        wait(&bars->k_full[0], 0, 0x601);
+        tc_fence_after();
+        for (int u = 0; u < 2; ++u)
+          if (n_vis[u] > 0) issue_s(u, 0);
+        tc_commit(&bars->k_empty[0]);
+        for (int j = 0; j < n_tiles; ++j) {
+          wait(&bars->v_full[j & 1], (j >> 1) & 1, 0x602);
+          tc_fence_after();
+          bool k_waited = false;
+          for (int u = 0; u < 2; ++u) {
+            if (j < n_vis[u]) {
+              wait(&bars->p_ready[u], j & 1, 0x610 + u);
+              tc_fence_after();
+              issue_pv(u, j, load_state || j > 0);
+            }
+            if (j + 1 < n_vis[u]) {
+              if (!k_waited) {
+                wait(&bars->k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, 0x603);
+                tc_fence_after();
+                k_waited = true;
+              }
+              issue_s(u, j + 1);
+            }
+          }
+          tc_commit(&bars->v_empty[j & 1]);
+          if (j + 1 < n_tiles) tc_commit(&bars->k_empty[(j + 1) & 1]);
+        }
+      }
       int s_next[2] = {0, 0}, pv_next[2] = {0, 0};  // next tile whose S / P V each unit issues
+      if (!poll_issue) pv_next[0] = n_vis[0], pv_next[1] = n_vis[1];
       int k_users[2] = {0, 0}, v_users[2] = {0, 0};
       long long t_idle = clock64();
       while (pv_next[0] < n_vis[0] || pv_next[1] < n_vis[1]) {
@@ -937,11 +969,11 @@ inline size_t staged_kv_bytes(const Params& p) { return align256((size_t)p.batch
 
 template <int D, bool STAGED>
 cudaError_t launch_attn(const Params& p, const uint8_t* wq, const uint8_t* wk, const uint8_t* wv,
-                        dim3 grid, bool head_major, size_t smem, cudaStream_t stream) {
+                        dim3 grid, bool head_major, bool poll_issue, size_t smem, cudaStream_t stream) {
   auto kern = tpa_fwd_sm100_kernel<D, STAGED>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
-  kern<<<grid, Roles<STAGED>::kThreads, smem, stream>>>(p, wq, wk, wv, head_major);
+  kern<<<grid, Roles<STAGED>::kThreads, smem, stream>>>(p, wq, wk, wv, head_major, poll_issue);
   return cudaGetLastError();
 }
 
@@ -982,6 +1014,9 @@ cudaError_t launch_sm100(const Params& p, int variant, void* workspace, TpaKerne
   // CTAs together instead so they share the tiles they stream.
   const bool head_major = staged && (size_t)p.heads * p.lk * p.dk * 4 > (size_t)96 << 20;
   dim3 grid = head_major ? dim3(pairs, p.heads, p.batch) : dim3(p.heads, pairs, p.batch);
+  // measured on B200: polling issue wins for CTAs that walk few key tiles (B4 T4096: 604 vs
+  // 418 TFLOP/s), fixed order from about 8192 keys on (T32768: 1010 vs 965)
+  const bool poll_issue = p.lk <= 8192;
   if (info) {
     info->kernel = variant;
     info->block_q = 2 * kUnitRows;
@@ -1007,11 +1042,11 @@ cudaError_t launch_sm100(const Params& p, int variant, void* workspace, TpaKerne
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     count_launch(1);
-    e = p.dk == 128 ? launch_attn<128, true>(p, wq, wk, wv, grid, head_major, smem, stream)
-                    : launch_attn<64, true>(p, wq, wk, wv, grid, head_major, smem, stream);
+    e = p.dk == 128 ? launch_attn<128, true>(p, wq, wk, wv, grid, head_major, poll_issue, smem, stream)
+                    : launch_attn<64, true>(p, wq, wk, wv, grid, head_major, poll_issue, smem, stream);
   } else {
-    e = p.dk == 128 ? launch_attn<128, false>(p, wq, wk, wv, grid, head_major, smem, stream)
-                    : launch_attn<64, false>(p, wq, wk, wv, grid, head_major, smem, stream);
+    e = p.dk == 128 ? launch_attn<128, false>(p, wq, wk, wv, grid, head_major, poll_issue, smem, stream)
+                    : launch_attn<64, false>(p, wq, wk, wv, grid, head_major, poll_issue, smem, stream);
   }
   if (e == cudaSuccess) count_launch(1);
   return e;
