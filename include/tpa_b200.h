@@ -58,8 +58,12 @@ enum {
                                (tpa/tpa.py:376-379 with both offsets 0)                        */
   TPA_FLAG_STATE_LOAD = 2,  /* start from the partial result in state_o / state_lse
                                (the carry of tpa/ring_tpa.py:69-71) instead of (0, -inf)       */
-  TPA_FLAG_STATE_STORE = 4  /* write the merged partial back to state_o / state_lse
+  TPA_FLAG_STATE_STORE = 4, /* write the merged partial back to state_o / state_lse
                                (tpa/ring_tpa.py:82-91) instead of the final o / lse            */
+  TPA_FLAG_REUSE_STAGED_Q = 8 /* the workspace is the one the previous call used, with the same
+                               q operand, sm_scale, ranks and shapes (the ring scan keeps q
+                               fixed, tpa/ring_tpa.py:73-79): the STAGED variant then skips
+                               re-staging Q.  Ignored by the other kernels.                    */
 };
 
 /* One factor operand: `ptr[b*stride[0] + l*stride[1] + r*stride[2] + c]`, c contiguous.

@@ -39,7 +39,8 @@ static int validate(const TpaFwdArgs* a, Params* p) {
   const bool load = (a->flags & TPA_FLAG_STATE_LOAD) != 0;
   if ((store || load) && (a->state_o == nullptr || a->state_lse == nullptr)) return TPA_ERR_BAD_ARG;
   if (!store && a->o == nullptr) return TPA_ERR_BAD_ARG;
-  if (a->flags & ~(uint32_t)(TPA_FLAG_CAUSAL | TPA_FLAG_STATE_LOAD | TPA_FLAG_STATE_STORE))
+  if (a->flags & ~(uint32_t)(TPA_FLAG_CAUSAL | TPA_FLAG_STATE_LOAD | TPA_FLAG_STATE_STORE |
+                             TPA_FLAG_REUSE_STAGED_Q))
     return TPA_ERR_BAD_ARG;
   if (a->kernel < TPA_KERNEL_AUTO || a->kernel > TPA_KERNEL_SM100_STAGED) return TPA_ERR_BAD_ARG;
   if (a->heads > 65535 || a->batch > 65535) return TPA_ERR_UNSUPPORTED;

@@ -196,11 +196,11 @@ __device__ __forceinline__ void rebuild_tile(uint8_t* dst, const __nv_bfloat16* 
 template <int D>
 __global__ void __launch_bounds__(256) tpa_stage_tiles_kernel(const Params p, uint8_t* ws_q,
                                                               uint8_t* ws_k, uint8_t* ws_v,
-                                                              float qscale) {
+                                                              float qscale, int first_tile) {
   constexpr int CH = D / 8;
   constexpr int kTileBytes = kUnitRows * D * 2;
   const int nq = p.lq / kUnitRows, nk = p.lk / kTileKv;
-  int tile = blockIdx.x;
+  int tile = blockIdx.x + first_tile;  // first_tile = lq/128 skips the Q tiles (already staged)
   const TpaFactor *fa, *fb;
   uint8_t* ws;
   int rank, ntiles;
@@ -1036,9 +1036,13 @@ cudaError_t launch_sm100(const Params& p, int variant, void* workspace, TpaKerne
     wk = wq + staged_q_bytes(p);
     wv = wk + staged_kv_bytes(p);
     const float qscale = p.sm_scale * kLog2e / ((float)p.rank_q * (float)p.rank_k);
-    dim3 sgrid(p.lq / kUnitRows + 2 * (p.lk / kTileKv), p.heads / 8, p.batch);
-    if (p.dk == 128) tpa_stage_tiles_kernel<128><<<sgrid, 256, 0, stream>>>(p, wq, wk, wv, qscale);
-    else tpa_stage_tiles_kernel<64><<<sgrid, 256, 0, stream>>>(p, wq, wk, wv, qscale);
+    // ring steps after the first keep the Q tiles the previous call staged in this workspace
+    const int first_tile = (p.flags & TPA_FLAG_REUSE_STAGED_Q) ? p.lq / kUnitRows : 0;
+    dim3 sgrid(p.lq / kUnitRows - first_tile + 2 * (p.lk / kTileKv), p.heads / 8, p.batch);
+    if (p.dk == 128)
+      tpa_stage_tiles_kernel<128><<<sgrid, 256, 0, stream>>>(p, wq, wk, wv, qscale, first_tile);
+    else
+      tpa_stage_tiles_kernel<64><<<sgrid, 256, 0, stream>>>(p, wq, wk, wv, qscale, first_tile);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     count_launch(1);

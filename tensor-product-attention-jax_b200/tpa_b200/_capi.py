@@ -28,7 +28,7 @@ KERNEL_AUTO, KERNEL_SIMT, KERNEL_SM100, KERNEL_SM100_FUSED, KERNEL_SM100_STAGED 
 KERNELS = {"auto": KERNEL_AUTO, "simt": KERNEL_SIMT, "sm100": KERNEL_SM100,
            "sm100_fused": KERNEL_SM100_FUSED, "sm100_staged": KERNEL_SM100_STAGED}
 KERNEL_NAMES = {KERNEL_SIMT: "simt", KERNEL_SM100_FUSED: "sm100_fused", KERNEL_SM100_STAGED: "sm100_staged"}
-FLAG_CAUSAL, FLAG_STATE_LOAD, FLAG_STATE_STORE = 1, 2, 4
+FLAG_CAUSAL, FLAG_STATE_LOAD, FLAG_STATE_STORE, FLAG_REUSE_STAGED_Q = 1, 2, 4, 8
 
 # Every symbol include/tpa_b200.h declares.
 EXPORTS = (

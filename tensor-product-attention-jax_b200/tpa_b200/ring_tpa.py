@@ -60,6 +60,7 @@ def _device_block(q, k, v, qs, ks, num_heads, sm_scale, causal, q_offset, k_offs
     return _tpa.fwd_device(
         q, k, v, num_heads, qs, ks, sm_scale, causal, q_offset=q_offset, k_offset=k_offset,
         state=state, load_state=load_state, store_state=store_state, out=out, want_lse=False,
+        reuse_staged_q=load_state,  # q and the workspace are those of the previous step
     )[0]
 
 

@@ -108,8 +108,12 @@ def fwd_device(
     lse=None,
     want_lse=True,
     kernel="auto",
+    reuse_staged_q=False,
 ):
     """One tpa_fwd call on CUDA tensors; returns (o, lse_fp32).
+
+    `reuse_staged_q=True` promises that the previous call on this stream had the same q,
+    shapes and scale (ring steps): the staged variant then keeps its Q tiles.
 
     `state = (state_o fp32 [b,lq,h,dv], state_lse fp32 [b,lq,h])` with `load_state` /
     `store_state` is the carry of the ring scan (tpa/ring_tpa.py:69-91): a call with
@@ -154,6 +158,8 @@ def fwd_device(
         flags |= _capi.FLAG_STATE_LOAD
     if store_state:
         flags |= _capi.FLAG_STATE_STORE
+    if reuse_staged_q:
+        flags |= _capi.FLAG_REUSE_STAGED_Q
     if load_state or store_state:
         so, sl = state
         assert so.dtype == torch.float32 and sl.dtype == torch.float32

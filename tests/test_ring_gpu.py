@@ -27,8 +27,8 @@ fails = []
 for (dtype, b, l, h, d, rq, rk, seg, mode, causal) in [
     ("f32", 2, 256 * world, 4, 32, 3, 2, 100, "reference_local", True),
     ("f32", 1, 256 * world, 4, 32, 3, 2, 0, "global", True),
-    ("bf16", 1, 1024 * world, 8, 128, 6, 2, 0, "reference_local", True),
-    ("bf16", 1, 1024 * world, 8, 128, 6, 2, 0, "global", True),
+    ("bf16", 1, 512 * world, 8, 128, 6, 2, 0, "reference_local", True),
+    ("bf16", 1, 512 * world, 8, 128, 6, 2, 0, "global", True),
     ("bf16", 1, 512 * world, 8, 64, 4, 4, 300, "reference_local", False),
 ]:
     q, k, v = orc.make_factors(77, b, l, l, rq, rk, h, d, d)
@@ -40,8 +40,13 @@ for (dtype, b, l, h, d, rq, rk, seg, mode, causal) in [
                                                  num_heads=h, sm_scale=d ** -0.5, causal=causal, mask_mode=mode,
                                                  gather_output=True)
     st, detail = tpa_b200.tpa.device_status()
+    if st != 0:
+        fails.append((dtype, l, mode, "device status", detail))
+    if rank != 0:
+        continue  # the gathered output is identical on every rank; one oracle run is enough
     ref = orc.ring_tpa_reference(tq.float().cpu().numpy(), tk.float().cpu().numpy(), tv.float().cpu().numpy(),
-                                 ids, ids, h, world, sm_scale=d ** -0.5, causal=causal, mask_mode=mode)
+                                 ids, ids, h, world, sm_scale=d ** -0.5, causal=causal, mask_mode=mode,
+                                 dtype=np.float32)
     diff = np.abs(o.float().cpu().numpy() - ref)
     ok = (diff.max() <= 1e-5) if dtype == "f32" else (diff.max() <= 2e-2 and diff.mean() <= 5e-3)
     ok = ok and st == 0 and np.array_equal(np.isnan(o.float().cpu().numpy()), np.isnan(ref))
