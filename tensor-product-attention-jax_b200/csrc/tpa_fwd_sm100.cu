@@ -192,7 +192,8 @@ __device__ __forceinline__ void rebuild_tile(uint8_t* dst, const __nv_bfloat16* 
 // Staging kernel: one CTA rebuilds one 128-row tile of Q, K or V for 8 heads and writes each
 // head's tile as the exact shared-memory image (64-column sub-tiles of 16 KB, 128-byte swizzle)
 // at ws[((batch * heads + head) * tiles + tile) * tile_bytes].
-// grid = (lq/128 + 2 * lk/128, heads/8, batch), 256 threads.
+// grid = (heads/8, lq/128 + 2 * lk/128, batch), 256 threads: the head groups of one tile are
+// adjacent in launch order, so the factor rows they share are read from HBM once.
 template <int D>
 __global__ void __launch_bounds__(256) tpa_stage_tiles_kernel(const Params p, uint8_t* ws_q,
                                                               uint8_t* ws_k, uint8_t* ws_v,
@@ -200,7 +201,7 @@ __global__ void __launch_bounds__(256) tpa_stage_tiles_kernel(const Params p, ui
   constexpr int CH = D / 8;
   constexpr int kTileBytes = kUnitRows * D * 2;
   const int nq = p.lq / kUnitRows, nk = p.lk / kTileKv;
-  int tile = blockIdx.x + first_tile;  // first_tile = lq/128 skips the Q tiles (already staged)
+  int tile = blockIdx.y + first_tile;  // first_tile = lq/128 skips the Q tiles (already staged)
   const TpaFactor *fa, *fb;
   uint8_t* ws;
   int rank, ntiles;
@@ -214,7 +215,7 @@ __global__ void __launch_bounds__(256) tpa_stage_tiles_kernel(const Params p, ui
     tile -= nq + nk;
     fa = &p.va; fb = &p.vb; ws = ws_v; rank = p.rank_k; ntiles = nk; scale = 1.f;
   }
-  const int hg = blockIdx.y, batch = blockIdx.z;
+  const int hg = blockIdx.x, batch = blockIdx.z;
   const __nv_bfloat16* a = static_cast<const __nv_bfloat16*>(fa->ptr) + batch * fa->stride[0] + hg * 8;
   const __nv_bfloat16* b = static_cast<const __nv_bfloat16*>(fb->ptr) + batch * fb->stride[0];
   const int chunk = threadIdx.x % CH, r_in = threadIdx.x / CH;
@@ -229,22 +230,33 @@ __global__ void __launch_bounds__(256) tpa_stage_tiles_kernel(const Params p, ui
     for (int h = 0; h < 8; ++h)
 #pragma unroll
       for (int e = 0; e < 8; ++e) acc[h][e] = 0.f;
-#pragma unroll 2
-    for (int r = 0; r < rank; ++r) {
-      const uint4 bv = __ldg(reinterpret_cast<const uint4*>(bp + r * fb->stride[2]));
-      const uint4 av = __ldg(reinterpret_cast<const uint4*>(ap + r * fa->stride[2]));
-      const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w}, aw[4] = {av.x, av.y, av.z, av.w};
-      float bf[8];
+    // four ranks at a time: their eight 16-byte loads are issued before any of the FMAs
+    for (int r0 = 0; r0 < rank; r0 += 4) {
+      uint4 bv[4], av[4];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        bf[2 * e] = __uint_as_float(bw[e] << 16);
-        bf[2 * e + 1] = __uint_as_float(bw[e] & 0xffff0000u);
+      for (int i = 0; i < 4; ++i) {
+        const int r = min(r0 + i, rank - 1);  // clamped loads; ranks past the end are skipped below
+        bv[i] = __ldg(reinterpret_cast<const uint4*>(bp + r * fb->stride[2]));
+        av[i] = __ldg(reinterpret_cast<const uint4*>(ap + r * fa->stride[2]));
       }
 #pragma unroll
-      for (int h = 0; h < 8; ++h) {
-        const float ah = __uint_as_float((h & 1) ? (aw[h >> 1] & 0xffff0000u) : (aw[h >> 1] << 16));
+      for (int i = 0; i < 4; ++i) {
+        if (r0 + i < rank) {
+          const uint32_t bw[4] = {bv[i].x, bv[i].y, bv[i].z, bv[i].w};
+          const uint32_t aw[4] = {av[i].x, av[i].y, av[i].z, av[i].w};
+          float bf[8];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) acc[h][e] = fmaf(ah, bf[e], acc[h][e]);
+          for (int e = 0; e < 4; ++e) {
+            bf[2 * e] = __uint_as_float(bw[e] << 16);
+            bf[2 * e + 1] = __uint_as_float(bw[e] & 0xffff0000u);
+          }
+#pragma unroll
+          for (int h = 0; h < 8; ++h) {
+            const float ah = __uint_as_float((h & 1) ? (aw[h >> 1] & 0xffff0000u) : (aw[h >> 1] << 16));
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[h][e] = fmaf(ah, bf[e], acc[h][e]);
+          }
+        }
       }
     }
     const uint32_t off = sw128_offset(row, chunk & 7);
@@ -1038,7 +1050,7 @@ cudaError_t launch_sm100(const Params& p, int variant, void* workspace, TpaKerne
     const float qscale = p.sm_scale * kLog2e / ((float)p.rank_q * (float)p.rank_k);
     // ring steps after the first keep the Q tiles the previous call staged in this workspace
     const int first_tile = (p.flags & TPA_FLAG_REUSE_STAGED_Q) ? p.lq / kUnitRows : 0;
-    dim3 sgrid(p.lq / kUnitRows - first_tile + 2 * (p.lk / kTileKv), p.heads / 8, p.batch);
+    dim3 sgrid(p.heads / 8, p.lq / kUnitRows - first_tile + 2 * (p.lk / kTileKv), p.batch);
     if (p.dk == 128)
       tpa_stage_tiles_kernel<128><<<sgrid, 256, 0, stream>>>(p, wq, wk, wv, qscale, first_tile);
     else
