@@ -47,17 +47,15 @@ namespace {
 
 using namespace ptx;
 
-constexpr int kSoftmaxWarps = 8;
 constexpr int kRebuildWarps = 8;
 template <bool STAGED>
 struct Roles {
+  // STAGED: two softmax threads per query row (16 warps); FUSED: one (8 warps)
+  static constexpr int kSoftmaxWarps = STAGED ? 16 : 8;
   static constexpr int kProducerWarps = STAGED ? 1 : kRebuildWarps;
   static constexpr int kMmaWarp = kSoftmaxWarps + kProducerWarps;
-  // STAGED: 12 warps = 3 warpgroups (producer, MMA and two idle warps form the third), so
-  // that registers can be moved from the third warpgroup to the softmax ones.  FUSED: 17.
-  static constexpr int kThreads = STAGED ? 384 : (kMmaWarp + 1) * 32;
+  static constexpr int kThreads = (kMmaWarp + 1) * 32;  // STAGED 18 warps, FUSED 17
 };
-constexpr int kSoftmaxRegs = 224, kOtherRegs = 56;  // 8*32*224 + 4*32*56 = 64512 <= 65536
 constexpr int kUnitRows = 128;
 constexpr int kTileKv = 128;
 constexpr float kLog2e = 1.4426950408889634f;
@@ -83,6 +81,8 @@ struct Barriers {
   volatile uint32_t abort;
   // key segment ids of the tile in each V stage (filled and released together with it)
   alignas(16) int32_t kseg[2][kTileKv];
+  // exchange between the two threads of a row (STAGED): [slot][unit][column half][row]
+  float xch[2][2][2][kUnitRows];
 };
 
 struct Waiter {
@@ -272,11 +272,13 @@ __global__ void __launch_bounds__(256) tpa_stage_tiles_kernel(const Params p, ui
   }
 }
 
+
 template <int D, bool STAGED>
 __global__ void __launch_bounds__(Roles<STAGED>::kThreads, 1)
 tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, const uint8_t* ws_v,
                      const bool head_major, const bool poll_issue) {
   constexpr int kMmaWarp = Roles<STAGED>::kMmaWarp;
+  constexpr int kSoftmaxWarps = Roles<STAGED>::kSoftmaxWarps;
   constexpr int kTileBytes = kUnitRows * D * 2;  // one Q unit, one K stage or one V stage
   constexpr uint32_t kIdescS = make_idesc(128, kTileKv, false, false);
   constexpr uint32_t kIdescPV = make_idesc(128, D, false, true);
@@ -329,7 +331,7 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
       mbar_init(&bars->k_empty[s], 1);
       mbar_init(&bars->v_empty[s], 1);
       mbar_init(&bars->s_full[s], 1);
-      mbar_init(&bars->p_ready[s], kUnitRows / 32);  // one arrival per softmax warp
+      mbar_init(&bars->p_ready[s], kSoftmaxWarps / 2);  // one arrival per softmax warp of the unit
       mbar_init(&bars->o_done[s], 1);
     }
     bars->abort = 0;
@@ -344,13 +346,6 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
   tc_fence_after();
   const uint32_t tmem = bars->tmem_base;
   const Waiter wait{bars, p.status};
-  if constexpr (STAGED) {
-    // whole-warpgroup register reallocation: the softmax threads keep 64 packed P words and
-    // two 32-column chunks of S live at once
-    if (warp < kSoftmaxWarps) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kSoftmaxRegs));
-    else asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kOtherRegs));
-  }
-
   const __nv_bfloat16* qa = static_cast<const __nv_bfloat16*>(p.qa.ptr) + batch * p.qa.stride[0] + head;
   const __nv_bfloat16* qb = static_cast<const __nv_bfloat16*>(p.qb.ptr) + batch * p.qb.stride[0];
   const __nv_bfloat16* ka = static_cast<const __nv_bfloat16*>(p.ka.ptr) + batch * p.ka.stride[0] + head;
@@ -359,6 +354,278 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
   const __nv_bfloat16* vb = static_cast<const __nv_bfloat16*>(p.vb.ptr) + batch * p.vb.stride[0];
 
   if (warp < kSoftmaxWarps) {
+   if constexpr (STAGED) {
+    // ------------------------------------------------------------------ softmax + epilogue (STAGED)
+    // Two threads per query row: 16 warps, warp w serves unit w >> 3, column half (w >> 2) & 1
+    // and TMEM lanes 32 (w & 3)...  Thread (unit, half, row) exponentiates 64 of the 128 keys of
+    // each tile and owns D/2 columns of the accumulator row.  The two warps that share 32 rows
+    // meet on their own named barrier: a one-bit vote per tile on the fast path, the row
+    // maximum (through shared memory) on the exact path, the row sum at the end.
+    const int u = warp >> 3;
+    const int half = (warp >> 2) & 1;
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const int pair_bar = 1 + u * 4 + quarter;  // named barrier of the two partner warps
+    const int n_u = n_vis[u];
+    const int q0u = q0 + u * kUnitRows;
+    const int grow = q0u + row;
+    const bool live = q0u < p.lq;
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    const uint32_t tS = tmem + lane_base + u * 128;
+    const uint32_t tSh = tS + half * 64;                        // this thread's 64 logits
+    const uint32_t tOh = tmem + lane_base + kOCol + u * D + half * (D / 2);  // its D/2 accumulators
+    const int64_t rh = live ? ((int64_t)batch * p.lq + grow) * p.heads + head : 0;
+    const int64_t qpos = (int64_t)grow + p.q_offset;
+    const int qseg = (has_seg && live) ? p.q_seg[(int64_t)batch * p.q_seg_bstride + grow] : 0;
+    const float rk = (float)p.rank_k;
+    constexpr int kOChunks = D / 64;  // 32-column chunks of the accumulator this thread owns
+
+    auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory"); };
+    auto pair_any = [&](bool pred) -> bool {
+      uint32_t out;
+      asm volatile(
+          "{\n\t.reg .pred pin, pout;\n\t"
+          "setp.ne.u32 pin, %1, 0;\n\t"
+          "bar.red.or.pred pout, %2, 64, pin;\n\t"
+          "selp.u32 %0, 1, 0, pout;\n\t}"
+          : "=r"(out)
+          : "r"((uint32_t)pred), "r"(pair_bar)
+          : "memory");
+      return out != 0;
+    };
+
+    float m = -CUDART_INF_F, l = 0.f;  // m is the same in both halves of a row; l is this half's share
+    bool loaded = false;
+    if (load_state && live && n_u > 0) {
+      // carried partial (tpa/ring_tpa.py:69-71): accumulator = o_prev (times R_k, see header),
+      // row sum 1 (counted once, in half 0), maximum = previous LSE
+      const float prev = p.state_lse[rh];
+      const bool has = prev != -CUDART_INF_F;
+      if (has) {
+        m = prev * kLog2e;
+        l = half == 0 ? 1.f : 0.f;
+      }
+      const float* so = p.state_o + rh * D + half * (D / 2);
+#pragma unroll
+      for (int c = 0; c < kOChunks; ++c) {
+        uint32_t r[32];
+#pragma unroll
+        for (int e = 0; e < 32; e += 4) {
+          float4 v = has ? *reinterpret_cast<const float4*>(so + c * 32 + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+          r[e] = __float_as_uint(v.x * rk);
+          r[e + 1] = __float_as_uint(v.y * rk);
+          r[e + 2] = __float_as_uint(v.z * rk);
+          r[e + 3] = __float_as_uint(v.w * rk);
+        }
+        tmem_st32(tOh + c * 32, r);
+      }
+      tmem_st_wait();
+      loaded = true;
+    }
+
+    for (int j = 0; j < n_u; ++j) {
+      wait(&bars->s_full[u], j & 1, 0x100 + u);
+      tc_fence_after();
+      const int k0 = j * kTileKv + half * 64;  // first key of this thread's columns
+      const bool diag = causal && ((int64_t)k0 + 63 + p.k_offset > (int64_t)q0u + p.q_offset);
+      // Segment ids: when every key of these 64 columns and every row of this warp carry the
+      // same id, nothing is masked and the element-wise test is skipped (warp-uniform).
+      const int32_t* ks = bars->kseg[j & 1] + half * 64;
+      bool seg_mask = false;
+      if (has_seg) {
+        wait(&bars->v_full[j & 1], (j >> 1) & 1, 0x700 + u);
+        const int2 k2 = *reinterpret_cast<const int2*>(ks + lane * 2);
+        const int kmin = __reduce_min_sync(0xffffffffu, min(k2.x, k2.y));
+        const int kmax = __reduce_max_sync(0xffffffffu, max(k2.x, k2.y));
+        seg_mask = !__all_sync(0xffffffffu, kmin == kmax && qseg == kmin);
+      }
+      const bool masked = diag || seg_mask;
+
+      auto mask_chunk = [&](uint32_t(&r)[32], int c) {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const int kc = k0 + c * 32 + e;
+          bool keep = true;
+          if (diag) keep = qpos >= (int64_t)kc + p.k_offset;
+          if (seg_mask) keep = keep && (qseg == ks[c * 32 + e]);
+          if (!keep) r[e] = 0xff800000u;  // -inf
+        }
+      };
+      // p = 2^(s - reference maximum) for one 32-column chunk, packed to bf16, plus the row
+      // sum in four packed partial sums.
+      uint64_t neg_m2 = 0, lsum[4];
+      auto set_reference = [&](float mm) {
+        const float neg_m = (mm == -CUDART_INF_F) ? 0.f : -mm;
+        neg_m2 = pack2(neg_m, neg_m);
+        lsum[0] = lsum[1] = lsum[2] = lsum[3] = 0ull;
+      };
+      auto exp_chunk = [&](const uint32_t(&r)[32], uint32_t* pk) {
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float x0, x1;
+          unpack2(add2(pack2(__uint_as_float(r[e]), __uint_as_float(r[e + 1])), neg_m2), x0, x1);
+          const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+          lsum[(e >> 1) & 3] = add2(lsum[(e >> 1) & 3], pack2(p0, p1));
+          pk[e / 2] = pack_bf16(p0, p1);
+        }
+      };
+      auto row_sum = [&]() {
+        float a0, a1, a2, a3;
+        unpack2(add2(lsum[0], lsum[1]), a0, a1);
+        unpack2(add2(lsum[2], lsum[3]), a2, a3);
+        return (a0 + a1) + (a2 + a3);
+      };
+
+      uint32_t pk[32];
+      // One 32-column chunk of logits is live at a time (the register budget of 18 warps):
+      // fetch, mask, use, fetch the next.
+      auto load_chunk = [&](uint32_t(&r)[32], int c) {
+        tmem_ld32(tSh + c * 32, r);
+        tmem_ld_wait();
+        if (masked) mask_chunk(r, c);
+      };
+      auto exp_row = [&]() {
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t r[32];
+          load_chunk(r, c);
+          exp_chunk(r, pk + c * 16);
+        }
+      };
+      // Optimistic: exponentiate against the maximum carried from earlier tiles.  A sum of
+      // at most 2^15 over this thread's columns proves each p is at most 2^15 (no overflow,
+      // bf16 keeps its relative precision), so the carried maximum may stay although it can
+      // be stale.  Both halves of every row of the warp pair must agree (one-bit vote);
+      // otherwise, or when a row has no maximum yet, nothing has been stored and the exact
+      // route finds the row maximum first (the logits are still in TMEM and are fetched again).
+      // m is identical in both halves, so both warps of a pair always take the same branches.
+      bool done = false;
+      if (__all_sync(0xffffffffu, m != -CUDART_INF_F)) {
+        set_reference(m);
+        exp_row();
+        const float tsum = row_sum();
+        const bool bad = __any_sync(0xffffffffu, !(tsum <= kOptimisticSumLimit));  // inf / NaN too
+        if (!pair_any(bad)) {
+          l += tsum;
+          done = true;
+        }
+      }
+      if (!done) {
+        float cm = -CUDART_INF_F;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t r[32];
+          load_chunk(r, c);
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) cm = max3(cm, __uint_as_float(r[e]), __uint_as_float(r[e + 1]));
+        }
+        // row maximum over both halves, through shared memory (slot alternates with the tile)
+        float* xch = bars->xch[j & 1][u][0];
+        xch[half * kUnitRows + row] = cm;
+        pair_sync();
+        const float m_new = fmaxf(m, fmaxf(xch[row], xch[kUnitRows + row]));
+        float factor = 1.f;
+        if (m == -CUDART_INF_F) {
+          m = m_new;  // nothing accumulated for this row yet (l = 0, accumulator row is 0)
+        } else if (m_new - m > kRescaleThreshold) {
+          factor = fast_exp2(m - m_new);
+          m = m_new;
+        }
+        if (__any_sync(0xffffffffu, factor != 1.f) && (j > 0 || loaded)) {
+          if (j > 0) {
+            wait(&bars->o_done[u], (j - 1) & 1, 0x200 + u);
+            tc_fence_after();
+          }
+#pragma unroll
+          for (int c = 0; c < kOChunks; ++c) {
+            uint32_t r[32];
+            tmem_ld32(tOh + c * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * factor);
+            tmem_st32(tOh + c * 32, r);
+          }
+        }
+        l *= factor;
+        set_reference(m);
+        exp_row();
+        l += row_sum();
+      }
+      // P of this half overwrites the first 32 columns of its own 64 logits: key k of the tile
+      // is at column (k / 64) * 64 + (k % 64) / 2 (the PV MMAs address it that way)
+      tmem_st32(tSh, pk);
+      tmem_st_wait();  // warp-wide: every lane's P (and any rescaled accumulator) has landed
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->p_ready[u]);
+    }
+
+    // ---- epilogue: o = acc / (l * R_k), lse = ln2 * (m + log2 l); NaN / -inf for empty rows
+    if (live) {
+      if (n_u > 0) {
+        wait(&bars->o_done[u], (n_u - 1) & 1, 0x300 + u);
+        tc_fence_after();
+      }
+      // row sum = this half's share + the partner's
+      float* xch = bars->xch[n_u & 1][u][0];
+      xch[half * kUnitRows + row] = l;
+      pair_sync();
+      l = xch[row] + xch[kUnitRows + row];
+      const bool empty = !(l > 0.f);
+      float inv = empty ? 0.f : 1.f / (l * rk);
+      float lse = empty ? -CUDART_INF_F : (m + log2f(l)) * kLn2;
+      const bool passthrough = (n_u == 0) && load_state;  // nothing visible: carry the state over
+      if (passthrough) {
+        lse = p.state_lse[rh];
+        inv = 1.f;
+      }
+      const bool none = passthrough ? (lse == -CUDART_INF_F) : empty;
+      __nv_bfloat16* orow = store_state ? nullptr
+                                        : static_cast<__nv_bfloat16*>(p.o) + rh * D + half * (D / 2);
+      float* srow = (store_state || passthrough) ? p.state_o + rh * D + half * (D / 2) : nullptr;
+#pragma unroll
+      for (int c = 0; c < kOChunks; ++c) {
+        uint32_t r[32];
+        if (n_u > 0) {
+          tmem_ld32(tOh + c * 32, r);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e)
+            r[e] = (passthrough && !none) ? __float_as_uint(srow[c * 32 + e]) : 0u;
+        }
+        if (store_state) {
+          if (!passthrough) {
+#pragma unroll
+            for (int e = 0; e < 32; e += 4) {
+              float4 v = make_float4(__uint_as_float(r[e]) * inv, __uint_as_float(r[e + 1]) * inv,
+                                     __uint_as_float(r[e + 2]) * inv, __uint_as_float(r[e + 3]) * inv);
+              *reinterpret_cast<float4*>(srow + c * 32 + e) = v;
+            }
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; e += 8) {
+            uint32_t w[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const float x0 = none ? CUDART_NAN_F : __uint_as_float(r[e + 2 * k]) * inv;
+              const float x1 = none ? CUDART_NAN_F : __uint_as_float(r[e + 2 * k + 1]) * inv;
+              w[k] = pack_bf16(x0, x1);
+            }
+            *reinterpret_cast<uint4*>(orow + c * 32 + e) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+      }
+      if (half == 0) {
+        if (store_state) {
+          if (!passthrough) p.state_lse[rh] = lse;
+        } else if (p.lse != nullptr) {
+          p.lse[rh] = lse;
+        }
+      }
+    }
+   } else {
     // ------------------------------------------------------------------ softmax + epilogue
     const int u = warp >> 2;
     const int row = (warp & 3) * 32 + lane;
@@ -788,6 +1055,7 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
         p.lse[rh] = lse;
       }
     }
+   }
   } else if (warp < kMmaWarp) {
    if constexpr (STAGED) {
     // ------------------------------------------------------------------ bulk copies of staged tiles
@@ -865,7 +1133,8 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
         const uint32_t vbase = aV + (j & 1) * kTileBytes;
 #pragma unroll
         for (int ks = 0; ks < kTileKv / 16; ++ks) {
-          mma_ts(tmem + kOCol + u * D, tmem + u * 128 + ks * 8,
+          // P of key k: column k / 2 (FUSED), or (k / 64) * 64 + (k % 64) / 2 (STAGED, see softmax)
+          mma_ts(tmem + kOCol + u * D, tmem + u * 128 + (STAGED ? (ks >> 2) * 64 + (ks & 3) * 8 : ks * 8),
                  make_desc(vbase + ks * 2048, kTileKv * 128, 1024), kIdescPV, (acc || ks > 0) ? 1u : 0u);
         }
         tc_commit(&bars->o_done[u]);
