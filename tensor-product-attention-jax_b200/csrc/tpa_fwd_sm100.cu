@@ -16,11 +16,14 @@
 //           the lq/256-fold repetition of the rebuild (64x on average at T = 32768).
 //
 // Roles, by warp:
-//   warps 0-3 / 4-7   online softmax of unit 0 / unit 1 (one thread per query row: TMEM lane)
-//   FUSED  warps 8-11 / 12-15  rebuild the K / V tile (all eight rebuild Q once at the start)
-//          warp 16             issues tcgen05.mma: S_u = Q_u K^T (fp32 in TMEM), O_u += P_u V
-//   STAGED warp 8              one thread issues the bulk copies of the staged tiles
-//          warp 9              issues tcgen05.mma
+//   FUSED   warps 0-3 / 4-7: online softmax of unit 0 / unit 1, one thread per query row
+//           (= TMEM lane); warps 8-11 / 12-15: rebuild the K / V tile (all eight rebuild Q once
+//           at the start); warp 16: issues tcgen05.mma: S_u = Q_u K^T (fp32 in TMEM), O_u += P_u V
+//   STAGED  warps 0-7 / 8-15: online softmax of unit 0 / unit 1, two threads per query row
+//           (each takes 64 of the 128 keys of a tile and half of the accumulator columns;
+//           the per-thread instruction stream, not the exponentials, is what the tensor pipe
+//           waits for, so halving it is worth a pair barrier per tile);
+//           warp 16: one thread issues the bulk copies of the staged tiles; warp 17: tcgen05.mma
 //
 // The 1/R_q, 1/R_k means and sm_scale * log2(e) are folded into Q once; the 1/R_k of V is
 // applied with the final 1/l.  K and V tiles are double buffered, in the 128-byte-swizzled
@@ -30,7 +33,9 @@
 //
 // The running maximum is only raised when the new tile exceeds it by more than 2^8 (the
 // accumulator and row sum are then rescaled); the final 1/l division makes the result
-// independent of which maximum was subtracted.
+// independent of which maximum was subtracted.  STAGED goes further: it exponentiates against
+// the carried maximum straight away and only falls back to finding the tile maximum when a
+// row sum shows that some p exceeded 2^15.
 //
 // Every mbarrier wait is bounded: after ~2^28 cycles the waiter records where it gave up in
 // the status block, raises a CTA-wide abort flag that makes all later waits fall through,
@@ -63,15 +68,6 @@ constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 constexpr float kOptimisticSumLimit = 32768.f;  // 2^15, see the softmax role
 constexpr long long kWaitCycles = 1ll << 28;
-// polynomial 2^x: which of every 8 column pairs leave the MUFU pipe (bit i = pair i mod 8)
-#ifndef TPA_POLY_PAIRS
-#define TPA_POLY_PAIRS 0x00
-#endif
-constexpr uint32_t kPolyPairs = TPA_POLY_PAIRS;
-constexpr float kExpMagic = 12582912.f;  // 1.5 * 2^23: adding it rounds to the nearest integer
-constexpr float kExpC0 = 0.9999280571937561f, kExpC1 = 0.6932609677314758f,
-                kExpC2 = 0.2426111251115799f, kExpC3 = 0.0551716648042202f;
-
 struct Barriers {
   uint64_t q_full;
   uint64_t k_full[2], k_empty[2];
@@ -90,10 +86,6 @@ struct Waiter {
   uint32_t* status;
   // Returns when the phase with this parity has completed, or after the cycle budget.
   __device__ __forceinline__ void operator()(uint64_t* bar, uint32_t parity, uint32_t where) const {
-#ifdef TPA_POLL_FIRST
-    for (int i = 0; i < TPA_POLL_FIRST; ++i)
-      if (mbar_test(bar, parity)) return;
-#endif
     if (mbar_try_wait(bar, parity)) return;
     const long long t0 = clock64();
     uint32_t spins = 0;
@@ -131,19 +123,10 @@ __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
   asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
   return r;
 }
-__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
-  uint64_t r;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
-  return r;
-}
 __device__ __forceinline__ float fast_exp2(float x) {
-#if defined(TPA_EXPERIMENT) && TPA_EXPERIMENT == 1
-  return x;
-#else
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
-#endif
 }
 
 // dst tile rows [0,128): dst[row][:] = scale * sum_r a[row0+row, r] * b[row0+row, r, :], bf16,
@@ -688,309 +671,87 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
       }
       const bool masked = diag || seg_mask;
 
-#if defined(TPA_EXPERIMENT) && TPA_EXPERIMENT == 3
-      if (true) {
-      } else
-#endif
-#if defined(TPA_EXPERIMENT) && (TPA_EXPERIMENT == 4 || TPA_EXPERIMENT == 5)
-      if (true) {  // perf ablation (numerics invalid): TMEM traffic and barriers only, no math
-        uint32_t xa[32], xb[32];
-#if TPA_EXPERIMENT == 4
-        tmem_ld32(tS, xa);
-        tmem_ld32(tS + 32, xb);
+      // pass 1: row maximum of the (masked) logits; they are already in log2 units
+      float tmax = -CUDART_INF_F;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tS + c * 32, r);
         tmem_ld_wait();
-        tmem_ld32(tS + 64, xa);
-        tmem_ld32(tS + 96, xb);
-        tmem_ld_wait();
-#else
-        for (int e = 0; e < 32; ++e) xa[e] = xb[e] = 0x3c003c00u;
-#endif
-        tmem_st32(tS, xa);
-        tmem_st32(tS + 32, xb);
-        l += 1.f;
-        if (m == -CUDART_INF_F) m = 0.f;
-      } else
-#endif
-      if constexpr (STAGED) {
-        auto mask_chunk = [&](uint32_t(&r)[32], int c) {
+        if (masked) {
 #pragma unroll
           for (int e = 0; e < 32; ++e) {
             const int kc = k0 + c * 32 + e;
             bool keep = true;
             if (diag) keep = qpos >= (int64_t)kc + p.k_offset;
             if (seg_mask) keep = keep && (qseg == ks[c * 32 + e]);
-            if (!keep) r[e] = 0xff800000u;  // -inf
+            if (keep) tmax = fmaxf(tmax, __uint_as_float(r[e]));
           }
-        };
-        // p = 2^(s - reference maximum) for one 32-column chunk, packed to bf16, with the
-        // row sum (four packed partial sums) and, optionally, the running maximum of s.
-        // On unmasked tiles the pairs selected by kPolyPairs are evaluated on the FMA pipe
-        // (round-to-nearest split x = n + f, degree-3 minimax polynomial for 2^f on
-        // [-1/2, 1/2], relative error 7.5e-5, n added to the exponent field) to take load
-        // off the MUFU pipe.  Masked tiles need exact zeros for -inf and use ex2 throughout.
-        uint64_t neg_m2 = 0, lsum[4];
-        float x_floor = 0.f, cmx[2];
-#ifdef TPA_SCALAR_SOFTMAX
-        float neg_m_s = 0.f, fsum[8];
-#endif
-        auto set_reference = [&](float mm) {
-          const float neg_m = (mm == -CUDART_INF_F) ? 0.f : -mm;
-          neg_m2 = pack2(neg_m, neg_m);
-#ifdef TPA_SCALAR_SOFTMAX
-          neg_m_s = neg_m;
-          for (int i = 0; i < 8; ++i) fsum[i] = 0.f;
-#endif
-          x_floor = -126.f - neg_m;
-          lsum[0] = lsum[1] = lsum[2] = lsum[3] = 0ull;
-          cmx[0] = cmx[1] = -CUDART_INF_F;
-        };
-        auto exp_chunk = [&](const uint32_t(&r)[32], uint32_t* pk, auto poly_tag, auto track_tag) {
-          constexpr bool kPoly = decltype(poly_tag)::value;
-          constexpr bool kTrack = decltype(track_tag)::value;
+        } else {
 #pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            const float s0 = __uint_as_float(r[e]), s1 = __uint_as_float(r[e + 1]);
-            if (kTrack) cmx[(e >> 1) & 1] = max3(cmx[(e >> 1) & 1], s0, s1);
-            float p0, p1;
-            if (kPoly && ((kPolyPairs >> ((e >> 1) & 7)) & 1)) {
-              const uint64_t x = add2(pack2(fmaxf(s0, x_floor), fmaxf(s1, x_floor)), neg_m2);
-              const uint64_t t = add2(x, pack2(kExpMagic, kExpMagic));
-              const uint64_t n = add2(t, pack2(-kExpMagic, -kExpMagic));
-              const uint64_t f = fma2(n, pack2(-1.f, -1.f), x);
-              uint64_t q = fma2(f, pack2(kExpC3, kExpC3), pack2(kExpC2, kExpC2));
-              q = fma2(q, f, pack2(kExpC1, kExpC1));
-              q = fma2(q, f, pack2(kExpC0, kExpC0));
-              float t0, t1, q0, q1;
-              unpack2(t, t0, t1);
-              unpack2(q, q0, q1);
-              p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(t0) << 23));
-              p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(t1) << 23));
-            } else {
-#ifdef TPA_SCALAR_SOFTMAX
-              p0 = fast_exp2(s0 + neg_m_s);
-              p1 = fast_exp2(s1 + neg_m_s);
-#else
-              float x0, x1;
-              unpack2(add2(pack2(s0, s1), neg_m2), x0, x1);
-              p0 = fast_exp2(x0);
-              p1 = fast_exp2(x1);
-#endif
-            }
-#ifdef TPA_SCALAR_SOFTMAX
-            fsum[(e >> 1) & 3] += p0;
-            fsum[4 + ((e >> 1) & 3)] += p1;
-#else
-            lsum[(e >> 1) & 3] = add2(lsum[(e >> 1) & 3], pack2(p0, p1));
-#endif
-            pk[e / 2] = pack_bf16(p0, p1);
-          }
-        };
-        auto row_sum = [&]() {
-#ifdef TPA_SCALAR_SOFTMAX
-          return ((fsum[0] + fsum[1]) + (fsum[2] + fsum[3])) + ((fsum[4] + fsum[5]) + (fsum[6] + fsum[7]));
-#endif
-          float a0, a1, a2, a3;
-          unpack2(add2(lsum[0], lsum[1]), a0, a1);
-          unpack2(add2(lsum[2], lsum[3]), a2, a3);
-          return (a0 + a1) + (a2 + a3);
-        };
+          for (int e = 0; e < 32; ++e) tmax = fmaxf(tmax, __uint_as_float(r[e]));
+        }
+      }
+      const float m_new = fmaxf(m, tmax);
+      float factor = 1.f;
+      if (m == -CUDART_INF_F) {
+        m = m_new;  // nothing accumulated for this row yet (l = 0, accumulator row is 0)
+      } else if (m_new - m > kRescaleThreshold) {
+        factor = fast_exp2(m - m_new);
+        m = m_new;
+      }
+      if (__any_sync(0xffffffffu, factor != 1.f) && (j > 0 || loaded)) {
+        if (j > 0) {
+          wait(&bars->o_done[u], (j - 1) & 1, 0x200 + u);
+          tc_fence_after();
+        }
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(tO + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * factor);
+          tmem_st32(tO + c * 32, r);
+        }
+        tmem_st_wait();
+      }
+      l *= factor;
+      const float m_sub = (m == -CUDART_INF_F) ? 0.f : m;
 
-        // Optimistic single pass: exponentiate against the maximum carried from earlier
-        // tiles; P stays in registers until the row sums are known.  A row sum of at most
-        // 2^15 proves every p of the row is at most 2^15 (no overflow anywhere, bf16 keeps its
-        // relative precision), so the carried maximum can stay although it may be stale.
-        // Otherwise (or when a row has no maximum yet) nothing has been stored and the exact
-        // two-pass path below runs instead and raises the maximum.
-        bool done = false;
-        if (__all_sync(0xffffffffu, m != -CUDART_INF_F)) {
-          set_reference(m);
-          uint32_t ra[32], rb[32], pk[64];
-          tmem_ld32(tS, ra);
-          tmem_ld32(tS + 32, rb);
-          tmem_ld_wait();
-          auto single = [&](auto poly_tag) {
-            if (masked) {
-              mask_chunk(ra, 0);
-              mask_chunk(rb, 1);
-            }
-            exp_chunk(ra, pk, poly_tag, std::false_type{});
-            tmem_ld32(tS + 64, ra);
-            exp_chunk(rb, pk + 16, poly_tag, std::false_type{});
-            tmem_ld32(tS + 96, rb);
-            tmem_ld_wait();
-            if (masked) {
-              mask_chunk(ra, 2);
-              mask_chunk(rb, 3);
-            }
-            exp_chunk(ra, pk + 32, poly_tag, std::false_type{});
-            exp_chunk(rb, pk + 48, poly_tag, std::false_type{});
-          };
-          if (masked) single(std::false_type{});
-          else single(std::true_type{});
-          const float tsum = row_sum();
-          if (!__any_sync(0xffffffffu, !(tsum <= kOptimisticSumLimit))) {  // also catches inf / NaN
-            tmem_st32(tS, *reinterpret_cast<uint32_t(*)[32]>(pk));
-            tmem_st32(tS + 32, *reinterpret_cast<uint32_t(*)[32]>(pk + 32));
-            l += tsum;
-            done = true;
-          }
-        }
-        if (!done) {
-          // Exact path.  Pass 1: all four chunks at once for the row maximum.  Pass 2 re-reads
-          // them two at a time, the second pair in flight while the first is exponentiated.
-          float tmax;
-          {
-            uint32_t sc[4][32];
+      // pass 2: p = 2^(s - m), row sum, bf16 P over the first 64 columns of S
 #pragma unroll
-            for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, sc[c]);
-            tmem_ld_wait();
-            if (masked) {
+      for (int half = 0; half < 2; ++half) {
+        uint32_t pk[32];
 #pragma unroll
-              for (int c = 0; c < 4; ++c) mask_chunk(sc[c], c);
-            }
-            float cm[4];
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-              cm[c] = fmaxf(__uint_as_float(sc[c][0]), __uint_as_float(sc[c][1]));
-#pragma unroll
-              for (int e = 2; e < 32; e += 2)
-                cm[c] = max3(cm[c], __uint_as_float(sc[c][e]), __uint_as_float(sc[c][e + 1]));
-            }
-            tmax = fmaxf(fmaxf(cm[0], cm[1]), fmaxf(cm[2], cm[3]));
-          }
-          uint32_t ra[32], rb[32];
-          tmem_ld32(tS, ra);
-          tmem_ld32(tS + 32, rb);
-          const float m_new = fmaxf(m, tmax);
-          float factor = 1.f;
-          if (m == -CUDART_INF_F) {
-            m = m_new;  // nothing accumulated for this row yet (l = 0, accumulator row is 0)
-          } else if (m_new - m > kRescaleThreshold) {
-            factor = fast_exp2(m - m_new);
-            m = m_new;
-          }
-          if (__any_sync(0xffffffffu, factor != 1.f) && (j > 0 || loaded)) {
-            if (j > 0) {
-              wait(&bars->o_done[u], (j - 1) & 1, 0x200 + u);
-              tc_fence_after();
-            }
-#pragma unroll
-            for (int c = 0; c < D / 32; ++c) {
-              uint32_t r[32];
-              tmem_ld32(tO + c * 32, r);
-              tmem_ld_wait();
-#pragma unroll
-              for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * factor);
-              tmem_st32(tO + c * 32, r);
-            }
-            tmem_st_wait();
-          }
-          l *= factor;
-          set_reference(m);
-          uint32_t pk[32];
-          tmem_ld_wait();
-          if (masked) {
-            mask_chunk(ra, 0);
-            mask_chunk(rb, 1);
-          }
-          exp_chunk(ra, pk, std::false_type{}, std::false_type{});
-          tmem_ld32(tS + 64, ra);
-          exp_chunk(rb, pk + 16, std::false_type{}, std::false_type{});
-          tmem_ld32(tS + 96, rb);
-          tmem_ld_wait();  // P below overwrites columns [0,32): both re-reads must have landed
-          tmem_st32(tS, pk);
-          if (masked) {
-            mask_chunk(ra, 2);
-            mask_chunk(rb, 3);
-          }
-          exp_chunk(ra, pk, std::false_type{}, std::false_type{});
-          exp_chunk(rb, pk + 16, std::false_type{}, std::false_type{});
-          tmem_st32(tS + 32, pk);
-          l += row_sum();
-        }
-      } else {
-        // pass 1: row maximum of the (masked) logits; they are already in log2 units
-        float tmax = -CUDART_INF_F;
-  #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int cc = 0; cc < 2; ++cc) {
+          const int c = half * 2 + cc;
           uint32_t r[32];
           tmem_ld32(tS + c * 32, r);
           tmem_ld_wait();
-          if (masked) {
-  #pragma unroll
-            for (int e = 0; e < 32; ++e) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            float s0 = __uint_as_float(r[e]), s1 = __uint_as_float(r[e + 1]);
+            if (masked) {
               const int kc = k0 + c * 32 + e;
-              bool keep = true;
-              if (diag) keep = qpos >= (int64_t)kc + p.k_offset;
-              if (seg_mask) keep = keep && (qseg == ks[c * 32 + e]);
-              if (keep) tmax = fmaxf(tmax, __uint_as_float(r[e]));
-            }
-          } else {
-  #pragma unroll
-            for (int e = 0; e < 32; ++e) tmax = fmaxf(tmax, __uint_as_float(r[e]));
-          }
-        }
-        const float m_new = fmaxf(m, tmax);
-        float factor = 1.f;
-        if (m == -CUDART_INF_F) {
-          m = m_new;  // nothing accumulated for this row yet (l = 0, accumulator row is 0)
-        } else if (m_new - m > kRescaleThreshold) {
-          factor = fast_exp2(m - m_new);
-          m = m_new;
-        }
-        if (__any_sync(0xffffffffu, factor != 1.f) && (j > 0 || loaded)) {
-          if (j > 0) {
-            wait(&bars->o_done[u], (j - 1) & 1, 0x200 + u);
-            tc_fence_after();
-          }
-  #pragma unroll
-          for (int c = 0; c < D / 32; ++c) {
-            uint32_t r[32];
-            tmem_ld32(tO + c * 32, r);
-            tmem_ld_wait();
-  #pragma unroll
-            for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * factor);
-            tmem_st32(tO + c * 32, r);
-          }
-          tmem_st_wait();
-        }
-        l *= factor;
-        const float m_sub = (m == -CUDART_INF_F) ? 0.f : m;
-
-        // pass 2: p = 2^(s - m), row sum, bf16 P over the first 64 columns of S
-  #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t pk[32];
-  #pragma unroll
-          for (int cc = 0; cc < 2; ++cc) {
-            const int c = half * 2 + cc;
-            uint32_t r[32];
-            tmem_ld32(tS + c * 32, r);
-            tmem_ld_wait();
-  #pragma unroll
-            for (int e = 0; e < 32; e += 2) {
-              float s0 = __uint_as_float(r[e]), s1 = __uint_as_float(r[e + 1]);
-              if (masked) {
-                const int kc = k0 + c * 32 + e;
-                bool keep0 = true, keep1 = true;
-                if (diag) {
-                  keep0 = qpos >= (int64_t)kc + p.k_offset;
-                  keep1 = qpos >= (int64_t)kc + 1 + p.k_offset;
-                }
-                if (seg_mask) {
-                  keep0 = keep0 && (qseg == ks[c * 32 + e]);
-                  keep1 = keep1 && (qseg == ks[c * 32 + e + 1]);
-                }
-                if (!keep0) s0 = -CUDART_INF_F;
-                if (!keep1) s1 = -CUDART_INF_F;
+              bool keep0 = true, keep1 = true;
+              if (diag) {
+                keep0 = qpos >= (int64_t)kc + p.k_offset;
+                keep1 = qpos >= (int64_t)kc + 1 + p.k_offset;
               }
-              const float p0 = fast_exp2(s0 - m_sub), p1 = fast_exp2(s1 - m_sub);
-              l += p0 + p1;
-              pk[cc * 16 + e / 2] = pack_bf16(p0, p1);
+              if (seg_mask) {
+                keep0 = keep0 && (qseg == ks[c * 32 + e]);
+                keep1 = keep1 && (qseg == ks[c * 32 + e + 1]);
+              }
+              if (!keep0) s0 = -CUDART_INF_F;
+              if (!keep1) s1 = -CUDART_INF_F;
             }
+            const float p0 = fast_exp2(s0 - m_sub), p1 = fast_exp2(s1 - m_sub);
+            l += p0 + p1;
+            pk[cc * 16 + e / 2] = pack_bf16(p0, p1);
           }
-          tmem_st32(tS + half * 32, pk);
         }
+        tmem_st32(tS + half * 32, pk);
       }
       tmem_st_wait();  // warp-wide: every lane's P has landed in TMEM
       tc_fence_before();
