@@ -259,7 +259,7 @@ __global__ void __launch_bounds__(256) tpa_stage_tiles_kernel(const Params p, ui
 template <int D, bool STAGED>
 __global__ void __launch_bounds__(Roles<STAGED>::kThreads, 1)
 tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, const uint8_t* ws_v,
-                     const bool head_major, const bool poll_issue) {
+                     const bool head_major) {
   constexpr int kMmaWarp = Roles<STAGED>::kMmaWarp;
   constexpr int kSoftmaxWarps = Roles<STAGED>::kSoftmaxWarps;
   constexpr int kTileBytes = kUnitRows * D * 2;  // one Q unit, one K stage or one V stage
@@ -900,15 +900,14 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
         }
         tc_commit(&bars->o_done[u]);
       };
-      // Per unit the order is fixed: S(j), O += P V of tile j, S(j+1) (which overwrites P), ...
-      // Two ways to interleave the units (chosen per launch, see launch_sm100):
-      //  - fixed order PV0(j) S0(j+1) PV1(j) S1(j+1) with blocking waits: least issue
-      //    overhead, best once a CTA walks many key tiles;
-      //  - polling: issue whichever unit's next operation has its operands ready, so a unit
-      //    whose softmax is late never holds back the other: best for short CTAs.
+      // Per unit the order is fixed: S(j), O += P V of tile j, S(j+1) (which overwrites P).  The
+      // units are interleaved in a fixed order too, PV0(j) S0(j+1) PV1(j) S1(j+1): it keeps them
+      // half a tile apart, so that the softmax of one always has the other's MMAs to hide behind.
+      // (Measured alternatives that lost: polling for whichever unit is ready first, and one
+      // issuing thread per unit; both let the units drift into phase.)
       wait(&bars->q_full, 0, 0x600);
       tc_fence_after();
-      if (!poll_issue) {
+      {
         wait(&bars->k_full[0], 0, 0x601);
         tc_fence_after();
         for (int u = 0; u < 2; ++u)
@@ -937,56 +936,6 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
           if (j + 1 < n_tiles) tc_commit(&bars->k_empty[(j + 1) & 1]);
         }
       }
-      int s_next[2] = {0, 0}, pv_next[2] = {0, 0};  // next tile whose S / P V each unit issues
-      if (!poll_issue) pv_next[0] = n_vis[0], pv_next[1] = n_vis[1];
-      int k_users[2] = {0, 0}, v_users[2] = {0, 0};
-      long long t_idle = clock64();
-      while (pv_next[0] < n_vis[0] || pv_next[1] < n_vis[1]) {
-        bool progress = false;
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          if (pv_next[u] < n_vis[u]) {
-            const int j = pv_next[u];
-            if (s_next[u] > j && mbar_test(&bars->p_ready[u], j & 1) &&
-                mbar_test(&bars->v_full[j & 1], (j >> 1) & 1)) {
-              tc_fence_after();
-              issue_pv(u, j, load_state || j > 0);
-              ++pv_next[u];
-              if (++v_users[j & 1] == (j < n_vis[0]) + (j < n_vis[1])) {
-                tc_commit(&bars->v_empty[j & 1]);
-                v_users[j & 1] = 0;
-              }
-              progress = true;
-            }
-          }
-          if (s_next[u] < n_vis[u]) {
-            const int j = s_next[u];
-            if (pv_next[u] >= j && mbar_test(&bars->k_full[j & 1], (j >> 1) & 1)) {
-              tc_fence_after();
-              issue_s(u, j);
-              ++s_next[u];
-              if (++k_users[j & 1] == (j < n_vis[0]) + (j < n_vis[1])) {
-                tc_commit(&bars->k_empty[j & 1]);
-                k_users[j & 1] = 0;
-              }
-              progress = true;
-            }
-          }
-        }
-        if (progress) {
-          t_idle = clock64();
-        } else if (bars->abort || clock64() - t_idle > kWaitCycles) {
-          if (!bars->abort) {
-            bars->abort = 1;
-            if (p.status != nullptr && atomicCAS(p.status, 0u, 1u) == 0u) {
-              p.status[1] = 0x610;
-              p.status[2] = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
-              p.status[3] = (uint32_t)(pv_next[0] | (pv_next[1] << 16));
-            }
-          }
-          break;
-        }
-      }
     }
     __syncwarp();
   }
@@ -1011,11 +960,11 @@ inline size_t staged_kv_bytes(const Params& p) { return align256((size_t)p.batch
 
 template <int D, bool STAGED>
 cudaError_t launch_attn(const Params& p, const uint8_t* wq, const uint8_t* wk, const uint8_t* wv,
-                        dim3 grid, bool head_major, bool poll_issue, size_t smem, cudaStream_t stream) {
+                        dim3 grid, bool head_major, size_t smem, cudaStream_t stream) {
   auto kern = tpa_fwd_sm100_kernel<D, STAGED>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
-  kern<<<grid, Roles<STAGED>::kThreads, smem, stream>>>(p, wq, wk, wv, head_major, poll_issue);
+  kern<<<grid, Roles<STAGED>::kThreads, smem, stream>>>(p, wq, wk, wv, head_major);
   return cudaGetLastError();
 }
 
@@ -1056,9 +1005,6 @@ cudaError_t launch_sm100(const Params& p, int variant, void* workspace, TpaKerne
   // CTAs together instead so they share the tiles they stream.
   const bool head_major = staged && (size_t)p.heads * p.lk * p.dk * 4 > (size_t)96 << 20;
   dim3 grid = head_major ? dim3(pairs, p.heads, p.batch) : dim3(p.heads, pairs, p.batch);
-  // measured on B200: polling issue wins for CTAs that walk few key tiles (B4 T4096: 604 vs
-  // 418 TFLOP/s), fixed order from about 8192 keys on (T32768: 1010 vs 965)
-  const bool poll_issue = p.lk <= 8192;
   if (info) {
     info->kernel = variant;
     info->block_q = 2 * kUnitRows;
@@ -1088,11 +1034,11 @@ cudaError_t launch_sm100(const Params& p, int variant, void* workspace, TpaKerne
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     count_launch(1);
-    e = p.dk == 128 ? launch_attn<128, true>(p, wq, wk, wv, grid, head_major, poll_issue, smem, stream)
-                    : launch_attn<64, true>(p, wq, wk, wv, grid, head_major, poll_issue, smem, stream);
+    e = p.dk == 128 ? launch_attn<128, true>(p, wq, wk, wv, grid, head_major, smem, stream)
+                    : launch_attn<64, true>(p, wq, wk, wv, grid, head_major, smem, stream);
   } else {
-    e = p.dk == 128 ? launch_attn<128, false>(p, wq, wk, wv, grid, head_major, poll_issue, smem, stream)
-                    : launch_attn<64, false>(p, wq, wk, wv, grid, head_major, poll_issue, smem, stream);
+    e = p.dk == 128 ? launch_attn<128, false>(p, wq, wk, wv, grid, head_major, smem, stream)
+                    : launch_attn<64, false>(p, wq, wk, wv, grid, head_major, smem, stream);
   }
   if (e == cudaSuccess) count_launch(1);
   return e;
