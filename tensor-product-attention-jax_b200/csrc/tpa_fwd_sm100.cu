@@ -95,7 +95,7 @@ struct Waiter {
         bars->abort = 1;
         if (status != nullptr && atomicCAS(status, 0u, 1u) == 0u) {
           status[1] = where;
-          status[2] = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+          status[2] = blockIdx.x;
           status[3] = spins;
         }
         return;
@@ -259,7 +259,7 @@ __global__ void __launch_bounds__(256) tpa_stage_tiles_kernel(const Params p, ui
 template <int D, bool STAGED>
 __global__ void __launch_bounds__(Roles<STAGED>::kThreads, 1)
 tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, const uint8_t* ws_v,
-                     const bool head_major) {
+                     const int pairs, const int group) {
   constexpr int kMmaWarp = Roles<STAGED>::kMmaWarp;
   constexpr int kSoftmaxWarps = Roles<STAGED>::kSoftmaxWarps;
   constexpr int kTileBytes = kUnitRows * D * 2;  // one Q unit, one K stage or one V stage
@@ -276,12 +276,14 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
   Barriers* bars = reinterpret_cast<Barriers*>(smem + 6 * kTileBytes);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // Launch order (x fastest) decides what shares L2 (see launch_sm100): head-major runs the
-  // CTAs of one head together, row-major runs the heads of one row block together.  Either
-  // way the longest causal rows go first.
-  const int head = head_major ? blockIdx.y : blockIdx.x;
-  const int pair = head_major ? gridDim.x - 1 - blockIdx.x : gridDim.y - 1 - blockIdx.y;
-  const int batch = blockIdx.z;
+  // Launch order decides what shares L2 and how the kernel ends (see launch_sm100): the
+  // (batch, head) slices are taken `group` at a time; within a group the longest causal rows
+  // of every slice go first and the slices of one row block are adjacent.
+  const int per_group = group * pairs;
+  const int slice = (blockIdx.x / per_group) * group + (blockIdx.x % per_group) % group;
+  const int pair = pairs - 1 - (blockIdx.x % per_group) / group;
+  const int head = slice % p.heads;
+  const int batch = slice / p.heads;
   const int q0 = pair * 2 * kUnitRows;
   const bool causal = (p.flags & TPA_FLAG_CAUSAL) != 0;
   const bool has_seg = p.q_seg != nullptr;
@@ -960,11 +962,11 @@ inline size_t staged_kv_bytes(const Params& p) { return align256((size_t)p.batch
 
 template <int D, bool STAGED>
 cudaError_t launch_attn(const Params& p, const uint8_t* wq, const uint8_t* wk, const uint8_t* wv,
-                        dim3 grid, bool head_major, size_t smem, cudaStream_t stream) {
+                        dim3 grid, int pairs, int group, size_t smem, cudaStream_t stream) {
   auto kern = tpa_fwd_sm100_kernel<D, STAGED>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
-  kern<<<grid, Roles<STAGED>::kThreads, smem, stream>>>(p, wq, wk, wv, head_major);
+  kern<<<grid, Roles<STAGED>::kThreads, smem, stream>>>(p, wq, wk, wv, pairs, group);
   return cudaGetLastError();
 }
 
@@ -1000,11 +1002,18 @@ cudaError_t launch_sm100(const Params& p, int variant, void* workspace, TpaKerne
   const bool staged = variant == TPA_KERNEL_SM100_STAGED;
   const size_t smem = p.dk == 128 ? smem_bytes<128>() : smem_bytes<64>();
   const int pairs = (p.lq + 2 * kUnitRows - 1) / (2 * kUnitRows);
-  // Row-major order (all heads of the longest rows first) balances best, but its concurrent
-  // CTAs touch the staged K/V of every head; once that exceeds what L2 holds, run one head's
-  // CTAs together instead so they share the tiles they stream.
-  const bool head_major = staged && (size_t)p.heads * p.lk * p.dk * 4 > (size_t)96 << 20;
-  dim3 grid = head_major ? dim3(pairs, p.heads, p.batch) : dim3(p.heads, pairs, p.batch);
+  // Taking all (batch, head) slices of the longest rows first balances best and leaves only
+  // short CTAs for the end, but the concurrent CTAs then touch the staged K/V of every slice.
+  // So slices are taken in groups whose K/V (lk * d * 4 bytes each) fit in about half of L2:
+  // the CTAs of a group stream the same tiles together, and the kernel still ends on the
+  // shortest rows of the last group instead of on a whole head's longest ones.
+  const int slices = p.heads * p.batch;
+  int group = slices;
+  if (staged) {
+    const size_t per_slice = (size_t)p.lk * p.dk * 4;
+    while (group > 1 && ((size_t)group * per_slice > ((size_t)72 << 20) || slices % group != 0)) --group;
+  }
+  dim3 grid((unsigned)(pairs * slices), 1, 1);
   if (info) {
     info->kernel = variant;
     info->block_q = 2 * kUnitRows;
@@ -1034,11 +1043,11 @@ cudaError_t launch_sm100(const Params& p, int variant, void* workspace, TpaKerne
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     count_launch(1);
-    e = p.dk == 128 ? launch_attn<128, true>(p, wq, wk, wv, grid, head_major, smem, stream)
-                    : launch_attn<64, true>(p, wq, wk, wv, grid, head_major, smem, stream);
+    e = p.dk == 128 ? launch_attn<128, true>(p, wq, wk, wv, grid, pairs, group, smem, stream)
+                    : launch_attn<64, true>(p, wq, wk, wv, grid, pairs, group, smem, stream);
   } else {
-    e = p.dk == 128 ? launch_attn<128, false>(p, wq, wk, wv, grid, head_major, smem, stream)
-                    : launch_attn<64, false>(p, wq, wk, wv, grid, head_major, smem, stream);
+    e = p.dk == 128 ? launch_attn<128, false>(p, wq, wk, wv, grid, pairs, group, smem, stream)
+                    : launch_attn<64, false>(p, wq, wk, wv, grid, pairs, group, smem, stream);
   }
   if (e == cudaSuccess) count_launch(1);
   return e;
