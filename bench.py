@@ -44,7 +44,7 @@ METRIC = "TPA forward throughput (algorithmic attention FLOPs 4*B*h*d*pairs per 
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
 # captures summarised under profiles/ (bytes; None until a capture for that workload exists)
-NCU_TRAFFIC = {"c2": 810022912 + 251772416}  # attention kernel at full size, profiles/c2_launch_list.md
+NCU_TRAFFIC = {"c2": 1231663104 + 264633856}  # attention kernel at full size, profiles/c2_launch_list.md
 
 
 def flops(b, t, h, d, causal):
