@@ -203,3 +203,45 @@ def test_bf16_peaky_and_segments(kernel):
     """Large logits (online-softmax rescaling really happens) and packed segments."""
     mx, mean, lerr, refmax = bf16_case(6, 2, 512, 8, 128, 4, 4, True, kernel, segs=200, scale=24.0)
     assert mx <= 2e-2 * max(1.0, refmax) and mean <= 5e-3, (mx, mean, lerr, refmax)
+
+
+def _random_cases(n=14, seed=1234):
+    rng = np.random.default_rng(seed)
+    cases = []
+    for i in range(n):
+        d = int(rng.choice([64, 128]))
+        cases.append(dict(
+            seed=2000 + i, b=int(rng.integers(1, 3)), lq=128 * int(rng.integers(1, 9)),
+            lk=128 * int(rng.integers(1, 9)), h=int(rng.choice([8, 16])), d=d,
+            rq=int(rng.integers(1, 7)), rk=int(rng.integers(1, 5)), causal=bool(rng.integers(0, 2)),
+            seg=int(rng.choice([0, 0, 100, 300])), q_off=128 * int(rng.integers(0, 4)),
+            k_off=128 * int(rng.integers(0, 4)), scale=float(rng.choice([1.0, 1.0, 16.0]))))
+    return cases
+
+
+@pytest.mark.parametrize("case", _random_cases(), ids=lambda c: f"s{c['seed']}")
+@pytest.mark.parametrize("kernel", ["sm100_fused", "sm100_staged"])
+def test_tensor_core_variants_agree_with_generic_kernel(case, kernel):
+    """Randomised shapes, ranks, offsets, segments and logit scales: each tensor-core variant
+    against the fp32-math kernel on the same bf16 inputs (the latter is pinned to the oracle)."""
+    c = case
+    q, k, v = orc.make_factors(c["seed"], c["b"], c["lq"], c["lk"], c["rq"], c["rk"], c["h"], c["d"], c["d"])
+    tq, tk, tv = dev(q * c["scale"], torch.bfloat16), dev(k, torch.bfloat16), dev(v, torch.bfloat16)
+    qs = dev(orc.segment_ids(c["b"], c["lq"], c["seg"])) if c["seg"] else None
+    ks = dev(orc.segment_ids(c["b"], c["lk"], c["seg"])) if c["seg"] else None
+    args = dict(q_offset=c["q_off"], k_offset=c["k_off"])
+    want, wl = tpa_b200.tpa.fwd_device(tq, tk, tv, c["h"], qs, ks, c["d"] ** -0.5, c["causal"], kernel="simt", **args)
+    got, gl = tpa_b200.tpa.fwd_device(tq, tk, tv, c["h"], qs, ks, c["d"] ** -0.5, c["causal"], kernel=kernel, **args)
+    want, got = want.float(), got.float()
+    assert torch.equal(torch.isnan(want), torch.isnan(got))
+    assert torch.equal(torch.isinf(wl), torch.isinf(gl))
+    ok = ~torch.isnan(want)
+    scale = max(1.0, float(want[ok].abs().max())) if ok.any() else 1.0
+    diff = (want[ok] - got[ok]).abs()
+    if diff.numel():
+        assert diff.max() <= 2e-2 * scale and diff.mean() <= 5e-3 * scale, (float(diff.max()), float(diff.mean()))
+    fin = ~torch.isinf(wl)
+    if fin.any():
+        # the tensor-core kernels round Q and K to bf16 (2^-8 relative), so a logit, and with it
+        # the LSE, moves in proportion to its size
+        assert ((wl[fin] - gl[fin]).abs() <= 2e-2 + 1e-2 * wl[fin].abs()).all()
