@@ -56,12 +56,143 @@ def _rotate_block(tensors, recv_into, group, rank, size):
 
 
 def _device_block(q, k, v, qs, ks, num_heads, sm_scale, causal, q_offset, k_offset, state,
-                  load_state, store_state, out):
+                  load_state, store_state, out, reuse_q=True):
     return _tpa.fwd_device(
         q, k, v, num_heads, qs, ks, sm_scale, causal, q_offset=q_offset, k_offset=k_offset,
         state=state, load_state=load_state, store_state=store_state, out=out, want_lse=False,
-        reuse_staged_q=load_state,  # q and the workspace are those of the previous step
+        # q and the workspace are those of the previous step (not so when two query chunks alternate)
+        reuse_staged_q=load_state and reuse_q,
     )[0]
+
+
+def _device_block_fresh_q(*args):
+    return _device_block(*args, reuse_q=False)
+
+
+def _zigzag_owner(chunk, size):
+    """Rank that computes `chunk` (of 2 * size equal chunks of the whole sequence)."""
+    return chunk if chunk < size else 2 * size - 1 - chunk
+
+
+def _exchange_chunks(send, recv, group, rank):
+    """send/recv: lists of (peer rank in group, [tensors]); peers in increasing chunk order on
+    both sides, so that the pairwise send/recv order matches.  Local moves are plain copies."""
+    ops, copies = [], []
+    to_global = (lambda r: dist.get_global_rank(group, r)) if group is not None else (lambda r: r)
+    local_src = [ts for peer, ts in send if peer == rank]
+    local_dst = [ts for peer, ts in recv if peer == rank]
+    for src, dst in zip(local_src, local_dst):
+        copies += list(zip(dst, src))
+    for peer, ts in send:
+        if peer != rank:
+            ops += [dist.P2POp(dist.isend, t.contiguous(), to_global(peer), group) for t in ts]
+    for peer, ts in recv:
+        if peer != rank:
+            ops += [dist.P2POp(dist.irecv, t, to_global(peer), group) for t in ts]
+    reqs = dist.batch_isend_irecv(ops) if ops else []
+    for d, s_ in copies:
+        d.copy_(s_)
+    for r in reqs:
+        r.wait()
+
+
+def _ring_global_zigzag(q, k, v, qseg, kseg, group, size, rank, num_heads, sm_scale, block):
+    """Causal attention over the whole sequence with balanced ranks.
+
+    Contiguous shards make rank r do r + 1 of the N key blocks.  Here the sequence is cut into
+    2N chunks and rank r computes the queries of chunks r and 2N-1-r (one early, one late):
+    the rank's shard is first re-dealt that way (q, k, v and ids; the factors are small), the
+    K/V factors of both chunks ring-rotate as usual, every step costs two chunk-by-chunk
+    blocks on every rank, and the two output chunks travel back to the ranks that own those
+    rows.  Same result as tpa(causal=True) on the unsharded input.
+    """
+    b, lq = q.shape[:2]
+    if lq % 2 != 0 or k.shape[1] != lq:
+        raise AssertionError("the balanced global mask needs equal, even shard lengths")
+    c = lq // 2
+    dv = v.shape[-1] - num_heads
+    mine = [2 * rank, 2 * rank + 1]                 # chunks this rank holds on entry
+    want = [rank, 2 * size - 1 - rank]              # chunks it computes (early, late)
+    holder = lambda ch: ch // 2                     # noqa: E731  rank that holds chunk `ch` on entry
+
+    def halves(x):
+        return [x[:, :c], x[:, c:]]
+
+    src = {ch: [h[i] for h in map(halves, (q, k, v, qseg, kseg))] for i, ch in enumerate(mine)}
+    got = {ch: [torch.empty_like(t) for t in src[mine[0]]] for ch in want}
+    send = sorted(((_zigzag_owner(ch, size), ch) for ch in mine), key=lambda x: x[1])
+    recv = sorted(((holder(ch), ch) for ch in want), key=lambda x: x[1])
+    _exchange_chunks([(peer, src[ch]) for peer, ch in send], [(peer, got[ch]) for peer, ch in recv],
+                     group, rank)
+    (q_e, k_e, v_e, qs_e, ks_e), (q_l, k_l, v_l, qs_l, ks_l) = got[want[0]], got[want[1]]
+
+    dev, f32 = q.device, torch.float32
+    out_e = torch.empty((b, c, num_heads, dv), dtype=q.dtype, device=dev)
+    out_l = torch.empty_like(out_e)
+    st_e = (torch.empty((b, c, num_heads, dv), dtype=f32, device=dev), torch.empty((b, c, num_heads), dtype=f32, device=dev))
+    st_l = (torch.empty_like(st_e[0]), torch.empty_like(st_e[1]))
+    cur = [torch.cat([k_e, k_l], 1), torch.cat([v_e, v_l], 1), torch.cat([ks_e, ks_l], 1)]
+    spare = [[torch.empty_like(t) for t in cur] for _ in range(min(2, size - 1))]
+    use_streams = q.is_cuda
+    if use_streams:
+        main = torch.cuda.current_stream(dev)
+        side = _side_streams.get(dev) or _side_streams.setdefault(dev, torch.cuda.Stream(dev))
+        ready = torch.cuda.Event()
+        ready.record(main)
+    started_e = started_l = False
+    for s in range(size):
+        origin = (rank - s) % size  # the rank whose chunks (origin, 2N-1-origin) are visiting
+        reqs = None
+        if s < size - 1:
+            nxt = spare[s % 2]
+            if use_streams:
+                side.wait_event(ready)
+                with torch.cuda.stream(side):
+                    reqs = _rotate_block(cur, nxt, group, rank, size)
+            else:
+                reqs = _rotate_block(cur, nxt, group, rank, size)
+        kk, vv, ss = cur
+        # late queries: the visiting early chunk is always wholly visible, the late one iff
+        # origin > rank (wholly) or origin == rank (diagonal)
+        last_l = s == size - 1
+        if origin > rank:
+            block(q_l, kk, vv, qs_l, ss, num_heads, sm_scale, False, 0, 0, st_l, started_l, not last_l, out_l)
+        elif origin < rank:
+            block(q_l, kk[:, :c], vv[:, :c], qs_l, ss[:, :c], num_heads, sm_scale, False, 0, 0, st_l,
+                  started_l, not last_l, out_l)
+        else:  # positions: early chunk just before the late one, so that it stays wholly visible
+            block(q_l, kk, vv, qs_l, ss, num_heads, sm_scale, True, (2 * size - 1 - rank) * c,
+                  (2 * size - 2 - rank) * c, st_l, started_l, not last_l, out_l)
+        started_l = True
+        # early queries: only early chunks of ranks <= this one (steps 0..rank)
+        if origin <= rank:
+            block(q_e, kk[:, :c], vv[:, :c], qs_e, ss[:, :c], num_heads, sm_scale, origin == rank,
+                  rank * c, origin * c, st_e, started_e, s != rank, out_e)
+            started_e = True
+        if s < size - 1:
+            if use_streams:
+                ready = torch.cuda.Event()
+                ready.record(main)
+                with torch.cuda.stream(side):
+                    for r in reqs:
+                        r.wait()
+                    arrived = torch.cuda.Event()
+                    arrived.record(side)
+                main.wait_event(arrived)
+            else:
+                for r in reqs:
+                    r.wait()
+            cur = nxt
+    # the two output chunks go back to the ranks that own those rows
+    out = torch.empty((b, lq, num_heads, dv), dtype=q.dtype, device=dev)
+    back_send = sorted(((holder(ch), ch, o) for ch, o in zip(want, (out_e, out_l))), key=lambda x: x[1])
+    back_recv = sorted(((_zigzag_owner(ch, size), ch, o) for ch, o in zip(mine, halves(out))), key=lambda x: x[1])
+    tmp = [torch.empty_like(out_e) for _ in back_recv]
+    _exchange_chunks([(peer, [o]) for peer, _, o in back_send], [(peer, [t]) for (peer, _, _), t in zip(back_recv, tmp)],
+                     group, rank)
+    for (_, _, dst), t in zip(back_recv, tmp):
+        dst.copy_(t)
+    return out
 
 
 def ring_tpa(
@@ -119,6 +250,11 @@ def ring_tpa(
         raise AssertionError(tuple(k.shape))
     kseg = kv_segment_ids.to(torch.int32).contiguous()
     qseg = q_segment_ids.to(torch.int32).contiguous()
+
+    if causal and mask_mode == "global" and size > 1 and lq == lk and lq % 2 == 0:
+        zz_block = _device_block_fresh_q if _block_fn is None else _block_fn
+        return _ring_global_zigzag(q, k.contiguous(), v.contiguous(), qseg, kseg, group, size, rank,
+                                   num_heads, sm_scale, zz_block)
 
     use_streams = q.is_cuda
     out = torch.empty((b, lq, num_heads, dv), dtype=q.dtype, device=q.device)
