@@ -42,6 +42,8 @@
 // and the CTA runs to its normal end (TMEM is freed).
 #include <math_constants.h>
 
+#include <climits>
+
 #include <type_traits>
 
 #include "sm100_ptx.cuh"
@@ -256,10 +258,65 @@ __global__ void __launch_bounds__(256) tpa_stage_tiles_kernel(const Params p, ui
 }
 
 
+// ---------------------------------------------------------------------------------------------
+// Segment ids: which key tiles can each 256-row block see at all?  One CTA per (row block,
+// batch element) finds the id range of its two 128-row units and of every 128-key tile and
+// writes {first tile, end tile of unit 0, end tile of unit 1, 0}: the attention kernel then
+// walks only [first, end).  With packed sequences (ids non-decreasing) that is exactly the
+// tiles of the block's own segments; for arbitrary ids it is a superset, and the element-wise
+// test inside the tiles still decides.  grid = (pairs, batch), 128 threads.
+__global__ void __launch_bounds__(128) tpa_seg_ranges_kernel(const Params p, int4* ranges) {
+  __shared__ int red[4][4];   // per warp: min/max of unit 0, min/max of unit 1
+  __shared__ int first, last[2];
+  const int pair = blockIdx.x, batch = blockIdx.y, t = threadIdx.x;
+  const int32_t* qs = p.q_seg + (int64_t)batch * p.q_seg_bstride;
+  const int32_t* ks = p.kv_seg + (int64_t)batch * p.kv_seg_bstride;
+  const int n_kv = p.lk / kTileKv;
+  int lo[2], hi[2];
+#pragma unroll
+  for (int u = 0; u < 2; ++u) {
+    const int row = pair * 2 * kUnitRows + u * kUnitRows + t;
+    const int id = row < p.lq ? qs[row] : 0;
+    lo[u] = __reduce_min_sync(0xffffffffu, row < p.lq ? id : INT_MAX);
+    hi[u] = __reduce_max_sync(0xffffffffu, row < p.lq ? id : INT_MIN);
+  }
+  if ((t & 31) == 0) {
+    red[t >> 5][0] = lo[0]; red[t >> 5][1] = hi[0]; red[t >> 5][2] = lo[1]; red[t >> 5][3] = hi[1];
+  }
+  if (t == 0) { first = n_kv; last[0] = -1; last[1] = -1; }
+  __syncthreads();
+#pragma unroll
+  for (int u = 0; u < 2; ++u) {
+    lo[u] = min(min(red[0][2 * u], red[1][2 * u]), min(red[2][2 * u], red[3][2 * u]));
+    hi[u] = max(max(red[0][2 * u + 1], red[1][2 * u + 1]), max(red[2][2 * u + 1], red[3][2 * u + 1]));
+  }
+  for (int tile = t; tile < n_kv; tile += 128) {
+    const int4* src = reinterpret_cast<const int4*>(ks + (int64_t)tile * kTileKv);
+    int kmin = INT_MAX, kmax = INT_MIN;
+    for (int i = 0; i < kTileKv / 4; ++i) {
+      const int4 v = __ldg(src + i);
+      kmin = min(kmin, min(min(v.x, v.y), min(v.z, v.w)));
+      kmax = max(kmax, max(max(v.x, v.y), max(v.z, v.w)));
+    }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      if (kmin <= hi[u] && kmax >= lo[u]) {  // id ranges intersect (never true for an absent unit)
+        atomicMin(&first, tile);
+        atomicMax(&last[u], tile);
+      }
+    }
+  }
+  __syncthreads();
+  if (t == 0) {
+    const int f = first < n_kv ? first : 0;
+    ranges[(int64_t)batch * gridDim.x + pair] = make_int4(f, max(f, last[0] + 1), max(f, last[1] + 1), 0);
+  }
+}
+
 template <int D, bool STAGED>
 __global__ void __launch_bounds__(Roles<STAGED>::kThreads, 1)
 tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, const uint8_t* ws_v,
-                     const int pairs, const int group) {
+                     const int pairs, const int group, const int4* seg_ranges) {
   constexpr int kMmaWarp = Roles<STAGED>::kMmaWarp;
   constexpr int kSoftmaxWarps = Roles<STAGED>::kSoftmaxWarps;
   constexpr int kTileBytes = kUnitRows * D * 2;  // one Q unit, one K stage or one V stage
@@ -305,6 +362,18 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
       n_vis[u] = n_kv;
     }
   }
+  // With segment ids the walk starts at the first tile any row of the block can match and ends
+  // where the unit's last match is (tpa_seg_ranges_kernel).  From here on tiles are counted
+  // from j0: tile j of the loops below is key tile j0 + j.
+  int j0 = 0;
+  if (seg_ranges != nullptr) {
+    const int4 r = seg_ranges[(int64_t)batch * pairs + pair];
+    j0 = r.x;
+    n_vis[0] = min(n_vis[0], r.y);
+    n_vis[1] = min(n_vis[1], r.z);
+  }
+  n_vis[0] = max(0, n_vis[0] - j0);
+  n_vis[1] = max(0, n_vis[1] - j0);
   const int n_tiles = max(n_vis[0], n_vis[1]);
 
   if (threadIdx.x == 0) {
@@ -411,7 +480,7 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
     for (int j = 0; j < n_u; ++j) {
       wait(&bars->s_full[u], j & 1, 0x100 + u);
       tc_fence_after();
-      const int k0 = j * kTileKv + half * 64;  // first key of this thread's columns
+      const int k0 = (j0 + j) * kTileKv + half * 64;  // first key of this thread's columns
       const bool diag = causal && ((int64_t)k0 + 63 + p.k_offset > (int64_t)q0u + p.q_offset);
       // Segment ids: when every key of these 64 columns and every row of this warp carry the
       // same id, nothing is masked and the element-wise test is skipped (warp-uniform).
@@ -658,7 +727,7 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
     for (int j = 0; j < n_u; ++j) {
       wait(&bars->s_full[u], j & 1, 0x100 + u);
       tc_fence_after();
-      const int k0 = j * kTileKv;
+      const int k0 = (j0 + j) * kTileKv;
       const bool diag = causal && ((int64_t)k0 + kTileKv - 1 + p.k_offset > (int64_t)q0u + p.q_offset);
       // Segment ids: when every key of the tile and every row of this warp carry the same
       // id, nothing is masked and the element-wise test is skipped (warp-uniform decision).
@@ -834,12 +903,12 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
         const int s = j & 1;
         if (j >= 2) wait(&bars->k_empty[s], ((j >> 1) - 1) & 1, 0x400);
         mbar_arrive_expect_tx(&bars->k_full[s], kTileBytes);
-        bulk_g2s(sK + s * kTileBytes, gk + (int64_t)j * kTileBytes, kTileBytes, &bars->k_full[s]);
+        bulk_g2s(sK + s * kTileBytes, gk + (int64_t)(j0 + j) * kTileBytes, kTileBytes, &bars->k_full[s]);
         if (j >= 2) wait(&bars->v_empty[s], ((j >> 1) - 1) & 1, 0x500);
         mbar_arrive_expect_tx(&bars->v_full[s], kTileBytes + (has_seg ? kTileKv * 4 : 0));
-        bulk_g2s(sV + s * kTileBytes, gv + (int64_t)j * kTileBytes, kTileBytes, &bars->v_full[s]);
+        bulk_g2s(sV + s * kTileBytes, gv + (int64_t)(j0 + j) * kTileBytes, kTileBytes, &bars->v_full[s]);
         if (has_seg)
-          bulk_g2s(bars->kseg[s], p.kv_seg + (int64_t)batch * p.kv_seg_bstride + (int64_t)j * kTileKv,
+          bulk_g2s(bars->kseg[s], p.kv_seg + (int64_t)batch * p.kv_seg_bstride + (int64_t)(j0 + j) * kTileKv,
                    kTileKv * 4, &bars->v_full[s]);
       }
     }
@@ -870,9 +939,9 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
       const int s = j & 1;
       if (j >= 2) wait(&empty[s], ((j >> 1) - 1) & 1, is_k ? 0x400 : 0x500);
       rebuild_tile<D>(stages + s * kTileBytes, fa, sa.stride[1], sa.stride[2], fb, sb.stride[1],
-                      sb.stride[2], p.rank_k, (int64_t)j * kTileKv, 1.f, t, kRebuildWarps * 16);
+                      sb.stride[2], p.rank_k, (int64_t)(j0 + j) * kTileKv, 1.f, t, kRebuildWarps * 16);
       if (!is_k && has_seg)
-        bars->kseg[s][t] = p.kv_seg[(int64_t)batch * p.kv_seg_bstride + (int64_t)j * kTileKv + t];
+        bars->kseg[s][t] = p.kv_seg[(int64_t)batch * p.kv_seg_bstride + (int64_t)(j0 + j) * kTileKv + t];
       fence_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(&full[s]);
@@ -962,11 +1031,12 @@ inline size_t staged_kv_bytes(const Params& p) { return align256((size_t)p.batch
 
 template <int D, bool STAGED>
 cudaError_t launch_attn(const Params& p, const uint8_t* wq, const uint8_t* wk, const uint8_t* wv,
-                        dim3 grid, int pairs, int group, size_t smem, cudaStream_t stream) {
+                        dim3 grid, int pairs, int group, const int4* seg_ranges, size_t smem,
+                        cudaStream_t stream) {
   auto kern = tpa_fwd_sm100_kernel<D, STAGED>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
-  kern<<<grid, Roles<STAGED>::kThreads, smem, stream>>>(p, wq, wk, wv, pairs, group);
+  kern<<<grid, Roles<STAGED>::kThreads, smem, stream>>>(p, wq, wk, wv, pairs, group, seg_ranges);
   return cudaGetLastError();
 }
 
@@ -992,9 +1062,16 @@ int sm100_pick_variant(const Params& p) {
   return p.lq > 2 * kUnitRows ? TPA_KERNEL_SM100_STAGED : TPA_KERNEL_SM100_FUSED;
 }
 
+// one int4 per (batch, 256-row block) when segment ids are given
+inline size_t seg_range_bytes(const Params& p) {
+  if (p.q_seg == nullptr) return 0;
+  const size_t pairs = (p.lq + 2 * kUnitRows - 1) / (2 * kUnitRows);
+  return align256((size_t)p.batch * pairs * sizeof(int4));
+}
+
 size_t sm100_workspace_bytes(const Params& p, int variant) {
-  if (variant != TPA_KERNEL_SM100_STAGED) return 0;
-  return staged_q_bytes(p) + 2 * staged_kv_bytes(p);
+  if (variant != TPA_KERNEL_SM100_STAGED) return seg_range_bytes(p);
+  return seg_range_bytes(p) + staged_q_bytes(p) + 2 * staged_kv_bytes(p);
 }
 
 cudaError_t launch_sm100(const Params& p, int variant, void* workspace, TpaKernelInfo* info,
@@ -1023,13 +1100,21 @@ cudaError_t launch_sm100(const Params& p, int variant, void* workspace, TpaKerne
     info->grid[1] = grid.y;
     info->grid[2] = grid.z;
     info->smem_bytes = (int)smem;
-    info->launches = staged ? 2 : 1;
+    info->launches = (staged ? 2 : 1) + (p.q_seg != nullptr ? 1 : 0);
   }
   if (dry_run) return cudaSuccess;
   cudaError_t e;
+  int4* seg_ranges = nullptr;
+  if (p.q_seg != nullptr) {
+    seg_ranges = static_cast<int4*>(workspace);
+    tpa_seg_ranges_kernel<<<dim3(pairs, p.batch), 128, 0, stream>>>(p, seg_ranges);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    count_launch(1);
+  }
   uint8_t *wq = nullptr, *wk = nullptr, *wv = nullptr;
   if (staged) {
-    wq = static_cast<uint8_t*>(workspace);
+    wq = static_cast<uint8_t*>(workspace) + seg_range_bytes(p);
     wk = wq + staged_q_bytes(p);
     wv = wk + staged_kv_bytes(p);
     const float qscale = p.sm_scale * kLog2e / ((float)p.rank_q * (float)p.rank_k);
@@ -1043,11 +1128,11 @@ cudaError_t launch_sm100(const Params& p, int variant, void* workspace, TpaKerne
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     count_launch(1);
-    e = p.dk == 128 ? launch_attn<128, true>(p, wq, wk, wv, grid, pairs, group, smem, stream)
-                    : launch_attn<64, true>(p, wq, wk, wv, grid, pairs, group, smem, stream);
+    e = p.dk == 128 ? launch_attn<128, true>(p, wq, wk, wv, grid, pairs, group, seg_ranges, smem, stream)
+                    : launch_attn<64, true>(p, wq, wk, wv, grid, pairs, group, seg_ranges, smem, stream);
   } else {
-    e = p.dk == 128 ? launch_attn<128, false>(p, wq, wk, wv, grid, pairs, group, smem, stream)
-                    : launch_attn<64, false>(p, wq, wk, wv, grid, pairs, group, smem, stream);
+    e = p.dk == 128 ? launch_attn<128, false>(p, wq, wk, wv, grid, pairs, group, seg_ranges, smem, stream)
+                    : launch_attn<64, false>(p, wq, wk, wv, grid, pairs, group, seg_ranges, smem, stream);
   }
   if (e == cudaSuccess) count_launch(1);
   return e;
