@@ -40,10 +40,12 @@ enum {
 
 enum { TPA_DTYPE_F32 = 0, TPA_DTYPE_BF16 = 1 };
 
-/* Which kernel runs.  AUTO picks a tensor-core variant when the shape allows, else SIMT.
- * SM100 = tensor cores, variant chosen by the library; FUSED rebuilds Q/K/V from the factors
- * inside the attention kernel (no scratch); STAGED rebuilds every tile once into the
- * workspace with a staging kernel and then runs the attention kernel on those tiles. */
+/* Which kernel runs.  AUTO and SM100 pick the STAGED tensor-core variant when the shape allows
+ * (bf16, dk = dv in {64,128}, lengths % 128 == 0, heads % 8 == 0, 16-byte aligned operands),
+ * else SIMT.  STAGED rebuilds every tile once into the workspace with a staging kernel and then
+ * runs the attention kernel on those tiles; FUSED rebuilds Q/K/V from the factors inside the
+ * attention kernel (slower, but needs no scratch beyond the 256-byte status block and, with
+ * segment ids or key splits, a few KB). */
 enum {
   TPA_KERNEL_AUTO = 0,
   TPA_KERNEL_SIMT = 1,

@@ -374,7 +374,21 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
   }
   n_vis[0] = max(0, n_vis[0] - j0);
   n_vis[1] = max(0, n_vis[1] - j0);
+  // Key splits (gridDim.y > 1, few query rows against many keys): this CTA walks only its share
+  // of the tiles and leaves a partial (o, lse) in its own slice of the scratch that
+  // tpa_combine_splits_kernel merges; the host has set STATE_STORE and pointed state_o/lse there.
+  const int split = blockIdx.y;
+  if (gridDim.y > 1) {
+    const int chunk = (max(n_vis[0], n_vis[1]) + gridDim.y - 1) / gridDim.y;
+    const int begin = split * chunk;
+    j0 += begin;
+    n_vis[0] = min(max(0, n_vis[0] - begin), chunk);
+    n_vis[1] = min(max(0, n_vis[1] - begin), chunk);
+  }
   const int n_tiles = max(n_vis[0], n_vis[1]);
+  const int64_t split_rows = (int64_t)split * p.batch * p.lq * p.heads;
+  float* const st_o = p.state_o + split_rows * D;
+  float* const st_lse = p.state_lse + split_rows;
 
   if (threadIdx.x == 0) {
     // producers: one expect_tx arrival (STAGED) or one arrival per rebuild warp (FUSED)
@@ -453,13 +467,13 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
     if (load_state && live && n_u > 0) {
       // carried partial (tpa/ring_tpa.py:69-71): accumulator = o_prev (times R_k, see header),
       // row sum 1 (counted once, in half 0), maximum = previous LSE
-      const float prev = p.state_lse[rh];
+      const float prev = st_lse[rh];
       const bool has = prev != -CUDART_INF_F;
       if (has) {
         m = prev * kLog2e;
         l = half == 0 ? 1.f : 0.f;
       }
-      const float* so = p.state_o + rh * D + half * (D / 2);
+      const float* so = st_o + rh * D + half * (D / 2);
 #pragma unroll
       for (int c = 0; c < kOChunks; ++c) {
         uint32_t r[32];
@@ -630,13 +644,13 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
       float lse = empty ? -CUDART_INF_F : (m + log2f(l)) * kLn2;
       const bool passthrough = (n_u == 0) && load_state;  // nothing visible: carry the state over
       if (passthrough) {
-        lse = p.state_lse[rh];
+        lse = st_lse[rh];
         inv = 1.f;
       }
       const bool none = passthrough ? (lse == -CUDART_INF_F) : empty;
       __nv_bfloat16* orow = store_state ? nullptr
                                         : static_cast<__nv_bfloat16*>(p.o) + rh * D + half * (D / 2);
-      float* srow = (store_state || passthrough) ? p.state_o + rh * D + half * (D / 2) : nullptr;
+      float* srow = (store_state || passthrough) ? st_o + rh * D + half * (D / 2) : nullptr;
 #pragma unroll
       for (int c = 0; c < kOChunks; ++c) {
         uint32_t r[32];
@@ -673,7 +687,7 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
       }
       if (half == 0) {
         if (store_state) {
-          if (!passthrough) p.state_lse[rh] = lse;
+          if (!passthrough) st_lse[rh] = lse;
         } else if (p.lse != nullptr) {
           p.lse[rh] = lse;
         }
@@ -700,13 +714,13 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
     if (load_state && live && n_u > 0) {
       // carried partial (tpa/ring_tpa.py:69-71): accumulator = o_prev (times R_k, see header),
       // row sum 1, maximum = previous LSE
-      const float prev = p.state_lse[rh];
+      const float prev = st_lse[rh];
       const bool has = prev != -CUDART_INF_F;
       if (has) {
         m = prev * kLog2e;
         l = 1.f;
       }
-      const float* so = p.state_o + rh * D;
+      const float* so = st_o + rh * D;
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
         uint32_t r[32];
@@ -841,12 +855,12 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
       float lse = empty ? -CUDART_INF_F : (m + log2f(l)) * kLn2;
       const bool passthrough = (n_u == 0) && load_state;  // nothing visible: carry the state over
       if (passthrough) {
-        lse = p.state_lse[rh];
+        lse = st_lse[rh];
         inv = 1.f;
       }
       const bool none = passthrough ? (lse == -CUDART_INF_F) : empty;
       __nv_bfloat16* orow = store_state ? nullptr : static_cast<__nv_bfloat16*>(p.o) + rh * D;
-      float* srow = (store_state || passthrough) ? p.state_o + rh * D : nullptr;
+      float* srow = (store_state || passthrough) ? st_o + rh * D : nullptr;
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
         uint32_t r[32];
@@ -882,7 +896,7 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
         }
       }
       if (store_state) {
-        if (!passthrough) p.state_lse[rh] = lse;
+        if (!passthrough) st_lse[rh] = lse;
       } else if (p.lse != nullptr) {
         p.lse[rh] = lse;
       }
@@ -1016,6 +1030,50 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
   if (warp == 0) tmem_dealloc(tmem, 512);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Merges the partial (o, lse) of the key splits (and the caller's carried state, if loaded) the
+// way the ring merges steps (tpa/ring_tpa.py:82-91): weights exp(lse_i - max), normalised.
+// One thread per (row, head, 4 columns).
+__global__ void __launch_bounds__(256) tpa_combine_splits_kernel(const Params p, const float* part_o,
+                                                                 const float* part_lse, int splits) {
+  const int d = p.dv;
+  const int64_t rows = (int64_t)p.batch * p.lq * p.heads;
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= rows * (d / 4)) return;
+  const int64_t rh = idx / (d / 4);
+  const int c = (int)(idx % (d / 4)) * 4;
+  const bool load = (p.flags & TPA_FLAG_STATE_LOAD) != 0, store = (p.flags & TPA_FLAG_STATE_STORE) != 0;
+  float m = load ? p.state_lse[rh] : -CUDART_INF_F;
+  for (int s = 0; s < splits; ++s) m = fmaxf(m, part_lse[s * rows + rh]);
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  float wsum = 0.f;
+  auto add = [&](const float* o, float lse) {
+    if (lse == -CUDART_INF_F) return;
+    const float w = expf(lse - m);
+    const float4 v = *reinterpret_cast<const float4*>(o);
+    acc.x += w * v.x; acc.y += w * v.y; acc.z += w * v.z; acc.w += w * v.w;
+    wsum += w;
+  };
+  if (m != -CUDART_INF_F) {
+    if (load) add(p.state_o + rh * d + c, p.state_lse[rh]);
+    for (int s = 0; s < splits; ++s) add(part_o + (s * rows + rh) * d + c, part_lse[s * rows + rh]);
+  }
+  const bool none = !(wsum > 0.f);
+  const float inv = none ? 0.f : 1.f / wsum;
+  const float lse = none ? -CUDART_INF_F : m + logf(wsum);
+  if (store) {
+    *reinterpret_cast<float4*>(p.state_o + rh * d + c) = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+    if (c == 0) p.state_lse[rh] = lse;
+  } else {
+    const float q = none ? CUDART_NAN_F : 1.f;  // rows that saw no key are NaN (tpa/tpa.py:439)
+    uint2 o;
+    o.x = pack_bf16(acc.x * inv * q, acc.y * inv * q);
+    o.y = pack_bf16(acc.z * inv * q, acc.w * inv * q);
+    *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(p.o) + rh * d + c) = o;
+    if (c == 0 && p.lse != nullptr) p.lse[rh] = lse;
+  }
+}
+
 template <int D>
 constexpr size_t smem_bytes() {
   return 6 * (size_t)kUnitRows * D * 2 + sizeof(Barriers) + 1024;
@@ -1057,10 +1115,10 @@ bool sm100_supported(const Params& p) {
   return true;
 }
 
-// The staged variant pays for itself once more than one CTA per head walks the K/V tiles.
-int sm100_pick_variant(const Params& p) {
-  return p.lq > 2 * kUnitRows ? TPA_KERNEL_SM100_STAGED : TPA_KERNEL_SM100_FUSED;
-}
+// STAGED is the default whenever the shape allows a tensor-core kernel: measured against FUSED it
+// wins from 256 x 256 (45 vs 50 us) to 128 x 32768 (0.25 vs 0.61 ms) and T = 32768 (8.1 vs 36.8 ms).
+// FUSED stays selectable for callers that want no scratch at all.
+int sm100_pick_variant(const Params&) { return TPA_KERNEL_SM100_STAGED; }
 
 // one int4 per (batch, 256-row block) when segment ids are given
 inline size_t seg_range_bytes(const Params& p) {
@@ -1069,9 +1127,29 @@ inline size_t seg_range_bytes(const Params& p) {
   return align256((size_t)p.batch * pairs * sizeof(int4));
 }
 
+// Few 256-row blocks against many keys (decode-like, cross attention) would leave most SMs idle:
+// the key tiles are then split over several CTAs per block and the partials merged afterwards.
+constexpr int kNumSms = 148;
+int sm100_pick_splits(const Params& p) {
+  const int pairs = (p.lq + 2 * kUnitRows - 1) / (2 * kUnitRows);
+  const int64_t items = (int64_t)pairs * p.heads * p.batch;
+  const int n_kv = p.lk / kTileKv;
+  if (items * 2 > kNumSms || n_kv < 8) return 1;
+  int splits = (int)(kNumSms / items);
+  if (splits > n_kv / 4) splits = n_kv / 4;
+  if (splits > 16) splits = 16;
+  return splits < 2 ? 1 : splits;
+}
+inline size_t split_bytes(const Params& p) {
+  const int splits = sm100_pick_splits(p);
+  if (splits == 1) return 0;
+  return align256((size_t)splits * p.batch * p.lq * p.heads * (p.dv + 1) * sizeof(float));
+}
+
 size_t sm100_workspace_bytes(const Params& p, int variant) {
-  if (variant != TPA_KERNEL_SM100_STAGED) return seg_range_bytes(p);
-  return seg_range_bytes(p) + staged_q_bytes(p) + 2 * staged_kv_bytes(p);
+  const size_t common = seg_range_bytes(p) + split_bytes(p);
+  if (variant != TPA_KERNEL_SM100_STAGED) return common;
+  return common + staged_q_bytes(p) + 2 * staged_kv_bytes(p);
 }
 
 cudaError_t launch_sm100(const Params& p, int variant, void* workspace, TpaKernelInfo* info,
@@ -1090,7 +1168,8 @@ cudaError_t launch_sm100(const Params& p, int variant, void* workspace, TpaKerne
     const size_t per_slice = (size_t)p.lk * p.dk * 4;
     while (group > 1 && ((size_t)group * per_slice > ((size_t)72 << 20) || slices % group != 0)) --group;
   }
-  dim3 grid((unsigned)(pairs * slices), 1, 1);
+  const int splits = sm100_pick_splits(p);
+  dim3 grid((unsigned)(pairs * slices), (unsigned)splits, 1);
   if (info) {
     info->kernel = variant;
     info->block_q = 2 * kUnitRows;
@@ -1100,7 +1179,7 @@ cudaError_t launch_sm100(const Params& p, int variant, void* workspace, TpaKerne
     info->grid[1] = grid.y;
     info->grid[2] = grid.z;
     info->smem_bytes = (int)smem;
-    info->launches = (staged ? 2 : 1) + (p.q_seg != nullptr ? 1 : 0);
+    info->launches = (staged ? 2 : 1) + (p.q_seg != nullptr ? 1 : 0) + (splits > 1 ? 1 : 0);
   }
   if (dry_run) return cudaSuccess;
   cudaError_t e;
@@ -1112,9 +1191,20 @@ cudaError_t launch_sm100(const Params& p, int variant, void* workspace, TpaKerne
     if (e != cudaSuccess) return e;
     count_launch(1);
   }
+  // with key splits the attention kernel stores partials (as a ring step would) into scratch
+  Params pk = p;
+  float* part_o = nullptr;
+  float* part_lse = nullptr;
+  if (splits > 1) {
+    part_o = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + seg_range_bytes(p));
+    part_lse = part_o + (size_t)splits * p.batch * p.lq * p.heads * p.dv;
+    pk.flags = (p.flags & TPA_FLAG_CAUSAL) | TPA_FLAG_STATE_STORE;
+    pk.state_o = part_o;
+    pk.state_lse = part_lse;
+  }
   uint8_t *wq = nullptr, *wk = nullptr, *wv = nullptr;
   if (staged) {
-    wq = static_cast<uint8_t*>(workspace) + seg_range_bytes(p);
+    wq = static_cast<uint8_t*>(workspace) + seg_range_bytes(p) + split_bytes(p);
     wk = wq + staged_q_bytes(p);
     wv = wk + staged_kv_bytes(p);
     const float qscale = p.sm_scale * kLog2e / ((float)p.rank_q * (float)p.rank_k);
@@ -1128,13 +1218,20 @@ cudaError_t launch_sm100(const Params& p, int variant, void* workspace, TpaKerne
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     count_launch(1);
-    e = p.dk == 128 ? launch_attn<128, true>(p, wq, wk, wv, grid, pairs, group, seg_ranges, smem, stream)
-                    : launch_attn<64, true>(p, wq, wk, wv, grid, pairs, group, seg_ranges, smem, stream);
+    e = p.dk == 128 ? launch_attn<128, true>(pk, wq, wk, wv, grid, pairs, group, seg_ranges, smem, stream)
+                    : launch_attn<64, true>(pk, wq, wk, wv, grid, pairs, group, seg_ranges, smem, stream);
   } else {
-    e = p.dk == 128 ? launch_attn<128, false>(p, wq, wk, wv, grid, pairs, group, seg_ranges, smem, stream)
-                    : launch_attn<64, false>(p, wq, wk, wv, grid, pairs, group, seg_ranges, smem, stream);
+    e = p.dk == 128 ? launch_attn<128, false>(pk, wq, wk, wv, grid, pairs, group, seg_ranges, smem, stream)
+                    : launch_attn<64, false>(pk, wq, wk, wv, grid, pairs, group, seg_ranges, smem, stream);
   }
-  if (e == cudaSuccess) count_launch(1);
+  if (e != cudaSuccess) return e;
+  count_launch(1);
+  if (splits > 1) {
+    const int64_t threads = (int64_t)p.batch * p.lq * p.heads * (p.dv / 4);
+    tpa_combine_splits_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(p, part_o, part_lse, splits);
+    e = cudaGetLastError();
+    if (e == cudaSuccess) count_launch(1);
+  }
   return e;
 }
 

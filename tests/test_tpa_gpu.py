@@ -156,8 +156,7 @@ def test_sm100_small(d, t, causal, kernel):
     """Both tensor-core variants on one to a few tiles, all rows checked, LSE included."""
     q, k, v = orc.make_factors(50 + t + d, 2, t, t, 3, 2, 8, d, d)
     tq, tk, tv = dev(q, torch.bfloat16), dev(k, torch.bfloat16), dev(v, torch.bfloat16)
-    assert tpa_b200.tpa.query_kernel(tq, tk, tv, 8, causal=causal)["kernel"] == (
-        "sm100_staged" if t > 256 else "sm100_fused")
+    assert tpa_b200.tpa.query_kernel(tq, tk, tv, 8, causal=causal)["kernel"] == "sm100_staged"
     o, lse = tpa_b200.tpa.fwd_device(tq, tk, tv, 8, None, None, d**-0.5, causal, kernel=kernel)
     ref, lref = orc.tpa_reference_torch(tq.float().cpu(), tk.float().cpu(), tv.float().cpu(), 8,
                                         sm_scale=d**-0.5, causal=causal, return_lse=True)
@@ -279,3 +278,34 @@ def test_packed_sequences_walk_only_their_own_tiles(kernel, seg):
             return e0.elapsed_time(e1)
         one = dev(np.zeros((1, t), np.int32))
         assert run(ids) < 0.6 * run(one)
+
+
+@pytest.mark.parametrize("kernel", ["sm100_fused", "sm100_staged"])
+@pytest.mark.parametrize("lq,lk,h,causal", [(128, 4096, 8, False), (256, 8192, 16, True), (384, 2048, 8, True)])
+def test_few_queries_many_keys_split_over_ctas(kernel, lq, lk, h, causal):
+    """Decode-like / cross shapes: the key tiles are split over several CTAs per row block and the
+    partials merged (one more launch); with and without carried state; against the oracle."""
+    d = 128
+    q, k, v = orc.make_factors(91, 1, max(lq, lk), max(lq, lk), 2, 2, h, d, d)
+    tq, tk, tv = dev(q[:, :lq], torch.bfloat16), dev(k[:, :lk], torch.bfloat16), dev(v[:, :lk], torch.bfloat16)
+    q_off = lk - lq if causal else 0  # the queries are the last rows of the sequence
+    info = tpa_b200.tpa.query_kernel(tq, tk, tv, h, kernel=kernel, causal=causal)
+    assert info["grid"][1] > 1, info  # really split
+    n0 = _capi.lib.tpa_launch_count()
+    o, lse = tpa_b200.tpa.fwd_device(tq, tk, tv, h, None, None, d**-0.5, causal, q_offset=q_off, kernel=kernel)
+    torch.cuda.synchronize()
+    assert _capi.lib.tpa_launch_count() - n0 == info["launches"]
+    ref, lref = orc.tpa_reference_torch(tq.float().cpu(), tk.float().cpu(), tv.float().cpu(), h, sm_scale=d**-0.5,
+                                        causal=causal, q_offset=q_off, return_lse=True)
+    diff = (o.float().cpu() - ref).abs()
+    assert diff.max() <= 2e-2 and diff.mean() <= 5e-3
+    assert (lse.cpu() - lref).abs().max() <= 1e-2
+    # two halves of the keys chained through the carried state give the same answer
+    half = lk // 2
+    state = (torch.empty(1, lq, h, d, device="cuda"), torch.empty(1, lq, h, device="cuda"))
+    tpa_b200.tpa.fwd_device(tq, tk[:, :half], tv[:, :half], h, None, None, d**-0.5, causal, q_offset=q_off,
+                            state=state, store_state=True, kernel=kernel)
+    o2, _ = tpa_b200.tpa.fwd_device(tq, tk[:, half:], tv[:, half:], h, None, None, d**-0.5, causal, q_offset=q_off,
+                                    k_offset=half, state=state, load_state=True, kernel=kernel)
+    d2 = (o2.float().cpu() - ref).abs()
+    assert d2.max() <= 2e-2 and d2.mean() <= 5e-3
