@@ -41,7 +41,8 @@ enum {
 enum { TPA_DTYPE_F32 = 0, TPA_DTYPE_BF16 = 1 };
 
 /* Which kernel runs.  AUTO and SM100 pick the STAGED tensor-core variant when the shape allows
- * (bf16, dk = dv in {64,128}, lengths % 128 == 0, heads % 8 == 0, 16-byte aligned operands),
+ * (bf16, dk = dv in {64,128}, any lengths, heads % 8 == 0, 16-byte aligned operands; with
+ * segment ids lk % 4 == 0),
  * else SIMT.  STAGED rebuilds every tile once into the workspace with a staging kernel and then
  * runs the attention kernel on those tiles; FUSED rebuilds Q/K/V from the factors inside the
  * attention kernel (slower, but needs no scratch beyond the 256-byte status block and, with

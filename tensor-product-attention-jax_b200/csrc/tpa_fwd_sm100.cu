@@ -137,8 +137,8 @@ template <int D>
 __device__ __forceinline__ void rebuild_tile(uint8_t* dst, const __nv_bfloat16* a,
                                              int64_t a_row, int64_t a_rank,
                                              const __nv_bfloat16* b, int64_t b_row, int64_t b_rank,
-                                             int rank, int64_t row0, float scale, int tid,
-                                             int nthreads) {
+                                             int rank, int64_t row0, int64_t row_end, float scale,
+                                             int tid, int nthreads) {
   constexpr int CH = D / 8;  // 16-byte chunks per row
   const int chunk = tid % CH;
   const int rows_per_pass = nthreads / CH;
@@ -153,8 +153,9 @@ __device__ __forceinline__ void rebuild_tile(uint8_t* dst, const __nv_bfloat16* 
     float acc[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+    const int nr = g < row_end ? rank : 0;  // rows past the end of a ragged last tile stay zero
 #pragma unroll 4
-    for (int r = 0; r < rank; ++r) {
+    for (int r = 0; r < nr; ++r) {
       const uint4 bv = __ldg(reinterpret_cast<const uint4*>(bp + r * b_rank));
       const float av = __bfloat162float(ap[r * a_rank]);
       const uint32_t w[4] = {bv.x, bv.y, bv.z, bv.w};
@@ -185,20 +186,20 @@ __global__ void __launch_bounds__(256) tpa_stage_tiles_kernel(const Params p, ui
                                                               float qscale, int first_tile) {
   constexpr int CH = D / 8;
   constexpr int kTileBytes = kUnitRows * D * 2;
-  const int nq = p.lq / kUnitRows, nk = p.lk / kTileKv;
+  const int nq = (p.lq + kUnitRows - 1) / kUnitRows, nk = (p.lk + kTileKv - 1) / kTileKv;
   int tile = blockIdx.y + first_tile;  // first_tile = lq/128 skips the Q tiles (already staged)
   const TpaFactor *fa, *fb;
   uint8_t* ws;
-  int rank, ntiles;
+  int rank, ntiles, length;
   float scale;
   if (tile < nq) {
-    fa = &p.qa; fb = &p.qb; ws = ws_q; rank = p.rank_q; ntiles = nq; scale = qscale;
+    fa = &p.qa; fb = &p.qb; ws = ws_q; rank = p.rank_q; ntiles = nq; scale = qscale; length = p.lq;
   } else if (tile < nq + nk) {
     tile -= nq;
-    fa = &p.ka; fb = &p.kb; ws = ws_k; rank = p.rank_k; ntiles = nk; scale = 1.f;
+    fa = &p.ka; fb = &p.kb; ws = ws_k; rank = p.rank_k; ntiles = nk; scale = 1.f; length = p.lk;
   } else {
     tile -= nq + nk;
-    fa = &p.va; fb = &p.vb; ws = ws_v; rank = p.rank_k; ntiles = nk; scale = 1.f;
+    fa = &p.va; fb = &p.vb; ws = ws_v; rank = p.rank_k; ntiles = nk; scale = 1.f; length = p.lk;
   }
   const int hg = blockIdx.x, batch = blockIdx.z;
   const __nv_bfloat16* a = static_cast<const __nv_bfloat16*>(fa->ptr) + batch * fa->stride[0] + hg * 8;
@@ -216,7 +217,8 @@ __global__ void __launch_bounds__(256) tpa_stage_tiles_kernel(const Params p, ui
 #pragma unroll
       for (int e = 0; e < 8; ++e) acc[h][e] = 0.f;
     // four ranks at a time: their eight 16-byte loads are issued before any of the FMAs
-    for (int r0 = 0; r0 < rank; r0 += 4) {
+    // rows past the end of a ragged last tile stay zero (the attention kernel masks them)
+    for (int r0 = 0; r0 < (g < length ? rank : 0); r0 += 4) {
       uint4 bv[4], av[4];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -271,7 +273,7 @@ __global__ void __launch_bounds__(128) tpa_seg_ranges_kernel(const Params p, int
   const int pair = blockIdx.x, batch = blockIdx.y, t = threadIdx.x;
   const int32_t* qs = p.q_seg + (int64_t)batch * p.q_seg_bstride;
   const int32_t* ks = p.kv_seg + (int64_t)batch * p.kv_seg_bstride;
-  const int n_kv = p.lk / kTileKv;
+  const int n_kv = (p.lk + kTileKv - 1) / kTileKv;
   int lo[2], hi[2];
 #pragma unroll
   for (int u = 0; u < 2; ++u) {
@@ -293,7 +295,8 @@ __global__ void __launch_bounds__(128) tpa_seg_ranges_kernel(const Params p, int
   for (int tile = t; tile < n_kv; tile += 128) {
     const int4* src = reinterpret_cast<const int4*>(ks + (int64_t)tile * kTileKv);
     int kmin = INT_MAX, kmax = INT_MIN;
-    for (int i = 0; i < kTileKv / 4; ++i) {
+    const int n4 = min(kTileKv, p.lk - tile * kTileKv) / 4;  // lk % 4 == 0
+    for (int i = 0; i < n4; ++i) {
       const int4 v = __ldg(src + i);
       kmin = min(kmin, min(min(v.x, v.y), min(v.z, v.w)));
       kmax = max(kmax, max(max(v.x, v.y), max(v.z, v.w)));
@@ -348,7 +351,7 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
   const bool store_state = (p.flags & TPA_FLAG_STATE_STORE) != 0;
 
   // number of key tiles each unit can see (tpa/tpa.py:427-431, with global offsets)
-  const int n_kv = p.lk / kTileKv;
+  const int n_kv = (p.lk + kTileKv - 1) / kTileKv;
   int n_vis[2];
 #pragma unroll
   for (int u = 0; u < 2; ++u) {
@@ -437,14 +440,15 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
     const int n_u = n_vis[u];
     const int q0u = q0 + u * kUnitRows;
     const int grow = q0u + row;
-    const bool live = q0u < p.lq;
+    const bool live = q0u < p.lq;      // the unit exists
+    const bool row_ok = grow < p.lq;   // this thread's row exists (the last unit may be ragged)
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     const uint32_t tS = tmem + lane_base + u * 128;
     const uint32_t tSh = tS + half * 64;                        // this thread's 64 logits
     const uint32_t tOh = tmem + lane_base + kOCol + u * D + half * (D / 2);  // its D/2 accumulators
-    const int64_t rh = live ? ((int64_t)batch * p.lq + grow) * p.heads + head : 0;
+    const int64_t rh = row_ok ? ((int64_t)batch * p.lq + grow) * p.heads + head : 0;
     const int64_t qpos = (int64_t)grow + p.q_offset;
-    const int qseg = (has_seg && live) ? p.q_seg[(int64_t)batch * p.q_seg_bstride + grow] : 0;
+    const int qseg = (has_seg && row_ok) ? p.q_seg[(int64_t)batch * p.q_seg_bstride + grow] : 0;
     const float rk = (float)p.rank_k;
     constexpr int kOChunks = D / 64;  // 32-column chunks of the accumulator this thread owns
 
@@ -467,7 +471,7 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
     if (load_state && live && n_u > 0) {
       // carried partial (tpa/ring_tpa.py:69-71): accumulator = o_prev (times R_k, see header),
       // row sum 1 (counted once, in half 0), maximum = previous LSE
-      const float prev = st_lse[rh];
+      const float prev = row_ok ? st_lse[rh] : -CUDART_INF_F;
       const bool has = prev != -CUDART_INF_F;
       if (has) {
         m = prev * kLog2e;
@@ -496,6 +500,7 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
       tc_fence_after();
       const int k0 = (j0 + j) * kTileKv + half * 64;  // first key of this thread's columns
       const bool diag = causal && ((int64_t)k0 + 63 + p.k_offset > (int64_t)q0u + p.q_offset);
+      const bool tail = k0 + 63 >= p.lk;  // columns past the last key (zero rows in the staged tile)
       // Segment ids: when every key of these 64 columns and every row of this warp carry the
       // same id, nothing is masked and the element-wise test is skipped (warp-uniform).
       const int32_t* ks = bars->kseg[j & 1] + half * 64;
@@ -507,14 +512,14 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
         const int kmax = __reduce_max_sync(0xffffffffu, max(k2.x, k2.y));
         seg_mask = !__all_sync(0xffffffffu, kmin == kmax && qseg == kmin);
       }
-      const bool masked = diag || seg_mask;
+      const bool masked = diag || seg_mask || tail;
 
       auto mask_chunk = [&](uint32_t(&r)[32], int c) {
 #pragma unroll
         for (int e = 0; e < 32; ++e) {
           const int kc = k0 + c * 32 + e;
-          bool keep = true;
-          if (diag) keep = qpos >= (int64_t)kc + p.k_offset;
+          bool keep = kc < p.lk;
+          if (diag) keep = keep && qpos >= (int64_t)kc + p.k_offset;
           if (seg_mask) keep = keep && (qseg == ks[c * 32 + e]);
           if (!keep) r[e] = 0xff800000u;  // -inf
         }
@@ -644,7 +649,7 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
       float lse = empty ? -CUDART_INF_F : (m + log2f(l)) * kLn2;
       const bool passthrough = (n_u == 0) && load_state;  // nothing visible: carry the state over
       if (passthrough) {
-        lse = st_lse[rh];
+        lse = row_ok ? st_lse[rh] : -CUDART_INF_F;
         inv = 1.f;
       }
       const bool none = passthrough ? (lse == -CUDART_INF_F) : empty;
@@ -668,7 +673,7 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
             for (int e = 0; e < 32; e += 4) {
               float4 v = make_float4(__uint_as_float(r[e]) * inv, __uint_as_float(r[e + 1]) * inv,
                                      __uint_as_float(r[e + 2]) * inv, __uint_as_float(r[e + 3]) * inv);
-              *reinterpret_cast<float4*>(srow + c * 32 + e) = v;
+              if (row_ok) *reinterpret_cast<float4*>(srow + c * 32 + e) = v;
             }
           }
         } else {
@@ -681,11 +686,11 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
               const float x1 = none ? CUDART_NAN_F : __uint_as_float(r[e + 2 * k + 1]) * inv;
               w[k] = pack_bf16(x0, x1);
             }
-            *reinterpret_cast<uint4*>(orow + c * 32 + e) = make_uint4(w[0], w[1], w[2], w[3]);
+            if (row_ok) *reinterpret_cast<uint4*>(orow + c * 32 + e) = make_uint4(w[0], w[1], w[2], w[3]);
           }
         }
       }
-      if (half == 0) {
+      if (half == 0 && row_ok) {
         if (store_state) {
           if (!passthrough) st_lse[rh] = lse;
         } else if (p.lse != nullptr) {
@@ -700,13 +705,14 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
     const int n_u = n_vis[u];
     const int q0u = q0 + u * kUnitRows;
     const int grow = q0u + row;
-    const bool live = q0u < p.lq;
+    const bool live = q0u < p.lq;      // the unit exists
+    const bool row_ok = grow < p.lq;   // this thread's row exists (the last unit may be ragged)
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t tS = tmem + lane_base + u * 128;
     const uint32_t tO = tmem + lane_base + kOCol + u * D;
-    const int64_t rh = live ? ((int64_t)batch * p.lq + grow) * p.heads + head : 0;
+    const int64_t rh = row_ok ? ((int64_t)batch * p.lq + grow) * p.heads + head : 0;
     const int64_t qpos = (int64_t)grow + p.q_offset;
-    const int qseg = (has_seg && live) ? p.q_seg[(int64_t)batch * p.q_seg_bstride + grow] : 0;
+    const int qseg = (has_seg && row_ok) ? p.q_seg[(int64_t)batch * p.q_seg_bstride + grow] : 0;
     const float rk = (float)p.rank_k;
 
     float m = -CUDART_INF_F, l = 0.f;
@@ -714,7 +720,7 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
     if (load_state && live && n_u > 0) {
       // carried partial (tpa/ring_tpa.py:69-71): accumulator = o_prev (times R_k, see header),
       // row sum 1, maximum = previous LSE
-      const float prev = st_lse[rh];
+      const float prev = row_ok ? st_lse[rh] : -CUDART_INF_F;
       const bool has = prev != -CUDART_INF_F;
       if (has) {
         m = prev * kLog2e;
@@ -743,6 +749,7 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
       tc_fence_after();
       const int k0 = (j0 + j) * kTileKv;
       const bool diag = causal && ((int64_t)k0 + kTileKv - 1 + p.k_offset > (int64_t)q0u + p.q_offset);
+      const bool tail = k0 + kTileKv - 1 >= p.lk;  // columns past the last key
       // Segment ids: when every key of the tile and every row of this warp carry the same
       // id, nothing is masked and the element-wise test is skipped (warp-uniform decision).
       const int32_t* ks = bars->kseg[j & 1];
@@ -754,7 +761,7 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
         const int kmax = __reduce_max_sync(0xffffffffu, max(max(k4.x, k4.y), max(k4.z, k4.w)));
         seg_mask = !__all_sync(0xffffffffu, kmin == kmax && qseg == kmin);
       }
-      const bool masked = diag || seg_mask;
+      const bool masked = diag || seg_mask || tail;
 
       // pass 1: row maximum of the (masked) logits; they are already in log2 units
       float tmax = -CUDART_INF_F;
@@ -767,8 +774,8 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
 #pragma unroll
           for (int e = 0; e < 32; ++e) {
             const int kc = k0 + c * 32 + e;
-            bool keep = true;
-            if (diag) keep = qpos >= (int64_t)kc + p.k_offset;
+            bool keep = kc < p.lk;
+            if (diag) keep = keep && qpos >= (int64_t)kc + p.k_offset;
             if (seg_mask) keep = keep && (qseg == ks[c * 32 + e]);
             if (keep) tmax = fmaxf(tmax, __uint_as_float(r[e]));
           }
@@ -819,10 +826,10 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
             float s0 = __uint_as_float(r[e]), s1 = __uint_as_float(r[e + 1]);
             if (masked) {
               const int kc = k0 + c * 32 + e;
-              bool keep0 = true, keep1 = true;
+              bool keep0 = kc < p.lk, keep1 = kc + 1 < p.lk;
               if (diag) {
-                keep0 = qpos >= (int64_t)kc + p.k_offset;
-                keep1 = qpos >= (int64_t)kc + 1 + p.k_offset;
+                keep0 = keep0 && qpos >= (int64_t)kc + p.k_offset;
+                keep1 = keep1 && qpos >= (int64_t)kc + 1 + p.k_offset;
               }
               if (seg_mask) {
                 keep0 = keep0 && (qseg == ks[c * 32 + e]);
@@ -855,7 +862,7 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
       float lse = empty ? -CUDART_INF_F : (m + log2f(l)) * kLn2;
       const bool passthrough = (n_u == 0) && load_state;  // nothing visible: carry the state over
       if (passthrough) {
-        lse = st_lse[rh];
+        lse = row_ok ? st_lse[rh] : -CUDART_INF_F;
         inv = 1.f;
       }
       const bool none = passthrough ? (lse == -CUDART_INF_F) : empty;
@@ -878,7 +885,7 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
             for (int e = 0; e < 32; e += 4) {
               float4 v = make_float4(__uint_as_float(r[e]) * inv, __uint_as_float(r[e + 1]) * inv,
                                      __uint_as_float(r[e + 2]) * inv, __uint_as_float(r[e + 3]) * inv);
-              *reinterpret_cast<float4*>(srow + c * 32 + e) = v;
+              if (row_ok) *reinterpret_cast<float4*>(srow + c * 32 + e) = v;
             }
           }
         } else {
@@ -891,11 +898,12 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
               const float x1 = none ? CUDART_NAN_F : __uint_as_float(r[e + 2 * k + 1]) * inv;
               w[k] = pack_bf16(x0, x1);
             }
-            *reinterpret_cast<uint4*>(orow + c * 32 + e) = make_uint4(w[0], w[1], w[2], w[3]);
+            if (row_ok) *reinterpret_cast<uint4*>(orow + c * 32 + e) = make_uint4(w[0], w[1], w[2], w[3]);
           }
         }
       }
-      if (store_state) {
+      if (!row_ok) {
+      } else if (store_state) {
         if (!passthrough) st_lse[rh] = lse;
       } else if (p.lse != nullptr) {
         p.lse[rh] = lse;
@@ -907,7 +915,7 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
     // ------------------------------------------------------------------ bulk copies of staged tiles
     if (lane == 0) {
       const int64_t bh = (int64_t)batch * p.heads + head;
-      const uint8_t* gq = ws_q + (bh * (p.lq / kUnitRows) + pair * 2) * kTileBytes;
+      const uint8_t* gq = ws_q + (bh * ((p.lq + kUnitRows - 1) / kUnitRows) + pair * 2) * kTileBytes;
       const uint8_t* gk = ws_k + bh * n_kv * kTileBytes;
       const uint8_t* gv = ws_v + bh * n_kv * kTileBytes;
       const int units = (q0 + kUnitRows < p.lq) ? 2 : 1;
@@ -919,11 +927,13 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
         mbar_arrive_expect_tx(&bars->k_full[s], kTileBytes);
         bulk_g2s(sK + s * kTileBytes, gk + (int64_t)(j0 + j) * kTileBytes, kTileBytes, &bars->k_full[s]);
         if (j >= 2) wait(&bars->v_empty[s], ((j >> 1) - 1) & 1, 0x500);
-        mbar_arrive_expect_tx(&bars->v_full[s], kTileBytes + (has_seg ? kTileKv * 4 : 0));
+        // ids of a ragged last tile: only the keys that exist (lk % 4 == 0, so 16-byte multiples)
+        const int n_ids = min(kTileKv, p.lk - (j0 + j) * kTileKv);
+        mbar_arrive_expect_tx(&bars->v_full[s], kTileBytes + (has_seg ? n_ids * 4 : 0));
         bulk_g2s(sV + s * kTileBytes, gv + (int64_t)(j0 + j) * kTileBytes, kTileBytes, &bars->v_full[s]);
         if (has_seg)
           bulk_g2s(bars->kseg[s], p.kv_seg + (int64_t)batch * p.kv_seg_bstride + (int64_t)(j0 + j) * kTileKv,
-                   kTileKv * 4, &bars->v_full[s]);
+                   n_ids * 4, &bars->v_full[s]);
       }
     }
     __syncwarp();
@@ -934,7 +944,7 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
     for (int u = 0; u < 2; ++u) {
       if (q0 + u * kUnitRows < p.lq)
         rebuild_tile<D>(sQ + u * kTileBytes, qa, p.qa.stride[1], p.qa.stride[2], qb, p.qb.stride[1],
-                        p.qb.stride[2], p.rank_q, q0 + u * kUnitRows, qscale, rt, kRebuildWarps * 32);
+                        p.qb.stride[2], p.rank_q, q0 + u * kUnitRows, p.lq, qscale, rt, kRebuildWarps * 32);
     }
     fence_async_smem();
     __syncwarp();
@@ -953,9 +963,11 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
       const int s = j & 1;
       if (j >= 2) wait(&empty[s], ((j >> 1) - 1) & 1, is_k ? 0x400 : 0x500);
       rebuild_tile<D>(stages + s * kTileBytes, fa, sa.stride[1], sa.stride[2], fb, sb.stride[1],
-                      sb.stride[2], p.rank_k, (int64_t)(j0 + j) * kTileKv, 1.f, t, kRebuildWarps * 16);
+                      sb.stride[2], p.rank_k, (int64_t)(j0 + j) * kTileKv, p.lk, 1.f, t, kRebuildWarps * 16);
       if (!is_k && has_seg)
-        bars->kseg[s][t] = p.kv_seg[(int64_t)batch * p.kv_seg_bstride + (int64_t)(j0 + j) * kTileKv + t];
+        bars->kseg[s][t] = ((j0 + j) * kTileKv + t < p.lk)
+                               ? p.kv_seg[(int64_t)batch * p.kv_seg_bstride + (int64_t)(j0 + j) * kTileKv + t]
+                               : 0;
       fence_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(&full[s]);
@@ -1084,8 +1096,9 @@ inline bool factor_vec_ok(const TpaFactor& f) {
   return aligned16(f.ptr) && f.stride[0] % 8 == 0 && f.stride[1] % 8 == 0 && f.stride[2] % 8 == 0;
 }
 inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
-inline size_t staged_q_bytes(const Params& p) { return align256((size_t)p.batch * p.heads * p.lq * p.dk * 2); }
-inline size_t staged_kv_bytes(const Params& p) { return align256((size_t)p.batch * p.heads * p.lk * p.dk * 2); }
+inline size_t ceil128(size_t x) { return (x + 127) / 128 * 128; }  // whole tiles are staged
+inline size_t staged_q_bytes(const Params& p) { return align256((size_t)p.batch * p.heads * ceil128(p.lq) * p.dk * 2); }
+inline size_t staged_kv_bytes(const Params& p) { return align256((size_t)p.batch * p.heads * ceil128(p.lk) * p.dk * 2); }
 
 template <int D, bool STAGED>
 cudaError_t launch_attn(const Params& p, const uint8_t* wq, const uint8_t* wk, const uint8_t* wv,
@@ -1103,7 +1116,9 @@ cudaError_t launch_attn(const Params& p, const uint8_t* wq, const uint8_t* wk, c
 bool sm100_supported(const Params& p) {
   if (p.dtype != TPA_DTYPE_BF16) return false;
   if (p.dk != p.dv || (p.dk != 64 && p.dk != 128)) return false;
-  if (p.lq % kUnitRows != 0 || p.lk % kTileKv != 0) return false;
+  // lengths need not be multiples of the 128-row tiles: ragged last tiles are zero-padded and
+  // masked.  Key ids travel as 16-byte multiples.
+  if (p.kv_seg != nullptr && p.lk % 4 != 0) return false;
   if (p.heads % 8 != 0) return false;
   // factors are read with 16-byte loads; output rows are written with them
   if (!factor_vec_ok(p.qa) || !factor_vec_ok(p.ka) || !factor_vec_ok(p.va)) return false;
@@ -1133,7 +1148,7 @@ constexpr int kNumSms = 148;
 int sm100_pick_splits(const Params& p) {
   const int pairs = (p.lq + 2 * kUnitRows - 1) / (2 * kUnitRows);
   const int64_t items = (int64_t)pairs * p.heads * p.batch;
-  const int n_kv = p.lk / kTileKv;
+  const int n_kv = (p.lk + kTileKv - 1) / kTileKv;
   if (items * 2 > kNumSms || n_kv < 8) return 1;
   int splits = (int)(kNumSms / items);
   if (splits > n_kv / 4) splits = n_kv / 4;
@@ -1209,8 +1224,9 @@ cudaError_t launch_sm100(const Params& p, int variant, void* workspace, TpaKerne
     wv = wk + staged_kv_bytes(p);
     const float qscale = p.sm_scale * kLog2e / ((float)p.rank_q * (float)p.rank_k);
     // ring steps after the first keep the Q tiles the previous call staged in this workspace
-    const int first_tile = (p.flags & TPA_FLAG_REUSE_STAGED_Q) ? p.lq / kUnitRows : 0;
-    dim3 sgrid(p.heads / 8, p.lq / kUnitRows - first_tile + 2 * (p.lk / kTileKv), p.batch);
+    const int nq = (p.lq + kUnitRows - 1) / kUnitRows, nk = (p.lk + kTileKv - 1) / kTileKv;
+    const int first_tile = (p.flags & TPA_FLAG_REUSE_STAGED_Q) ? nq : 0;
+    dim3 sgrid(p.heads / 8, nq - first_tile + 2 * nk, p.batch);
     if (p.dk == 128)
       tpa_stage_tiles_kernel<128><<<sgrid, 256, 0, stream>>>(p, wq, wk, wv, qscale, first_tile);
     else

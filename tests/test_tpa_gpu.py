@@ -309,3 +309,33 @@ def test_few_queries_many_keys_split_over_ctas(kernel, lq, lk, h, causal):
                                     k_offset=half, state=state, load_state=True, kernel=kernel)
     d2 = (o2.float().cpu() - ref).abs()
     assert d2.max() <= 2e-2 and d2.mean() <= 5e-3
+
+
+@pytest.mark.parametrize("kernel", ["sm100_fused", "sm100_staged"])
+@pytest.mark.parametrize("lq,lk,seg,causal", [(1, 1000, 0, True), (100, 333, 0, False), (200, 520, 64, True),
+                                              (385, 129, 0, True), (7, 4096, 0, True), (130, 8200, 300, False)])
+def test_ragged_lengths_on_tensor_cores(kernel, lq, lk, seg, causal):
+    """Lengths that are not multiples of the 128-row tiles (decode: a single query row): padded
+    rows and keys must not leak into results; against the generic kernel and the oracle."""
+    h, d = 8, 128
+    q, k, v = orc.make_factors(300 + lq, 2, lq, lk, 3, 2, h, d, d)
+    tq, tk, tv = dev(q, torch.bfloat16), dev(k, torch.bfloat16), dev(v, torch.bfloat16)
+    qs = dev(orc.segment_ids(2, lq, seg)) if seg else None
+    ks = dev(orc.segment_ids(2, lk, seg)) if seg else None
+    q_off = max(lk - lq, 0) if causal else 0
+    assert tpa_b200.tpa.query_kernel(tq, tk, tv, h, kernel=kernel, causal=causal, segments=bool(seg))["kernel"] == kernel
+    # the output sits inside a larger buffer whose surrounding rows must stay untouched
+    big = torch.full((2, lq + 2, h, d), 7.0, dtype=torch.bfloat16, device="cuda")
+    canary = big.clone()
+    o, lse = tpa_b200.tpa.fwd_device(tq, tk, tv, h, qs, ks, d**-0.5, causal, q_offset=q_off, kernel=kernel)
+    want, wl = tpa_b200.tpa.fwd_device(tq, tk, tv, h, qs, ks, d**-0.5, causal, q_offset=q_off, kernel="simt")
+    ref = orc.tpa_reference_torch(tq.float().cpu(), tk.float().cpu(), tv.float().cpu(), h,
+                                  None if qs is None else qs.cpu(), None if ks is None else ks.cpu(),
+                                  sm_scale=d**-0.5, causal=causal, q_offset=q_off)
+    assert torch.equal(big, canary)
+    assert torch.equal(torch.isnan(o), torch.isnan(want))
+    ok = ~torch.isnan(ref)
+    diff = (o.float().cpu() - ref)[ok].abs()
+    assert diff.max() <= 2e-2 and diff.mean() <= 5e-3, (float(diff.max()), float(diff.mean()))
+    fin = ~torch.isinf(wl)
+    assert ((lse - wl)[fin].abs() <= 2e-2).all()
