@@ -179,6 +179,70 @@ def tpa_reference(
     return o
 
 
+def tpa_bwd_reference(
+    q,
+    k,
+    v,
+    do,
+    num_heads,
+    q_segment_ids=None,
+    kv_segment_ids=None,
+    sm_scale=1.0,
+    causal=False,
+    dtype=np.float64,
+    q_offset=0,
+    k_offset=0,
+):
+    """Gradients of `tpa_reference` with respect to the concatenated factors, given `do`.
+
+    Follows the materialising branch of the backward kernel (tpa/tpa.py:777-799):
+    p = exp(x - lse) with NaN -> 0 (tpa/tpa.py:676-677), delta = nansum(o * do)
+    (tpa/tpa.py:976-980), ds = p (do v^T - delta) sm_scale, dq = ds k, dk = ds^T q,
+    dv = p^T do, and the factor contraction da = dX b / R, db = dX a / R
+    (tpa/tpa.py:779-781, 789-791, 796-799).  A query row that sees no key has p = 0 and a
+    NaN-free delta, so it contributes nothing, here as there.  Two deliberate differences,
+    both outside what the reference's own tests execute (tpa/tpa_test.py:128-205 is
+    non-causal with at most two heads):
+      * db sums over ALL heads.  The reference's program for head block i overwrites the
+        db block written by head block i-1 (tpa/tpa.py:929,933 ignore the head index),
+        which is only right while num_heads <= block_h.
+      * the causal trip count of the reference (tpa/tpa.py:811-812) is not followed; the
+        mask itself defines which pairs contribute.
+    Pinned by tests/golden/bwd_matrix.npz: the reference's own _tpa_bwd executed on the
+    24 shapes of its backward test.
+    Returns (dq, dk, dv) shaped like q, k, v.
+    """
+    qa, qb = split_factors(np.asarray(q, dtype), num_heads)
+    ka, kb = split_factors(np.asarray(k, dtype), num_heads)
+    va, vb = split_factors(np.asarray(v, dtype), num_heads)
+    do = np.asarray(do, dtype)
+    rq, rk = qa.shape[2], ka.shape[2]
+    q_, k_, v_ = materialize(q, k, v, num_heads, dtype)
+    b, lq = q_.shape[:2]
+    lk = k_.shape[1]
+    x = np.einsum("bqhd,bkhd->bhqk", q_, k_) * dtype(sm_scale)
+    keep = _mask(b, lq, lk, q_segment_ids, kv_segment_ids, causal, q_offset, k_offset)
+    x = np.where(keep[:, None], x, -np.inf)
+    with np.errstate(invalid="ignore", divide="ignore"):
+        l = lse(x)[..., None]  # [b, h, lq, 1]
+        p = np.exp(x - l)
+    p = np.where(np.isnan(p), 0.0, p)
+    o = np.einsum("bhqk,bkhd->bqhd", p, v_)
+    delta = np.einsum("bqhd,bqhd->bhq", o, do)[..., None]
+    dp = np.einsum("bqhd,bkhd->bhqk", do, v_) - delta
+    ds = p * dp * dtype(sm_scale)
+    dq_ = np.einsum("bhqk,bkhd->bqhd", ds, k_)
+    dk_ = np.einsum("bhqk,bqhd->bkhd", ds, q_)
+    dv_ = np.einsum("bhqk,bqhd->bkhd", p, do)
+
+    def contract(dx, a, bf, rank):
+        da = np.einsum("blhd,blrd->blrh", dx, bf) / rank
+        db = np.einsum("blhd,blrh->blrd", dx, a) / rank
+        return np.concatenate([da, db], axis=-1)
+
+    return contract(dq_, qa, qb, rq), contract(dk_, ka, kb, rk), contract(dv_, va, vb, rk)
+
+
 # --------------------------------------------------------------------------- (ii) block-wise kernel semantics
 
 

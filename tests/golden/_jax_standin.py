@@ -1,4 +1,4 @@
-"""A numpy stand-in for the slice of the jax API the reference's forward path touches.
+"""A numpy stand-in for the slice of the jax API the reference's forward and backward paths touch.
 
 Purpose: the golden fixtures in this folder must come from the reference's own
 source, but jax is not installed where they are generated.  Installing this
@@ -56,20 +56,18 @@ def _tree_map(f, tree):
 
 
 def vmap(fn, in_axes=0, out_axes=0):
-    assert out_axes == 0
-
     def wrapped(*args, **kwargs):
         axes = in_axes if isinstance(in_axes, (list, tuple)) else [in_axes] * len(args)
-        n = next(a.shape[0] for a, ax in zip(args, axes) if ax is not None)
+        n = next(a.shape[ax] for a, ax in zip(args, axes) if ax is not None)
         outs = []
         for i in range(n):
-            sl = [a[i] if ax is not None else a for a, ax in zip(args, axes)]
+            sl = [np.take(a, i, axis=ax) if ax is not None else a for a, ax in zip(args, axes)]
             kw = {key: val[i] for key, val in kwargs.items()}  # keyword operands map over axis 0
             outs.append(fn(*sl, **kw))
         first = outs[0]
         if isinstance(first, (list, tuple)):
-            return type(first)(np.stack([o[j] for o in outs]) for j in range(len(first)))
-        return np.stack(outs)
+            return type(first)(np.stack([o[j] for o in outs], axis=out_axes) for j in range(len(first)))
+        return np.stack(outs, axis=out_axes)
 
     return wrapped
 
@@ -200,9 +198,23 @@ def _block_view(arr, spec, pid):
     return arr[sl]
 
 
-def pallas_call(kernel, grid, in_specs, out_specs, out_shape, **_):
+def atomic_add(ref, idx, val):
+    # programs run one after another here, so a plain read-modify-write is the atomic add
+    ref[idx] += val
+
+
+def pallas_call(kernel, grid, in_specs, out_specs, out_shape, input_output_aliases=None, **_):
+    single = not isinstance(out_shape, (list, tuple))
+    if single:
+        out_shape, out_specs = [out_shape], [out_specs]
+
     def run(*args):
         outs = [np.zeros(s.shape, dtype=s.dtype) for s in out_shape]
+        # an aliased output starts as its input operand; operand numbers count the
+        # non-None operands only (the reference numbers them that way, tpa/tpa.py:943-946)
+        present = [a for a in args if a is not None]
+        for src, dst in (input_output_aliases or {}).items():
+            outs[dst][...] = present[src]
         for g0 in range(grid[0]):
             for g1 in range(grid[1] if len(grid) > 1 else 1):
                 pid = (g0, g1)[: len(grid)]
@@ -214,7 +226,7 @@ def pallas_call(kernel, grid, in_specs, out_specs, out_shape, **_):
                 os_ = [_block_view(o, sp, pid) for o, sp in zip(outs, out_specs)]
                 with np.errstate(invalid="ignore", divide="ignore", over="ignore"):
                     kernel(*ins, *os_)
-        return outs
+        return outs[0] if single else outs
 
     return run
 
@@ -248,6 +260,7 @@ def install():
         cdiv=cdiv,
         BlockSpec=BlockSpec,
         pallas_call=pallas_call,
+        atomic_add=atomic_add,
     )
     smap = mod("jax.experimental.shard_map", shard_map=None)
     exp = mod("jax.experimental", pallas=pallas, shard_map=smap)

@@ -12,7 +12,7 @@ tests regenerate them from the stored seed and compare against the stored
 outputs.  The script also re-runs the reference's own assertion (Pallas kernel
 vs its test-file reference(), rtol = atol = 1e-3) on every forward case.
 
-Writes tests/golden/fwd_matrix.npz, ring_matrix.npz, extra.npz.
+Writes tests/golden/fwd_matrix.npz, ring_matrix.npz, extra.npz, bwd_matrix.npz.
 """
 
 from __future__ import annotations
@@ -88,12 +88,49 @@ def load_reference(ref_root):
     return tpa, mha, ring, ttest
 
 
+def make_backward(tpa, ttest):
+    """Backward matrix of tpa/tpa_test.py:128-140: the reference's own _tpa_bwd (materialising
+    branch; the nomat branch needs jax's functional `.at[].add`, which numpy arrays lack) on the
+    residuals of its own forward, non-causal as in the reference's test, for a random `do`."""
+    bw = {}
+    seed = 300
+    for shape in FWD_SHAPES:
+        b, lq, lk, h, dk, dv, seg = shape
+        for rq in RANKS_Q:
+            for rk in RANKS_K:
+                seed += 1
+                q, k, v = make_factors(seed, b, lq, lk, rq, rk, h, dk, dv, dist="normal")
+                do = np.random.Generator(np.random.Philox(key=seed + 5000)).standard_normal(
+                    (b, lq, h, dv), dtype=np.float32)
+                qs = segment_ids(b, lq, seg) if seg else None
+                ks = segment_ids(b, lk, seg) if seg else None
+                _, res = tpa._tpa_fwd(
+                    q, k, v, num_heads=h, q_segment_ids=qs, kv_segment_ids=ks, sm_scale=1.0,
+                    causal=False, block_sizes=None, nomat=False, debug=False, interpret=True,
+                )
+                dq, dk_, dv_, _, _ = tpa._tpa_bwd(h, 1.0, False, None, False, False, True, res, do)
+                key = f"b{b}_lq{lq}_lk{lk}_h{h}_dk{dk}_dv{dv}_seg{seg or 0}_rq{rq}_rk{rk}"
+                bw[key + "/meta"] = np.array([seed, b, lq, lk, rq, rk, h, dk, dv, seg or 0])
+                bw[key + "/dq"] = np.asarray(dq, np.float32)
+                bw[key + "/dk"] = np.asarray(dk_, np.float32)
+                bw[key + "/dv"] = np.asarray(dv_, np.float32)
+    print(f"backward matrix: {len(bw) // 4} cases")
+    np.savez_compressed(os.path.join(HERE, "bwd_matrix.npz"), **bw)
+    print("bwd_matrix.npz", os.path.getsize(os.path.join(HERE, "bwd_matrix.npz")) // 1024, "KiB")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default=os.environ.get("TPA_REFERENCE", "/root/reference"))
+    ap.add_argument("--only", choices=["all", "bwd"], default="all",
+                    help="bwd: regenerate bwd_matrix.npz only")
     args = ap.parse_args()
     tpa, mha, ring, ttest = load_reference(args.reference)
     import _jax_standin as js
+
+    make_backward(tpa, ttest)
+    if args.only == "bwd":
+        return
 
     # ---------------------------------------------------------------- forward matrix
     fwd = {}

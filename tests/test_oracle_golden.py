@@ -14,6 +14,7 @@ from oracle import tpa_oracle as orc
 FWD = load_golden("fwd_matrix")
 RING = load_golden("ring_matrix")
 EXTRA = load_golden("extra")
+BWD = load_golden("bwd_matrix")
 
 
 def _close(a, b, tight=2e-5):
@@ -84,3 +85,45 @@ def test_ring_causal_is_shard_local_in_the_reference(case):
     og = orc.ring_tpa_reference(q, k, v, qs, qs, h, n, sm_scale=sm, causal=True, mask_mode="global")
     _close(og, orc.tpa_reference(q, k, v, h, qs, qs, sm_scale=sm, causal=True), tight=1e-9)
     assert np.nanmax(np.abs(og - g["o"])) > 1e-2
+
+
+def _bwd_inputs(g):
+    seed, b, lq, lk, rq, rk, h, dk, dv, seg = (int(x) for x in g["meta"])
+    q, k, v = orc.make_factors(seed, b, lq, lk, rq, rk, h, dk, dv, dist="normal")
+    do = np.random.Generator(np.random.Philox(key=seed + 5000)).standard_normal((b, lq, h, dv), dtype=np.float32)
+    qs = orc.segment_ids(b, lq, seg) if seg else None
+    ks = orc.segment_ids(b, lk, seg) if seg else None
+    return q, k, v, do, h, qs, ks
+
+
+@pytest.mark.parametrize("case", sorted(BWD))
+def test_backward_matrix(case):
+    """Oracle gradients against the reference's own _tpa_bwd; tolerance of tpa/tpa_test.py:203-205."""
+    g = BWD[case]
+    q, k, v, do, h, qs, ks = _bwd_inputs(g)
+    grads = orc.tpa_bwd_reference(q, k, v, do, h, qs, ks)
+    for name, got in zip(("dq", "dk", "dv"), grads):
+        np.testing.assert_allclose(got, g[name], atol=1e-3, rtol=1e-2)
+        assert np.max(np.abs(got - g[name]) / (1e-3 + 1e-2 * np.abs(g[name]))) < 0.05
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("seg", [None, 9])
+def test_backward_oracle_is_the_autograd_of_the_definition(causal, seg):
+    """jax.grad of reference() is what tpa/tpa_test.py:196 compares with; torch autograd of the
+    same definition stands in for it (causal and multi-head cases included)."""
+    import torch
+
+    b, lq, lk, h, dk, dv = 2, 24, 40, 6, 8, 10
+    q, k, v = orc.make_factors(3, b, lq, lk, 3, 2, h, dk, dv)
+    do = np.random.default_rng(0).standard_normal((b, lq, h, dv))
+    qs = orc.segment_ids(b, lq, seg) if seg else None
+    ks = orc.segment_ids(b, lk, seg) if seg else None
+    grads = orc.tpa_bwd_reference(q, k, v, do, h, qs, ks, 0.3, causal)
+    tq, tk, tv = (torch.tensor(x, dtype=torch.float64, requires_grad=True) for x in (q, k, v))
+    o = orc.tpa_reference_torch(tq, tk, tv, h, None if qs is None else torch.tensor(qs),
+                                None if ks is None else torch.tensor(ks), 0.3, causal)
+    loss = (torch.nan_to_num(o) * torch.tensor(do, dtype=o.dtype)).sum()
+    want = torch.autograd.grad(loss, (tq, tk, tv))
+    for got, w in zip(grads, want):
+        np.testing.assert_allclose(got, w.numpy(), atol=2e-5, rtol=1e-4)
