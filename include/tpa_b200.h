@@ -1,5 +1,5 @@
 /*
- * tpa_b200.h — C ABI of libtpa_b200.so: Tensor Product Attention forward on B200 (sm_100a).
+ * tpa_b200.h — C ABI of libtpa_b200.so: Tensor Product Attention forward and backward on B200 (sm_100a).
  *
  * The reference (jondeaton/tensor-product-attention-jax) has no FFI of its own; its
  * narrowest seam is the Pallas custom call in tpa/tpa.py:492-543,
@@ -123,15 +123,51 @@ int tpa_fwd(const TpaFwdArgs* args, void* workspace, size_t workspace_bytes, voi
 /* Same forward pass for callers that cannot allocate the workspace: an XLA custom-call
  * handler (device memory is owned, and mostly pre-reserved, by XLA's allocator) or an embedder
  * with a fixed device-memory budget.  No counterpart in the reference.  Runs the STAGED
- * tensor-core variant (bf16, head_dim 64/128, lengths % 128 == 0; other shapes return
- * TPA_ERR_KERNEL_FORCED) with its scratch in a static device array inside the library:
- * 256 + (lq + 2*lk) * batch * heads * dk * 2 bytes must fit TPA_STATIC_SCRATCH_BYTES, else
+ * tensor-core variant (bf16, head_dim 64/128; other shapes return TPA_ERR_KERNEL_FORCED) with
+ * its scratch in a static device array inside the library: what tpa_fwd_workspace_bytes reports
+ * for TPA_KERNEL_SM100_STAGED (about 256 + (lq + 2*lk) * batch * heads * dk * 2 bytes, lengths
+ * rounded up to 128) must fit TPA_STATIC_SCRATCH_BYTES, else
  * TPA_ERR_STATIC_SCRATCH and nothing is launched.  Allocates nothing.  The first call on each
  * device (with that device current) looks the array's address up once: make it at start-up,
  * before any stream capture begins.  Calls on one GPU share the array: do not let two of
  * them overlap.  Every GPU that loads the library holds TPA_STATIC_SCRATCH_BYTES until exit. */
 #define TPA_STATIC_SCRATCH_BYTES (64u << 20)
 int tpa_fwd_static_scratch(const TpaFwdArgs* args, void* stream);
+
+/* Backward pass: gradients of the forward result with respect to the three concatenated
+ * factor arrays.  Replaces _tpa_bwd / _bwd (tpa/tpa.py:168-217, 823-962): _precompute_delta
+ * (tpa/tpa.py:965-995), the custom call pl.pallas_call(_bwd_kernel ...) at tpa/tpa.py:882-956
+ * and the concatenation of the factor gradients (tpa/tpa.py:958-960), for the whole batch.
+ *
+ * `fwd` holds the forward call's operands unchanged; fwd.o and fwd.lse are the forward's
+ * RESULTS and are read here (the residuals of tpa/tpa.py:165); of fwd.flags only
+ * TPA_FLAG_CAUSAL is allowed; fwd.kernel must be TPA_KERNEL_AUTO or TPA_KERNEL_SIMT (the
+ * backward has one implementation: fp32 SIMT math, any shape the forward accepts).
+ * A query row that saw no key (lse = -inf, o = NaN) contributes nothing, as in the reference
+ * (p = 0 after tpa/tpa.py:676-677, delta by nansum).  The dim-factor gradients sum over all
+ * heads. */
+enum {
+  TPA_BWD_ACCUMULATE_DQ = 1,  /* add to dq instead of overwriting it                        */
+  TPA_BWD_ACCUMULATE_DKV = 2  /* add to dk and dv (a ring step's travelling accumulators,
+                                 tpa/ring_tpa.py:115-172)                                    */
+};
+
+typedef struct TpaBwdArgs {
+  uint32_t struct_size; /* = sizeof(TpaBwdArgs) */
+  int32_t grad_dtype;   /* TPA_DTYPE_* of dq/dk/dv: fwd.dtype, or TPA_DTYPE_F32             */
+  TpaFwdArgs fwd;
+  const void* d_o;      /* [batch, lq, heads, dv] contiguous, fwd.dtype                      */
+  void* dq;             /* [batch, lq, rank_q, heads + dk] contiguous, grad_dtype            */
+  void* dk;             /* [batch, lk, rank_k, heads + dk]                                   */
+  void* dv;             /* [batch, lk, rank_k, heads + dv]                                   */
+  uint32_t bwd_flags;   /* TPA_BWD_*                                                        */
+  int32_t reserved;
+} TpaBwdArgs;
+
+/* `workspace`: tpa_bwd_workspace_bytes(args) bytes, 256-byte aligned (dense fp32 dQ, dK, dV
+ * of the whole batch plus delta).  Six launches; enqueue-only. */
+int tpa_bwd(const TpaBwdArgs* args, void* workspace, size_t workspace_bytes, void* stream);
+size_t tpa_bwd_workspace_bytes(const TpaBwdArgs* args);
 
 /* Bytes of scratch tpa_fwd needs for these arguments (0 is possible). */
 size_t tpa_fwd_workspace_bytes(const TpaFwdArgs* args);

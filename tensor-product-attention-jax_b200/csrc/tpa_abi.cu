@@ -70,6 +70,43 @@ static int choose(const TpaFwdArgs* a, const Params& p, int* kernel) {
 
 constexpr size_t kStatusBytes = 256;  // status block at the head of every non-empty workspace
 
+static size_t round256(size_t n) { return (n + 255) & ~(size_t)255; }
+
+// Scratch of the backward: status block, delta, dense fp32 dQ / dK / dV.
+struct BwdLayout {
+  size_t delta, dq, dk, dv, total;
+};
+static BwdLayout bwd_layout(const Params& p) {
+  BwdLayout l;
+  size_t off = kStatusBytes;
+  l.delta = off; off += round256(sizeof(float) * (size_t)p.batch * p.lq * p.heads);
+  l.dq = off;    off += round256(sizeof(float) * (size_t)p.batch * p.lq * p.heads * p.dk);
+  l.dk = off;    off += round256(sizeof(float) * (size_t)p.batch * p.lk * p.heads * p.dk);
+  l.dv = off;    off += round256(sizeof(float) * (size_t)p.batch * p.lk * p.heads * p.dv);
+  l.total = off;
+  return l;
+}
+
+static int validate_bwd(const TpaBwdArgs* a, BwdParams* bp) {
+  if (a == nullptr || a->struct_size != sizeof(TpaBwdArgs)) return TPA_ERR_BAD_ARG;
+  int st = validate(&a->fwd, &bp->f);
+  if (st != TPA_OK) return st;
+  if (a->fwd.flags & ~(uint32_t)TPA_FLAG_CAUSAL) return TPA_ERR_BAD_ARG;
+  if (a->fwd.o == nullptr || a->fwd.lse == nullptr || a->d_o == nullptr || a->dq == nullptr ||
+      a->dk == nullptr || a->dv == nullptr)
+    return TPA_ERR_BAD_ARG;
+  if (a->bwd_flags & ~(uint32_t)(TPA_BWD_ACCUMULATE_DQ | TPA_BWD_ACCUMULATE_DKV)) return TPA_ERR_BAD_ARG;
+  if (a->grad_dtype != TPA_DTYPE_F32 && a->grad_dtype != a->fwd.dtype) return TPA_ERR_UNSUPPORTED;
+  if (a->fwd.kernel != TPA_KERNEL_AUTO && a->fwd.kernel != TPA_KERNEL_SIMT) return TPA_ERR_KERNEL_FORCED;
+  bp->d_o = a->d_o;
+  bp->dq = a->dq; bp->dk = a->dk; bp->dv = a->dv;
+  bp->grad_dtype = a->grad_dtype;
+  bp->accumulate_dq = (a->bwd_flags & TPA_BWD_ACCUMULATE_DQ) != 0;
+  bp->accumulate_dkv = (a->bwd_flags & TPA_BWD_ACCUMULATE_DKV) != 0;
+  bp->delta = bp->dq_dense = bp->dk_dense = bp->dv_dense = nullptr;
+  return TPA_OK;
+}
+
 }  // namespace tpa
 
 using namespace tpa;
@@ -139,6 +176,33 @@ int tpa_fwd(const TpaFwdArgs* args, void* workspace, size_t workspace_bytes, voi
   } else {
     e = launch_simt(p, nullptr, false, s);
   }
+  return e == cudaSuccess ? TPA_OK : fail_cuda(e);
+}
+
+size_t tpa_bwd_workspace_bytes(const TpaBwdArgs* args) {
+  BwdParams bp;
+  if (validate_bwd(args, &bp) != TPA_OK) return 0;
+  return bwd_layout(bp.f).total;
+}
+
+int tpa_bwd(const TpaBwdArgs* args, void* workspace, size_t workspace_bytes, void* stream) {
+  BwdParams bp;
+  int st = validate_bwd(args, &bp);
+  if (st != TPA_OK) return st;
+  const BwdLayout l = bwd_layout(bp.f);
+  if (workspace == nullptr || workspace_bytes < l.total ||
+      (reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
+    return TPA_ERR_WORKSPACE;
+  char* ws = static_cast<char*>(workspace);
+  bp.delta = reinterpret_cast<float*>(ws + l.delta);
+  bp.dq_dense = reinterpret_cast<float*>(ws + l.dq);
+  bp.dk_dense = reinterpret_cast<float*>(ws + l.dk);
+  bp.dv_dense = reinterpret_cast<float*>(ws + l.dv);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemsetAsync(workspace, 0, kStatusBytes, s);
+  if (e == cudaSuccess) e = launch_bwd_delta(bp, s);
+  if (e == cudaSuccess) e = launch_bwd_pairs_simt(bp, s);
+  if (e == cudaSuccess) e = launch_bwd_contract(bp, s);
   return e == cudaSuccess ? TPA_OK : fail_cuda(e);
 }
 

@@ -27,6 +27,25 @@ struct Params {
   uint32_t* status;  // device status block {flag, where, block, spins} or nullptr
 };
 
+// Device-side view of one backward call.
+struct BwdParams {
+  Params f;           // the forward operands; f.o and f.lse are inputs here
+  const void* d_o;    // [batch, lq, heads, dv], dtype of the factors
+  float* delta;       // scratch [batch, lq, heads]
+  float* dq_dense;    // scratch [batch, lq, heads, dk] fp32
+  float* dk_dense;    // scratch [batch, lk, heads, dk] fp32
+  float* dv_dense;    // scratch [batch, lk, heads, dv] fp32
+  void* dq;           // gradients in the concatenated layout [batch, l, rank, heads + d]
+  void* dk;
+  void* dv;
+  int grad_dtype;     // TPA_DTYPE_* of dq / dk / dv
+  bool accumulate_dq, accumulate_dkv;
+};
+
+cudaError_t launch_bwd_delta(const BwdParams& bp, cudaStream_t stream);
+cudaError_t launch_bwd_pairs_simt(const BwdParams& bp, cudaStream_t stream);
+cudaError_t launch_bwd_contract(const BwdParams& bp, cudaStream_t stream);
+
 // Launchers: enqueue on `stream`, return a cudaError_t.  `info` is filled either way.
 cudaError_t launch_simt(const Params& p, TpaKernelInfo* info, bool dry_run, cudaStream_t stream);
 bool sm100_supported(const Params& p);

@@ -29,12 +29,15 @@ KERNELS = {"auto": KERNEL_AUTO, "simt": KERNEL_SIMT, "sm100": KERNEL_SM100,
            "sm100_fused": KERNEL_SM100_FUSED, "sm100_staged": KERNEL_SM100_STAGED}
 KERNEL_NAMES = {KERNEL_SIMT: "simt", KERNEL_SM100_FUSED: "sm100_fused", KERNEL_SM100_STAGED: "sm100_staged"}
 FLAG_CAUSAL, FLAG_STATE_LOAD, FLAG_STATE_STORE, FLAG_REUSE_STAGED_Q = 1, 2, 4, 8
+BWD_ACCUMULATE_DQ, BWD_ACCUMULATE_DKV = 1, 2
 
 # Every symbol include/tpa_b200.h declares.
 EXPORTS = (
     "tpa_fwd",
     "tpa_fwd_static_scratch",
     "tpa_fwd_workspace_bytes",
+    "tpa_bwd",
+    "tpa_bwd_workspace_bytes",
     "tpa_query_kernel",
     "tpa_read_status",
     "tpa_status_string",
@@ -83,6 +86,20 @@ class TpaFwdArgs(C.Structure):
     ]
 
 
+class TpaBwdArgs(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32),
+        ("grad_dtype", C.c_int32),
+        ("fwd", TpaFwdArgs),
+        ("d_o", C.c_void_p),
+        ("dq", C.c_void_p),
+        ("dk", C.c_void_p),
+        ("dv", C.c_void_p),
+        ("bwd_flags", C.c_uint32),
+        ("reserved", C.c_int32),
+    ]
+
+
 class TpaKernelInfo(C.Structure):
     _fields_ = [
         ("kernel", C.c_int32),
@@ -110,6 +127,10 @@ def _load():
     lib.tpa_fwd_static_scratch.restype = C.c_int
     lib.tpa_fwd_workspace_bytes.argtypes = [C.POINTER(TpaFwdArgs)]
     lib.tpa_fwd_workspace_bytes.restype = C.c_size_t
+    lib.tpa_bwd.argtypes = [C.POINTER(TpaBwdArgs), C.c_void_p, C.c_size_t, C.c_void_p]
+    lib.tpa_bwd.restype = C.c_int
+    lib.tpa_bwd_workspace_bytes.argtypes = [C.POINTER(TpaBwdArgs)]
+    lib.tpa_bwd_workspace_bytes.restype = C.c_size_t
     lib.tpa_query_kernel.argtypes = [C.POINTER(TpaFwdArgs), C.POINTER(TpaKernelInfo)]
     lib.tpa_query_kernel.restype = C.c_int
     lib.tpa_read_status.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_uint32 * 4)]

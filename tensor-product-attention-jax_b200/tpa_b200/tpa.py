@@ -1,11 +1,13 @@
-"""Tensor Product Attention forward: the reference's call signatures over libtpa_b200.so.
+"""Tensor Product Attention: the reference's call signatures over libtpa_b200.so.
 
-Mirrors tpa/tpa.py of jondeaton/tensor-product-attention-jax for the forward path:
+Mirrors tpa/tpa.py of jondeaton/tensor-product-attention-jax:
 
     BlockSizes   tpa/tpa.py:35-70
-    tpa()        tpa/tpa.py:73-121
+    tpa()        tpa/tpa.py:73-121    (differentiable: torch autograd plays custom_vjp)
     _tpa_fwd()   tpa/tpa.py:124-165
-    _fwd()       tpa/tpa.py:446-543   (the custom call this library replaces)
+    _tpa_bwd()   tpa/tpa.py:168-214
+    _fwd()       tpa/tpa.py:446-543   (the forward custom call this library replaces)
+    _bwd()       tpa/tpa.py:823-962   (the backward custom call and its delta pre-pass)
 
 Arrays are torch tensors.  CUDA tensors are used in place (zero copy: the head factor
 A = x[..., :h] and the dim factor B = x[..., h:] are passed as pointer + strides).  Host
@@ -23,7 +25,7 @@ import torch
 
 from . import _capi
 
-__all__ = ["BlockSizes", "tpa", "fwd_device"]
+__all__ = ["BlockSizes", "tpa", "fwd_device", "bwd_device"]
 
 
 @dataclasses.dataclass
@@ -43,11 +45,14 @@ _DTYPES = {torch.float32: _capi.DTYPE_F32, torch.bfloat16: _capi.DTYPE_BF16}
 _workspaces: dict = {}
 
 
-def _workspace(device, nbytes):
-    """Per-(device, stream) scratch buffer, grown on demand and reused across calls."""
+def _workspace(device, nbytes, kind=None):
+    """Per-(device, stream) scratch buffer, grown on demand and reused across calls.  The
+    backward keeps its own (`kind="bwd"`) so that it never overwrites staged forward tiles."""
     if nbytes == 0:
         return None
     key = (device, torch.cuda.current_stream(device).cuda_stream)
+    if kind is not None:
+        key += (kind,)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
         ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
@@ -89,6 +94,45 @@ def _check_shapes(q, k, v, num_heads):
     return b, lq, lk, rank_q, rank_k, dk, dv
 
 
+def _fill_operands(a, q, k, v, num_heads, q_segment_ids, kv_segment_ids):
+    """Shapes, dtype, factor pointers and segment ids of a TpaFwdArgs; returns tensors to keep alive."""
+    b, lq, lk, rank_q, rank_k, dk, dv = _check_shapes(q, k, v, num_heads)
+    a.struct_size = C.sizeof(_capi.TpaFwdArgs)
+    a.dtype = _DTYPES[q.dtype]
+    a.batch, a.lq, a.lk = b, lq, lk
+    a.rank_q, a.rank_k = rank_q, rank_k
+    a.heads, a.dk, a.dv = num_heads, dk, dv
+    a.qa, a.qb = _factor(q, 0), _factor(q, num_heads)
+    a.ka, a.kb = _factor(k, 0), _factor(k, num_heads)
+    a.va, a.vb = _factor(v, 0), _factor(v, num_heads)
+    keep = []
+    if q_segment_ids is not None:
+        qs = q_segment_ids.to(device=q.device, dtype=torch.int32)
+        ks = kv_segment_ids.to(device=q.device, dtype=torch.int32)
+        # a 1-D id row is shared by the whole batch (vmap in_axes None, tpa/tpa.py:155-161)
+        qs = qs.contiguous()
+        ks = ks.contiguous()
+        if qs.shape[-1] != lq or ks.shape[-1] != lk:
+            raise AssertionError((tuple(qs.shape), tuple(ks.shape)))
+        a.q_segment_ids, a.kv_segment_ids = qs.data_ptr(), ks.data_ptr()
+        a.q_segment_batch_stride = lq if qs.ndim == 2 else 0
+        a.kv_segment_batch_stride = lk if ks.ndim == 2 else 0
+        keep += [qs, ks]
+    return keep
+
+
+def _check_operands(q, k, v, q_segment_ids, kv_segment_ids):
+    if not q.is_cuda:
+        raise RuntimeError("tpa_b200 needs a CUDA device: there is no CPU implementation")
+    if q.dtype not in _DTYPES or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise NotImplementedError(f"dtype {q.dtype}/{k.dtype}/{v.dtype}: float32 or bfloat16 factors only")
+    for x in (q, k, v):
+        if x.stride(3) != 1:
+            raise ValueError("the last (h+d) axis of the factors must be contiguous")
+    if (q_segment_ids is None) != (kv_segment_ids is None):
+        raise AssertionError("segment ids must be given for both sides or neither")  # tpa/tpa.py:369-371
+
+
 def fwd_device(
     q,
     k,
@@ -120,39 +164,11 @@ def fwd_device(
     `store_state=True` writes the merged partial into `state` and returns (None, None).
     Work is enqueued on the current stream of q's device.
     """
-    if not q.is_cuda:
-        raise RuntimeError("tpa_b200 needs a CUDA device: there is no CPU implementation")
+    _check_operands(q, k, v, q_segment_ids, kv_segment_ids)
     b, lq, lk, rank_q, rank_k, dk, dv = _check_shapes(q, k, v, num_heads)
-    if q.dtype not in _DTYPES or k.dtype != q.dtype or v.dtype != q.dtype:
-        raise NotImplementedError(f"dtype {q.dtype}/{k.dtype}/{v.dtype}: float32 or bfloat16 factors only")
-    for x in (q, k, v):
-        if x.stride(3) != 1:
-            raise ValueError("the last (h+d) axis of the factors must be contiguous")
-    if (q_segment_ids is None) != (kv_segment_ids is None):
-        raise AssertionError("segment ids must be given for both sides or neither")  # tpa/tpa.py:369-371
 
     a = _capi.TpaFwdArgs()
-    a.struct_size = C.sizeof(_capi.TpaFwdArgs)
-    a.dtype = _DTYPES[q.dtype]
-    a.batch, a.lq, a.lk = b, lq, lk
-    a.rank_q, a.rank_k = rank_q, rank_k
-    a.heads, a.dk, a.dv = num_heads, dk, dv
-    a.qa, a.qb = _factor(q, 0), _factor(q, num_heads)
-    a.ka, a.kb = _factor(k, 0), _factor(k, num_heads)
-    a.va, a.vb = _factor(v, 0), _factor(v, num_heads)
-    keep = []
-    if q_segment_ids is not None:
-        qs = q_segment_ids.to(device=q.device, dtype=torch.int32)
-        ks = kv_segment_ids.to(device=q.device, dtype=torch.int32)
-        # a 1-D id row is shared by the whole batch (vmap in_axes None, tpa/tpa.py:155-161)
-        qs = qs.contiguous()
-        ks = ks.contiguous()
-        if qs.shape[-1] != lq or ks.shape[-1] != lk:
-            raise AssertionError((tuple(qs.shape), tuple(ks.shape)))
-        a.q_segment_ids, a.kv_segment_ids = qs.data_ptr(), ks.data_ptr()
-        a.q_segment_batch_stride = lq if qs.ndim == 2 else 0
-        a.kv_segment_batch_stride = lk if ks.ndim == 2 else 0
-        keep += [qs, ks]
+    keep = _fill_operands(a, q, k, v, num_heads, q_segment_ids, kv_segment_ids)
     flags = _capi.FLAG_CAUSAL if causal else 0
     if load_state:
         flags |= _capi.FLAG_STATE_LOAD
@@ -195,6 +211,73 @@ def fwd_device(
     return out, lse
 
 
+def bwd_device(
+    q,
+    k,
+    v,
+    num_heads,
+    q_segment_ids,
+    kv_segment_ids,
+    sm_scale,
+    causal,
+    o,
+    lse,
+    do,
+    *,
+    q_offset=0,
+    k_offset=0,
+    grad_dtype=None,
+    out=None,
+    accumulate_dq=False,
+    accumulate_dkv=False,
+):
+    """One tpa_bwd call on CUDA tensors; returns (dq, dk, dv) shaped like q, k, v.
+
+    `o` and `lse` (fp32) are the forward's results, `do[b, lq, h, dv]` the incoming gradient.
+    `grad_dtype` is q's dtype (default) or torch.float32; `out = (dq, dk, dv)` supplies the
+    gradient buffers, which `accumulate_dq` / `accumulate_dkv` add to instead of overwriting
+    (the travelling dk, dv of a ring backward, tpa/ring_tpa.py:115-172).
+    """
+    _check_operands(q, k, v, q_segment_ids, kv_segment_ids)
+    b, lq, lk, rank_q, rank_k, dk, dv = _check_shapes(q, k, v, num_heads)
+    grad_dtype = q.dtype if grad_dtype is None else grad_dtype
+    if grad_dtype not in (q.dtype, torch.float32):
+        raise NotImplementedError(f"gradient dtype {grad_dtype} for {q.dtype} factors")
+    a = _capi.TpaBwdArgs()
+    a.struct_size = C.sizeof(_capi.TpaBwdArgs)
+    a.grad_dtype = _DTYPES[grad_dtype]
+    keep = _fill_operands(a.fwd, q, k, v, num_heads, q_segment_ids, kv_segment_ids)
+    o, do = o.contiguous(), do.contiguous()
+    lse = lse.to(torch.float32).contiguous()
+    if tuple(o.shape) != (b, lq, num_heads, dv) or tuple(do.shape) != tuple(o.shape):
+        raise AssertionError((tuple(o.shape), tuple(do.shape)))
+    if tuple(lse.shape) != (b, lq, num_heads) or o.dtype != q.dtype or do.dtype != q.dtype:
+        raise AssertionError((tuple(lse.shape), o.dtype, do.dtype))
+    a.fwd.o, a.fwd.lse, a.d_o = o.data_ptr(), lse.data_ptr(), do.data_ptr()
+    a.fwd.sm_scale = float(sm_scale)
+    a.fwd.flags = _capi.FLAG_CAUSAL if causal else 0
+    a.fwd.q_offset, a.fwd.k_offset = int(q_offset), int(k_offset)
+    a.fwd.kernel = _capi.KERNEL_AUTO
+    if out is None:
+        if accumulate_dq or accumulate_dkv:
+            raise ValueError("accumulating needs the buffers to add to (out=(dq, dk, dv))")
+        out = tuple(torch.empty(x.shape, dtype=grad_dtype, device=q.device) for x in (q, k, v))
+    for g, x in zip(out, (q, k, v)):
+        assert g.is_contiguous() and g.dtype == grad_dtype and tuple(g.shape) == tuple(x.shape)
+    a.dq, a.dk, a.dv = (g.data_ptr() for g in out)
+    a.bwd_flags = (_capi.BWD_ACCUMULATE_DQ if accumulate_dq else 0) | (
+        _capi.BWD_ACCUMULATE_DKV if accumulate_dkv else 0
+    )
+    with torch.cuda.device(q.device):
+        nbytes = _capi.lib.tpa_bwd_workspace_bytes(C.byref(a))
+        ws = _workspace(q.device, nbytes, "bwd")
+        stream = torch.cuda.current_stream(q.device).cuda_stream
+        st = _capi.lib.tpa_bwd(C.byref(a), ws.data_ptr() if ws is not None else None, nbytes, C.c_void_p(stream))
+    _capi.check(st)
+    del keep
+    return out
+
+
 def query_kernel(q, k, v, num_heads, kernel="auto", causal=False, segments=False):
     """Which kernel / tiles / grid a call with these operands would use (tpa_query_kernel)."""
     b, lq, lk, rank_q, rank_k, dk, dv = _check_shapes(q, k, v, num_heads)
@@ -233,6 +316,19 @@ def _to_device(x, device):
     return x.to(device, non_blocking=x.is_pinned() if not x.is_cuda else False)
 
 
+def _tpa_fwd_checks(q, k, block_sizes):
+    """The divisibility rule of the reference launcher (tpa/tpa.py:485-490)."""
+    if block_sizes is None:
+        block_sizes = BlockSizes()
+    lq, lk = q.shape[1], k.shape[1]
+    block_q = min(block_sizes.block_q, lq)
+    block_kv = min(block_sizes.block_kv, lk)
+    if lq % block_q != 0:
+        raise AssertionError((lq, block_q))
+    if lk % block_kv != 0:
+        raise AssertionError((lk, block_kv))
+
+
 def _tpa_fwd(
     q,
     k,
@@ -255,18 +351,52 @@ def _tpa_fwd(
     and the other two are Pallas debugging switches.
     """
     del nomat, debug, interpret
-    if block_sizes is None:
-        block_sizes = BlockSizes()
-    lq, lk = q.shape[1], k.shape[1]
-    block_q = min(block_sizes.block_q, lq)  # tpa/tpa.py:485-490
-    block_kv = min(block_sizes.block_kv, lk)
-    if lq % block_q != 0:
-        raise AssertionError((lq, block_q))
-    if lk % block_kv != 0:
-        raise AssertionError((lk, block_kv))
+    _tpa_fwd_checks(q, k, block_sizes)
     o, l = fwd_device(q, k, v, num_heads, q_segment_ids, kv_segment_ids, sm_scale, causal)
     l = l.to(q.dtype)
     return o, (q, k, v, q_segment_ids, kv_segment_ids, o, l)
+
+
+def _tpa_bwd(num_heads, sm_scale, causal, block_sizes, nomat, debug, interpret, residuals, do):
+    """Backward of the batch forward, same arguments and result as tpa/tpa.py:168-214:
+    (dq, dk, dv, None, None) for residuals = (q, k, v, q_segment_ids, kv_segment_ids, o, l)."""
+    del block_sizes, nomat, debug, interpret
+    q, k, v, q_segment_ids, kv_segment_ids, o, l = residuals
+    dq, dk, dv = bwd_device(q, k, v, num_heads, q_segment_ids, kv_segment_ids, sm_scale, causal, o, l, do)
+    return dq, dk, dv, None, None
+
+
+def _bwd(q, k, v, q_segment_ids, kv_segment_ids, o, l, do, num_heads, sm_scale, causal,
+         block_sizes=None, nomat=False, debug=False, interpret=False):
+    """Per-batch-element backward (dq, dk, dv) as tpa/tpa.py:823-962."""
+    dq, dk, dv, _, _ = _tpa_bwd(
+        num_heads, sm_scale, causal, block_sizes, nomat, debug, interpret,
+        (q[None], k[None], v[None],
+         None if q_segment_ids is None else q_segment_ids[None],
+         None if kv_segment_ids is None else kv_segment_ids[None], o[None], l[None]),
+        do[None],
+    )
+    return dq[0], dk[0], dv[0]
+
+
+class _TpaFunction(torch.autograd.Function):
+    """What jax.custom_vjp + tpa.defvjp(_tpa_fwd, _tpa_bwd) is in the reference (tpa/tpa.py:73,217):
+    the forward keeps (o, fp32 lse) as residuals, the backward is tpa_bwd."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, num_heads, q_segment_ids, kv_segment_ids, sm_scale, causal):
+        o, lse = fwd_device(q, k, v, num_heads, q_segment_ids, kv_segment_ids, sm_scale, causal)
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.segments = (q_segment_ids, kv_segment_ids)
+        ctx.meta = (num_heads, sm_scale, causal)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, lse = ctx.saved_tensors
+        num_heads, sm_scale, causal = ctx.meta
+        dq, dk, dv = bwd_device(q, k, v, num_heads, *ctx.segments, sm_scale, causal, o, lse, do)
+        return dq, dk, dv, None, None, None, None, None
 
 
 def tpa(
@@ -303,6 +433,9 @@ def tpa(
         q, k, v = (_to_device(x, dev) for x in (q, k, v))
         q_segment_ids = _to_device(q_segment_ids, dev)
         kv_segment_ids = _to_device(kv_segment_ids, dev)
+    if host_kind is None and torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad):
+        _tpa_fwd_checks(q, k, block_sizes)
+        return _TpaFunction.apply(q, k, v, num_heads, q_segment_ids, kv_segment_ids, sm_scale, causal)
     o, _ = _tpa_fwd(
         q,
         k,
