@@ -141,8 +141,9 @@ int tpa_fwd_static_scratch(const TpaFwdArgs* args, void* stream);
  *
  * `fwd` holds the forward call's operands unchanged; fwd.o and fwd.lse are the forward's
  * RESULTS and are read here (the residuals of tpa/tpa.py:165); of fwd.flags only
- * TPA_FLAG_CAUSAL is allowed; fwd.kernel must be TPA_KERNEL_AUTO or TPA_KERNEL_SIMT (the
- * backward has one implementation: fp32 SIMT math, any shape the forward accepts).
+ * TPA_FLAG_CAUSAL is allowed; fwd.kernel is TPA_KERNEL_AUTO, TPA_KERNEL_SIMT (fp32 math, any
+ * shape the forward accepts) or TPA_KERNEL_SM100 (tcgen05 pair passes; same shapes as the
+ * tensor-core forward, plus d_o 16-byte aligned; AUTO picks them whenever they apply).
  * A query row that saw no key (lse = -inf, o = NaN) contributes nothing, as in the reference
  * (p = 0 after tpa/tpa.py:676-677, delta by nansum).  The dim-factor gradients sum over all
  * heads. */
@@ -165,7 +166,9 @@ typedef struct TpaBwdArgs {
 } TpaBwdArgs;
 
 /* `workspace`: tpa_bwd_workspace_bytes(args) bytes, 256-byte aligned (dense fp32 dQ, dK, dV
- * of the whole batch plus delta).  Six launches; enqueue-only. */
+ * of the whole batch, delta and, for the tensor-core passes, the staged bf16 Q, K, V, dO tiles).
+ * Six launches (SIMT) or eight (tensor cores); enqueue-only.  The first 16 bytes are the device
+ * status block that tpa_read_status reads. */
 int tpa_bwd(const TpaBwdArgs* args, void* workspace, size_t workspace_bytes, void* stream);
 size_t tpa_bwd_workspace_bytes(const TpaBwdArgs* args);
 

@@ -74,15 +74,16 @@ static size_t round256(size_t n) { return (n + 255) & ~(size_t)255; }
 
 // Scratch of the backward: status block, delta, dense fp32 dQ / dK / dV.
 struct BwdLayout {
-  size_t delta, dq, dk, dv, total;
+  size_t delta, dq, dk, dv, tc, total;  // tc: scratch of the tensor-core passes
 };
-static BwdLayout bwd_layout(const Params& p) {
+static BwdLayout bwd_layout(const Params& p, bool tensor_cores) {
   BwdLayout l;
   size_t off = kStatusBytes;
   l.delta = off; off += round256(sizeof(float) * (size_t)p.batch * p.lq * p.heads);
   l.dq = off;    off += round256(sizeof(float) * (size_t)p.batch * p.lq * p.heads * p.dk);
   l.dk = off;    off += round256(sizeof(float) * (size_t)p.batch * p.lk * p.heads * p.dk);
   l.dv = off;    off += round256(sizeof(float) * (size_t)p.batch * p.lk * p.heads * p.dv);
+  l.tc = off;    off += tensor_cores ? bwd_sm100_workspace_bytes(p) : 0;
   l.total = off;
   return l;
 }
@@ -97,13 +98,22 @@ static int validate_bwd(const TpaBwdArgs* a, BwdParams* bp) {
     return TPA_ERR_BAD_ARG;
   if (a->bwd_flags & ~(uint32_t)(TPA_BWD_ACCUMULATE_DQ | TPA_BWD_ACCUMULATE_DKV)) return TPA_ERR_BAD_ARG;
   if (a->grad_dtype != TPA_DTYPE_F32 && a->grad_dtype != a->fwd.dtype) return TPA_ERR_UNSUPPORTED;
-  if (a->fwd.kernel != TPA_KERNEL_AUTO && a->fwd.kernel != TPA_KERNEL_SIMT) return TPA_ERR_KERNEL_FORCED;
+  if (a->fwd.kernel == TPA_KERNEL_SM100_FUSED || a->fwd.kernel == TPA_KERNEL_SM100_STAGED)
+    return TPA_ERR_KERNEL_FORCED;
   bp->d_o = a->d_o;
   bp->dq = a->dq; bp->dk = a->dk; bp->dv = a->dv;
   bp->grad_dtype = a->grad_dtype;
   bp->accumulate_dq = (a->bwd_flags & TPA_BWD_ACCUMULATE_DQ) != 0;
   bp->accumulate_dkv = (a->bwd_flags & TPA_BWD_ACCUMULATE_DKV) != 0;
   bp->delta = bp->dq_dense = bp->dk_dense = bp->dv_dense = nullptr;
+  return TPA_OK;
+}
+
+// TPA_OK and whether the tensor-core passes run; SM100 forced on an unsupported shape is an error
+static int choose_bwd(const TpaBwdArgs* a, const BwdParams& bp, bool* tensor_cores) {
+  const bool tc = bwd_sm100_supported(bp);
+  if (a->fwd.kernel == TPA_KERNEL_SM100 && !tc) return TPA_ERR_KERNEL_FORCED;
+  *tensor_cores = tc && a->fwd.kernel != TPA_KERNEL_SIMT;
   return TPA_OK;
 }
 
@@ -181,15 +191,19 @@ int tpa_fwd(const TpaFwdArgs* args, void* workspace, size_t workspace_bytes, voi
 
 size_t tpa_bwd_workspace_bytes(const TpaBwdArgs* args) {
   BwdParams bp;
-  if (validate_bwd(args, &bp) != TPA_OK) return 0;
-  return bwd_layout(bp.f).total;
+  bool tc;
+  if (validate_bwd(args, &bp) != TPA_OK || choose_bwd(args, bp, &tc) != TPA_OK) return 0;
+  return bwd_layout(bp.f, tc).total;
 }
 
 int tpa_bwd(const TpaBwdArgs* args, void* workspace, size_t workspace_bytes, void* stream) {
   BwdParams bp;
   int st = validate_bwd(args, &bp);
   if (st != TPA_OK) return st;
-  const BwdLayout l = bwd_layout(bp.f);
+  bool tc;
+  st = choose_bwd(args, bp, &tc);
+  if (st != TPA_OK) return st;
+  const BwdLayout l = bwd_layout(bp.f, tc);
   if (workspace == nullptr || workspace_bytes < l.total ||
       (reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
     return TPA_ERR_WORKSPACE;
@@ -200,8 +214,13 @@ int tpa_bwd(const TpaBwdArgs* args, void* workspace, size_t workspace_bytes, voi
   bp.dv_dense = reinterpret_cast<float*>(ws + l.dv);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   cudaError_t e = cudaMemsetAsync(workspace, 0, kStatusBytes, s);
-  if (e == cudaSuccess) e = launch_bwd_delta(bp, s);
-  if (e == cudaSuccess) e = launch_bwd_pairs_simt(bp, s);
+  if (tc) {
+    bp.f.status = static_cast<uint32_t*>(workspace);
+    if (e == cudaSuccess) e = launch_bwd_pairs_sm100(bp, ws + l.tc, s);
+  } else {
+    if (e == cudaSuccess) e = launch_bwd_delta(bp, s);
+    if (e == cudaSuccess) e = launch_bwd_pairs_simt(bp, s);
+  }
   if (e == cudaSuccess) e = launch_bwd_contract(bp, s);
   return e == cudaSuccess ? TPA_OK : fail_cuda(e);
 }

@@ -1,0 +1,478 @@
+// Tensor-core TPA backward for sm_100a: bf16 factors, head_dim 64 or 128, any lengths.
+// Replaces _bwd_kernel (tpa/tpa.py:546-820) for those shapes; the arithmetic is the
+// materialising branch of the reference (tpa/tpa.py:777-799).
+//
+// Per 128 x 128 (query tile, key tile) pair and head, with S2 = log2(e) sm_scale q k^T:
+//     p  = 2^(S2 - log2(e) lse)                 masked entries 0      tpa/tpa.py:662-677
+//     ds = p (do v^T - delta)                                          tpa/tpa.py:783-786
+//     dv += p^T do     dk += sm_scale ds^T q     dq += sm_scale ds k   tpa/tpa.py:778,789,796
+//
+// The reference gives a program one key block and adds its dq contribution with atomics
+// (tpa/tpa.py:806-807).  Here ONE kernel template runs twice, without atomics:
+//
+//   KV_OWNER   a CTA owns a key tile (K, V resident in shared memory) and streams the query
+//              tiles (Q, dO, row statistics) past it.  It computes the TRANSPOSED tiles
+//              S^T = K Q^T and dP^T = V dO^T, so that p^T and ds^T sit in TMEM with keys on the
+//              lanes and feed dV += p^T dO and dK += ds^T Q as the TMEM (A) operand.
+//   !KV_OWNER  a CTA owns a query tile (Q, dO resident) and streams the key tiles (K, V):
+//              S = Q K^T, dP = dO V^T, dQ += ds K with ds as the TMEM operand.
+//
+// Seven tile GEMMs instead of five, all tcgen05.mma with fp32 accumulators in TMEM, in
+// exchange for bitwise reproducible gradients and no zero-fill or atomic traffic.  Both passes
+// read the same staged operands: tpa_stage_tiles_kernel (shared with the forward) rebuilds the
+// per-head Q, K, V tiles from the factors once, tpa_bwd_stage_do_kernel lays dO out the same
+// way, and tpa_bwd_stats_kernel writes log2(e) lse and delta per (head, row).  One staged tile
+// serves as a K-major operand of the first two GEMMs and as an MN-major operand of the
+// accumulating ones; only the descriptor differs.
+//
+// Roles, by warp: 0-7 element-wise (two threads per TMEM lane, 64 columns each) and the
+// epilogue; 8: one thread issues the bulk copies; 9: one thread issues tcgen05.mma.
+// TMEM columns: T1 [0,128) (S, then p as bf16), T2 [128,256) (dP, then ds as bf16),
+// accumulators from 256 (dQ, or dK and dV).  Dense fp32 dQ / dK / dV go to scratch; the
+// factor contraction (tpa_bwd_contract_kernel) is shared with the SIMT path.
+//
+// Every mbarrier wait is bounded (~2^28 cycles): the waiter then records where it gave up in
+// the status block, raises a CTA-wide abort flag that makes later waits fall through, and the
+// CTA runs to its normal end (TMEM is freed).
+#include <math_constants.h>
+
+#include "sm100_ptx.cuh"
+#include "tpa_common.cuh"
+
+namespace tpa {
+namespace {
+
+using namespace ptx;
+
+constexpr int kRows = 128;  // rows of every tile (queries or keys)
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+constexpr long long kWaitCycles = 1ll << 28;
+constexpr int kEwWarps = 8;
+constexpr int kProducerWarp = kEwWarps;
+constexpr int kMmaWarp = kEwWarps + 1;
+constexpr int kThreads = (kMmaWarp + 1) * 32;
+
+struct BwdBarriers {
+  uint64_t x_full;                   // the CTA's own two tiles have landed
+  uint64_t y_full[2], y_empty[2];    // streamed tiles (+ row statistics), double buffered
+  uint64_t t_full, p_ready, acc_done;
+  uint32_t tmem_base;
+  volatile uint32_t abort;
+  alignas(16) float stats[2][2][kRows];  // [stage][log2e*lse | delta][query row] (KV_OWNER)
+};
+
+struct BoundedWait {
+  BwdBarriers* bars;
+  uint32_t* status;
+  __device__ __forceinline__ void operator()(uint64_t* bar, uint32_t parity, uint32_t where) const {
+    if (mbar_try_wait(bar, parity)) return;
+    const long long t0 = clock64();
+    uint32_t spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+      if (bars->abort) return;
+      if ((++spins & 63u) == 0 && clock64() - t0 > kWaitCycles) {
+        bars->abort = 1;
+        if (status != nullptr && atomicCAS(status, 0u, 1u) == 0u) {
+          status[1] = where;
+          status[2] = blockIdx.x;
+          status[3] = spins;
+        }
+        return;
+      }
+    }
+  }
+};
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Row statistics, one warp per (batch, padded row, head):
+//   stats[((batch*heads + head) * tiles + row/128) * 256 + row%128]       = log2(e) * lse
+//   stats[...                                       + 128 + row%128]      = delta
+// delta = nansum(o * do) (tpa/tpa.py:976-980).  Rows that saw no key (lse = -inf) and the
+// padding rows of a ragged last tile get lse = +inf, so that p = 2^(s - inf) = 0 for them.
+__global__ void __launch_bounds__(256) tpa_bwd_stats_kernel(const Params p, const __nv_bfloat16* d_o,
+                                                            float* stats, int tiles) {
+  const int lane = threadIdx.x & 31;
+  const int64_t w = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int64_t total = (int64_t)p.batch * tiles * kRows * p.heads;
+  if (w >= total) return;
+  const int head = (int)(w % p.heads);
+  const int64_t rest = w / p.heads;
+  const int row = (int)(rest % ((int64_t)tiles * kRows));
+  const int batch = (int)(rest / ((int64_t)tiles * kRows));
+  float acc = 0.f, l2 = CUDART_INF_F;
+  if (row < p.lq) {
+    const int64_t rh = ((int64_t)batch * p.lq + row) * p.heads + head;
+    const __nv_bfloat16* o = static_cast<const __nv_bfloat16*>(p.o) + rh * p.dv;
+    const __nv_bfloat16* g = d_o + rh * p.dv;
+    for (int t = lane; t < p.dv; t += 32) {
+      const float x = __bfloat162float(o[t]) * __bfloat162float(g[t]);
+      if (x == x) acc += x;
+    }
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+    const float lse = p.lse[rh];
+    if (lse != -CUDART_INF_F) l2 = lse * kLog2e;
+  }
+  if (lane == 0) {
+    float* dst = stats + (((int64_t)batch * p.heads + head) * tiles + row / kRows) * (2 * kRows) + row % kRows;
+    dst[0] = l2;
+    dst[kRows] = acc;
+  }
+}
+
+// dO[batch, lq, heads, D] -> per (batch, head, tile) shared-memory images (64-column sub-tiles of
+// 16 KB, 128-byte swizzle), rows past lq zero.  grid = (tiles, batch), 256 threads.
+template <int D>
+__global__ void __launch_bounds__(256) tpa_bwd_stage_do_kernel(const Params p, const __nv_bfloat16* d_o,
+                                                               uint8_t* ws, int tiles) {
+  constexpr int CH = D / 8;
+  constexpr int kTileBytes = kRows * D * 2;
+  const int tile = blockIdx.x, batch = blockIdx.y;
+  const int per_row = p.heads * CH;
+  for (int idx = threadIdx.x; idx < kRows * per_row; idx += 256) {
+    const int row = idx / per_row, rem = idx - row * per_row;
+    const int head = rem / CH, chunk = rem - head * CH;
+    const int64_t g = (int64_t)tile * kRows + row;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (g < p.lq)
+      v = __ldg(reinterpret_cast<const uint4*>(d_o + (((int64_t)batch * p.lq + g) * p.heads + head) * D + chunk * 8));
+    uint8_t* dst = ws + (((int64_t)batch * p.heads + head) * tiles + tile) * kTileBytes +
+                   (chunk >> 3) * (kRows * 128) + sw128_offset(row, chunk & 7);
+    *reinterpret_cast<uint4*>(dst) = v;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// The pair kernel.  "own" = the tile pair the CTA keeps (K,V or Q,dO), "moving" = the tiles it
+// streams (Q,dO or K,V).  T1 = own0 moving0^T, T2 = own1 moving1^T; acc0 += ds moving0,
+// acc1 += p moving1 (KV_OWNER only).  dense0 / dense1: fp32 [batch, len, heads, D].
+template <int D, bool KV_OWNER>
+__global__ void __launch_bounds__(kThreads, 1)
+tpa_bwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, const uint8_t* ws_v,
+                     const uint8_t* ws_do, const float* stats, float* dense0, float* dense1,
+                     const int own_tiles, const int group) {
+  constexpr int kTileBytes = kRows * D * 2;
+  constexpr uint32_t kIdescT = make_idesc(128, kRows, false, false);
+  constexpr uint32_t kIdescAcc = make_idesc(128, D, false, true);
+  constexpr int kT2 = 128, kAcc = 256;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sX = smem;                   // own tiles: [0] K or Q, [1] V or dO
+  uint8_t* sY = smem + 2 * kTileBytes;  // moving tiles: stage s at s * 2 tiles: [0] Q or K, [1] dO or V
+  BwdBarriers* bars = reinterpret_cast<BwdBarriers*>(smem + 6 * kTileBytes);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nq = (p.lq + kRows - 1) / kRows, nk = (p.lk + kRows - 1) / kRows;
+  // (batch, head) slices are taken `group` at a time so that the CTAs running together stream
+  // the same moving tiles through L2; within a group the tiles with the longest walk go first.
+  const int per_group = group * own_tiles;
+  const int slice = (blockIdx.x / per_group) * group + (blockIdx.x % per_group) % group;
+  const int ord = (blockIdx.x % per_group) / group;
+  const int own = KV_OWNER ? ord : own_tiles - 1 - ord;
+  const int head = slice % p.heads, batch = slice / p.heads;
+  const int own0 = own * kRows;
+  const bool causal = (p.flags & TPA_FLAG_CAUSAL) != 0;
+  const bool has_seg = p.q_seg != nullptr;
+
+  // moving tiles that can hold a visible pair
+  int t_lo = 0, t_hi = KV_OWNER ? nq : nk;
+  if (causal) {
+    if (KV_OWNER) {
+      const int64_t first = (int64_t)own0 + p.k_offset - p.q_offset;  // first row that sees key own0
+      if (first > 0) t_lo = (int)min((int64_t)t_hi, first / kRows);
+    } else {
+      const int64_t last = (int64_t)own0 + kRows - 1 + p.q_offset - p.k_offset;  // last visible key
+      t_hi = last < 0 ? 0 : (int)min((int64_t)t_hi, last / kRows + 1);
+    }
+  }
+  const int n_tiles = max(0, t_hi - t_lo);
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->x_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bars->y_full[s], 1);
+      mbar_init(&bars->y_empty[s], 1);
+    }
+    mbar_init(&bars->t_full, 1);
+    mbar_init(&bars->p_ready, kEwWarps);
+    mbar_init(&bars->acc_done, 1);
+    bars->abort = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(&bars->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_base;
+  const BoundedWait wait{bars, p.status};
+  const int64_t bh = (int64_t)batch * p.heads + head;
+
+  if (warp < kEwWarps) {
+    // ------------------------------------------------------------------ element-wise + epilogue
+    const int quarter = warp & 3, half = warp >> 2;
+    const int row = quarter * 32 + lane;  // TMEM lane = row of the own tile
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    const uint32_t tT1 = tmem + lane_base + half * 64;
+    const uint32_t tT2 = tmem + lane_base + kT2 + half * 64;
+    const int own_idx = own0 + row;
+    const bool own_ok = own_idx < (KV_OWNER ? p.lk : p.lq);
+    const int64_t own_pos = (int64_t)own_idx + (KV_OWNER ? p.k_offset : p.q_offset);
+    const int mov_len = KV_OWNER ? p.lq : p.lk;
+    const int64_t mov_off = KV_OWNER ? p.q_offset : p.k_offset;
+    int own_seg = 0;
+    const int32_t* mov_seg = nullptr;
+    if (has_seg) {
+      const int32_t* own_ids = KV_OWNER ? p.kv_seg + (int64_t)batch * p.kv_seg_bstride
+                                        : p.q_seg + (int64_t)batch * p.q_seg_bstride;
+      mov_seg = KV_OWNER ? p.q_seg + (int64_t)batch * p.q_seg_bstride
+                         : p.kv_seg + (int64_t)batch * p.kv_seg_bstride;
+      if (own_ok) own_seg = own_ids[own_idx];
+    }
+    float my_l2 = CUDART_INF_F, my_dl = 0.f;  // !KV_OWNER: this lane's query row
+    if (!KV_OWNER) {
+      const float* st = stats + (bh * nq + own) * (2 * kRows);
+      my_l2 = st[row];
+      my_dl = st[kRows + row];
+    }
+    const float inv_rk = 1.f / (float)p.rank_k;
+
+    for (int n = 0; n < n_tiles; ++n) {
+      const int s = n & 1;
+      const int m0 = (t_lo + n) * kRows + half * 64;  // first moving row of this thread's columns
+      wait(&bars->t_full, n & 1, 0x100);
+      tc_fence_after();
+      if (KV_OWNER) wait(&bars->y_full[s], (n >> 1) & 1, 0x101);  // the statistics have landed
+      const float* sl2 = bars->stats[s][0] + half * 64;
+      const float* sdl = bars->stats[s][1] + half * 64;
+      // does any pair of these 32 lanes x 64 columns need the element-wise test?
+      bool masked = has_seg;
+      if (causal) {
+        const int64_t lane0_pos = (int64_t)own0 + quarter * 32 + (KV_OWNER ? p.k_offset : p.q_offset);
+        if (KV_OWNER) masked = masked || ((int64_t)m0 + mov_off < lane0_pos + 31);      // min q < max key
+        else masked = masked || ((int64_t)m0 + 63 + mov_off > lane0_pos);                // max key > min q
+      }
+      if (!KV_OWNER) masked = masked || (m0 + 64 > p.lk);  // padded keys of a ragged last tile
+
+      uint32_t ppk[32], dpk[32];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t t1[32], t2[32];
+        tmem_ld32(tT1 + c * 32, t1);
+        tmem_ld32(tT2 + c * 32, t2);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float pe[2], de[2];
+#pragma unroll
+          for (int k = 0; k < 2; ++k) {
+            const int col = c * 32 + e + k;
+            const float l2 = KV_OWNER ? sl2[col] : my_l2;
+            const float dl = KV_OWNER ? sdl[col] : my_dl;
+            float pr = ex2(__uint_as_float(t1[e + k]) - l2);
+            if (masked) {
+              const int mi = m0 + col;
+              const int64_t mpos = (int64_t)mi + mov_off;
+              bool keep = mi < mov_len;
+              if (causal) keep = keep && (KV_OWNER ? (mpos >= own_pos) : (own_pos >= mpos));
+              if (has_seg && keep) keep = mov_seg[mi] == own_seg;
+              if (!keep) pr = 0.f;
+            }
+            pe[k] = pr;
+            de[k] = pr * fmaf(__uint_as_float(t2[e + k]), inv_rk, -dl);
+          }
+          ppk[c * 16 + e / 2] = pack_bf16(pe[0], pe[1]);
+          dpk[c * 16 + e / 2] = pack_bf16(de[0], de[1]);
+        }
+      }
+      // bf16 p / ds of this half overwrite the first 32 columns of its own 64 fp32 columns:
+      // moving row k of the tile is at column (k / 64) * 64 + (k % 64) / 2 of T1 / T2
+      if (KV_OWNER) tmem_st32(tT1, ppk);
+      tmem_st32(tT2, dpk);
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->p_ready);
+    }
+
+    // epilogue: accumulators -> dense fp32 rows (zeros when nothing was visible)
+    if (n_tiles > 0) {
+      wait(&bars->acc_done, 0, 0x200);
+      tc_fence_after();
+    }
+    const int own_len = KV_OWNER ? p.lk : p.lq;
+    const float scale0 = KV_OWNER ? (float)p.rank_k * kLn2 : p.sm_scale * inv_rk;
+#pragma unroll
+    for (int a = 0; a < (KV_OWNER ? 2 : 1); ++a) {
+      float* dst = (a == 0 ? dense0 : dense1) +
+                   (((int64_t)batch * own_len + own_idx) * p.heads + head) * D + half * (D / 2);
+      const float scale = a == 0 ? scale0 : 1.f;
+#pragma unroll
+      for (int c = 0; c < D / 64; ++c) {
+        uint32_t r[32];
+        if (n_tiles > 0) {
+          tmem_ld32(tmem + lane_base + kAcc + a * D + half * (D / 2) + c * 32, r);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) r[e] = 0u;
+        }
+        if (own_ok) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 4)
+            *reinterpret_cast<float4*>(dst + c * 32 + e) =
+                make_float4(__uint_as_float(r[e]) * scale, __uint_as_float(r[e + 1]) * scale,
+                            __uint_as_float(r[e + 2]) * scale, __uint_as_float(r[e + 3]) * scale);
+        }
+      }
+    }
+  } else if (warp == kProducerWarp) {
+    // ------------------------------------------------------------------ bulk copies of staged tiles
+    if (lane == 0 && n_tiles > 0) {  // every copy issued here is waited for by the MMA thread
+      const uint8_t* gx0 = (KV_OWNER ? ws_k + (bh * nk + own) * kTileBytes : ws_q + (bh * nq + own) * kTileBytes);
+      const uint8_t* gx1 = (KV_OWNER ? ws_v + (bh * nk + own) * kTileBytes : ws_do + (bh * nq + own) * kTileBytes);
+      mbar_arrive_expect_tx(&bars->x_full, 2 * kTileBytes);
+      bulk_g2s(sX, gx0, kTileBytes, &bars->x_full);
+      bulk_g2s(sX + kTileBytes, gx1, kTileBytes, &bars->x_full);
+      for (int n = 0; n < n_tiles; ++n) {
+        const int s = n & 1;
+        const int64_t t = t_lo + n;
+        if (n >= 2) wait(&bars->y_empty[s], ((n >> 1) - 1) & 1, 0x400);
+        const uint8_t* gy0 = KV_OWNER ? ws_q + (bh * nq + t) * kTileBytes : ws_k + (bh * nk + t) * kTileBytes;
+        const uint8_t* gy1 = KV_OWNER ? ws_do + (bh * nq + t) * kTileBytes : ws_v + (bh * nk + t) * kTileBytes;
+        mbar_arrive_expect_tx(&bars->y_full[s], 2 * kTileBytes + (KV_OWNER ? 2 * kRows * 4 : 0));
+        bulk_g2s(sY + s * 2 * kTileBytes, gy0, kTileBytes, &bars->y_full[s]);
+        bulk_g2s(sY + s * 2 * kTileBytes + kTileBytes, gy1, kTileBytes, &bars->y_full[s]);
+        if (KV_OWNER)
+          bulk_g2s(bars->stats[s], stats + (bh * nq + t) * (2 * kRows), 2 * kRows * 4, &bars->y_full[s]);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ MMA issue (one thread)
+    if (lane == 0 && n_tiles > 0) {
+      const uint32_t aX = smem_u32(sX), aY = smem_u32(sY);
+      wait(&bars->x_full, 0, 0x600);
+      tc_fence_after();
+      for (int n = 0; n < n_tiles; ++n) {
+        const int s = n & 1;
+        const uint32_t y0 = aY + s * 2 * kTileBytes, y1 = y0 + kTileBytes;
+        wait(&bars->y_full[s], (n >> 1) & 1, 0x601);
+        tc_fence_after();
+#pragma unroll
+        for (int g = 0; g < 2; ++g) {
+          const uint32_t xb = aX + g * kTileBytes, yb = g == 0 ? y0 : y1;
+#pragma unroll
+          for (int ks = 0; ks < D / 16; ++ks) {
+            const uint32_t off = (ks >> 2) * (kRows * 128) + (ks & 3) * 32;
+            mma_ss(tmem + g * kT2, make_desc(xb + off, 16, 1024), make_desc(yb + off, 16, 1024), kIdescT, ks > 0);
+          }
+        }
+        tc_commit(&bars->t_full);
+        wait(&bars->p_ready, n & 1, 0x610);
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < kRows / 16; ++ks) {
+          const uint32_t acol = (ks >> 2) * 64 + (ks & 3) * 8;
+          const uint32_t accum = (n > 0 || ks > 0) ? 1u : 0u;
+          mma_ts(tmem + kAcc, tmem + kT2 + acol, make_desc(y0 + ks * 2048, kRows * 128, 1024), kIdescAcc, accum);
+          if (KV_OWNER)
+            mma_ts(tmem + kAcc + D, tmem + acol, make_desc(y1 + ks * 2048, kRows * 128, 1024), kIdescAcc, accum);
+        }
+        tc_commit(&bars->y_empty[s]);
+      }
+      tc_commit(&bars->acc_done);
+    }
+    __syncwarp();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 512);
+}
+
+inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
+inline size_t ceil128(size_t x) { return (x + 127) / 128 * 128; }
+inline size_t staged_bytes(const Params& p, int len) { return align256((size_t)p.batch * p.heads * ceil128(len) * p.dk * 2); }
+inline size_t stats_bytes(const Params& p) { return align256((size_t)p.batch * p.heads * ceil128(p.lq) * 2 * sizeof(float)); }
+
+template <int D, bool KV_OWNER>
+cudaError_t launch_pairs(const Params& p, const uint8_t* wq, const uint8_t* wk, const uint8_t* wv,
+                         const uint8_t* wdo, const float* stats, float* dense0, float* dense1,
+                         cudaStream_t stream) {
+  const int nq = (p.lq + kRows - 1) / kRows, nk = (p.lk + kRows - 1) / kRows;
+  const int own_tiles = KV_OWNER ? nk : nq;
+  const int slices = p.heads * p.batch;
+  // slices whose streamed tiles (two arrays of len * D bf16) fit in about half of L2 run together
+  const size_t per_slice = (size_t)(KV_OWNER ? p.lq : p.lk) * D * 4;
+  int group = slices;
+  while (group > 1 && ((size_t)group * per_slice > ((size_t)72 << 20) || slices % group != 0)) --group;
+  const size_t smem = 6 * (size_t)kRows * D * 2 + sizeof(BwdBarriers) + 1024;
+  auto kern = tpa_bwd_sm100_kernel<D, KV_OWNER>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  kern<<<(unsigned)(own_tiles * slices), kThreads, smem, stream>>>(p, wq, wk, wv, wdo, stats, dense0, dense1,
+                                                                  own_tiles, group);
+  count_launch(1);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+bool bwd_sm100_supported(const BwdParams& bp) {
+  return sm100_supported(bp.f) && (reinterpret_cast<uintptr_t>(bp.d_o) & 15) == 0;
+}
+
+// statistics + staged Q, K, V, dO
+size_t bwd_sm100_workspace_bytes(const Params& p) {
+  return stats_bytes(p) + 2 * staged_bytes(p, p.lq) + 2 * staged_bytes(p, p.lk);
+}
+
+// dense dQ / dK / dV of the whole batch into bp.{dq,dk,dv}_dense: statistics, two staging
+// launches, the key-owner pass and the query-owner pass (five launches)
+cudaError_t launch_bwd_pairs_sm100(const BwdParams& bp, void* workspace, cudaStream_t stream) {
+  const Params& p = bp.f;
+  const int nq = (p.lq + kRows - 1) / kRows;
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  float* stats = reinterpret_cast<float*>(ws);
+  uint8_t* wq = ws + stats_bytes(p);
+  uint8_t* wdo = wq + staged_bytes(p, p.lq);
+  uint8_t* wk = wdo + staged_bytes(p, p.lq);
+  uint8_t* wv = wk + staged_bytes(p, p.lk);
+  const __nv_bfloat16* d_o = static_cast<const __nv_bfloat16*>(bp.d_o);
+
+  const int64_t warps = (int64_t)p.batch * nq * kRows * p.heads;
+  tpa_bwd_stats_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, stream>>>(p, d_o, stats, nq);
+  count_launch(1);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  const float qscale = p.sm_scale * kLog2e / ((float)p.rank_q * (float)p.rank_k);
+  e = launch_stage_tiles(p, wq, wk, wv, qscale, stream);
+  if (e != cudaSuccess) return e;
+  if (p.dk == 128) tpa_bwd_stage_do_kernel<128><<<dim3(nq, p.batch), 256, 0, stream>>>(p, d_o, wdo, nq);
+  else tpa_bwd_stage_do_kernel<64><<<dim3(nq, p.batch), 256, 0, stream>>>(p, d_o, wdo, nq);
+  count_launch(1);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  if (p.dk == 128) {
+    e = launch_pairs<128, true>(p, wq, wk, wv, wdo, stats, bp.dk_dense, bp.dv_dense, stream);
+    if (e == cudaSuccess) e = launch_pairs<128, false>(p, wq, wk, wv, wdo, stats, bp.dq_dense, nullptr, stream);
+  } else {
+    e = launch_pairs<64, true>(p, wq, wk, wv, wdo, stats, bp.dk_dense, bp.dv_dense, stream);
+    if (e == cudaSuccess) e = launch_pairs<64, false>(p, wq, wk, wv, wdo, stats, bp.dq_dense, nullptr, stream);
+  }
+  return e;
+}
+
+}  // namespace tpa

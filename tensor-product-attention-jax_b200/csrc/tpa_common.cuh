@@ -45,6 +45,12 @@ struct BwdParams {
 cudaError_t launch_bwd_delta(const BwdParams& bp, cudaStream_t stream);
 cudaError_t launch_bwd_pairs_simt(const BwdParams& bp, cudaStream_t stream);
 cudaError_t launch_bwd_contract(const BwdParams& bp, cudaStream_t stream);
+// tensor-core pair passes (bf16, head_dim 64 / 128): `workspace` holds bwd_sm100_workspace_bytes
+bool bwd_sm100_supported(const BwdParams& bp);
+size_t bwd_sm100_workspace_bytes(const Params& p);
+cudaError_t launch_bwd_pairs_sm100(const BwdParams& bp, void* workspace, cudaStream_t stream);
+cudaError_t launch_stage_tiles(const Params& p, uint8_t* wq, uint8_t* wk, uint8_t* wv, float qscale,
+                               cudaStream_t stream);
 
 // Launchers: enqueue on `stream`, return a cudaError_t.  `info` is filled either way.
 cudaError_t launch_simt(const Params& p, TpaKernelInfo* info, bool dry_run, cudaStream_t stream);

@@ -1113,6 +1113,18 @@ cudaError_t launch_attn(const Params& p, const uint8_t* wq, const uint8_t* wk, c
 
 }  // namespace
 
+// Rebuilds every 128-row tile of Q (times qscale), K and V of all heads into the three arrays
+// (the staging launch of the STAGED forward; the backward reads the same images).
+cudaError_t launch_stage_tiles(const Params& p, uint8_t* wq, uint8_t* wk, uint8_t* wv, float qscale,
+                               cudaStream_t stream) {
+  const int nq = (p.lq + kUnitRows - 1) / kUnitRows, nk = (p.lk + kTileKv - 1) / kTileKv;
+  dim3 sgrid(p.heads / 8, nq + 2 * nk, p.batch);
+  if (p.dk == 128) tpa_stage_tiles_kernel<128><<<sgrid, 256, 0, stream>>>(p, wq, wk, wv, qscale, 0);
+  else tpa_stage_tiles_kernel<64><<<sgrid, 256, 0, stream>>>(p, wq, wk, wv, qscale, 0);
+  count_launch(1);
+  return cudaGetLastError();
+}
+
 bool sm100_supported(const Params& p) {
   if (p.dtype != TPA_DTYPE_BF16) return false;
   if (p.dk != p.dv || (p.dk != 64 && p.dk != 128)) return false;

@@ -71,6 +71,16 @@ def device_status(device=None):
     return st, list(detail)
 
 
+def device_status_bwd(device=None):
+    """device_status for the backward's scratch (it keeps its own buffer)."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+    stream = torch.cuda.current_stream(device).cuda_stream
+    ws = _workspaces.get((device, stream, "bwd"))
+    detail = (C.c_uint32 * 4)()
+    st = _capi.lib.tpa_read_status(ws.data_ptr() if ws is not None else None, C.c_void_p(stream), C.byref(detail))
+    return st, list(detail)
+
+
 def _factor(x, col0):
     f = _capi.TpaFactor()
     f.ptr = x.data_ptr() + col0 * x.element_size()
@@ -230,8 +240,11 @@ def bwd_device(
     out=None,
     accumulate_dq=False,
     accumulate_dkv=False,
+    kernel="auto",
 ):
     """One tpa_bwd call on CUDA tensors; returns (dq, dk, dv) shaped like q, k, v.
+
+    `kernel`: "auto" (tensor cores when the shape allows, as for the forward), "simt" or "sm100".
 
     `o` and `lse` (fp32) are the forward's results, `do[b, lq, h, dv]` the incoming gradient.
     `grad_dtype` is q's dtype (default) or torch.float32; `out = (dq, dk, dv)` supplies the
@@ -257,7 +270,7 @@ def bwd_device(
     a.fwd.sm_scale = float(sm_scale)
     a.fwd.flags = _capi.FLAG_CAUSAL if causal else 0
     a.fwd.q_offset, a.fwd.k_offset = int(q_offset), int(k_offset)
-    a.fwd.kernel = _capi.KERNEL_AUTO
+    a.fwd.kernel = _capi.KERNELS[kernel]
     if out is None:
         if accumulate_dq or accumulate_dkv:
             raise ValueError("accumulating needs the buffers to add to (out=(dq, dk, dv))")

@@ -95,19 +95,19 @@ def test_backward_bf16_and_accumulation(causal):
     o, lse = tpa_b200.tpa.fwd_device(tq, tk, tv, h, None, None, d**-0.5, causal)
     f = lambda t: t.float().cpu().numpy()
     want = orc.tpa_bwd_reference(f(tq), f(tk), f(tv), f(do), h, None, None, d**-0.5, causal)
-    got = tpa_b200.tpa.bwd_device(tq, tk, tv, h, None, None, d**-0.5, causal, o, lse, do)
+    got = tpa_b200.tpa.bwd_device(tq, tk, tv, h, None, None, d**-0.5, causal, o, lse, do, kernel="simt")
     for g, w in zip(got, want):
         assert g.dtype == torch.bfloat16
         assert _rel(f(g), w) < 3e-2
     # fp32 gradients, added twice onto a known start
     bufs = tuple(torch.full(x.shape, 0.5, dtype=torch.float32, device="cuda") for x in (tq, tk, tv))
     for _ in range(2):
-        tpa_b200.tpa.bwd_device(tq, tk, tv, h, None, None, d**-0.5, causal, o, lse, do,
+        tpa_b200.tpa.bwd_device(tq, tk, tv, h, None, None, d**-0.5, causal, o, lse, do, kernel="simt",
                                 grad_dtype=torch.float32, out=bufs, accumulate_dq=True, accumulate_dkv=True)
     for g, w in zip(bufs, want):
         assert _rel((f(g) - 0.5) / 2, w) < 2e-2
     # overwriting ignores what the buffers held
-    tpa_b200.tpa.bwd_device(tq, tk, tv, h, None, None, d**-0.5, causal, o, lse, do,
+    tpa_b200.tpa.bwd_device(tq, tk, tv, h, None, None, d**-0.5, causal, o, lse, do, kernel="simt",
                             grad_dtype=torch.float32, out=bufs)
     for g, w in zip(bufs, want):
         assert _rel(f(g), w) < 2e-2
@@ -137,3 +137,54 @@ def test_backward_rejects_bad_arguments():
         tpa_b200.tpa.bwd_device(q, k, v, 2, None, None, 1.0, False, o, lse, o, grad_dtype=torch.bfloat16)
     with pytest.raises(ValueError):
         tpa_b200.tpa.bwd_device(q, k, v, 2, None, None, 1.0, False, o, lse, o, accumulate_dq=True)
+
+
+TC_CASES = [
+    # b, lq, lk, rq, rk, h, d, seg_q, seg_k, causal, q_off, k_off
+    (1, 128, 128, 2, 2, 8, 128, 0, 0, False, 0, 0),
+    (1, 256, 256, 2, 2, 8, 64, 0, 0, True, 0, 0),
+    (2, 384, 640, 3, 2, 8, 128, 0, 0, False, 0, 0),
+    (1, 512, 512, 6, 2, 16, 128, 0, 0, True, 0, 0),
+    (1, 300, 200, 2, 4, 8, 128, 0, 0, False, 0, 0),       # ragged last tiles
+    (2, 130, 260, 2, 2, 8, 64, 0, 0, True, 200, 0),       # ragged + offsets
+    (1, 256, 384, 2, 2, 8, 128, 0, 0, True, 128, 0),      # later query block of a ring
+    (1, 256, 256, 2, 2, 8, 128, 0, 0, True, 0, 100),      # rows that see no key
+    (1, 384, 512, 2, 2, 8, 128, 100, 100, True, 0, 0),    # packed sequences
+    (1, 256, 256, 1, 1, 8, 64, 32, 96, False, 0, 0),      # ids that leave rows empty
+]
+
+
+@pytest.mark.parametrize("case", TC_CASES)
+def test_tensor_core_backward(case):
+    """tcgen05 pair passes against the fp32 oracle on bf16-rounded inputs, and against the
+    SIMT passes on the same inputs."""
+    b, lq, lk, rq, rk, h, d, sq, sk, causal, q_off, k_off = case
+    q, k, v = orc.make_factors(21, b, lq, lk, rq, rk, h, d, d)
+    tq, tk, tv = (dev(x, torch.bfloat16) for x in (q, k, v))
+    do = dev(_do(21, (b, lq, h, d)), torch.bfloat16)
+    qs = orc.segment_ids(b, lq, sq) if sq else None
+    ks = orc.segment_ids(b, lk, sk) if sk else None
+    dqs, dks = (None if qs is None else dev(qs)), (None if ks is None else dev(ks))
+    scale = d**-0.5
+    o, lse = tpa_b200.tpa.fwd_device(tq, tk, tv, h, dqs, dks, scale, causal, q_offset=q_off, k_offset=k_off)
+    f = lambda t: t.float().cpu().numpy()
+    want = orc.tpa_bwd_reference(f(tq), f(tk), f(tv), f(do), h, qs, ks, scale, causal,
+                                 q_offset=q_off, k_offset=k_off)
+    n0 = _capi.lib.tpa_launch_count()
+    got = tpa_b200.tpa.bwd_device(tq, tk, tv, h, dqs, dks, scale, causal, o, lse, do, q_offset=q_off,
+                                  k_offset=k_off, kernel="sm100", grad_dtype=torch.float32)
+    assert _capi.lib.tpa_launch_count() == n0 + 8
+    st, detail = tpa_b200.tpa.device_status_bwd()
+    assert st == 0, detail
+    simt = tpa_b200.tpa.bwd_device(tq, tk, tv, h, dqs, dks, scale, causal, o, lse, do, q_offset=q_off,
+                                   k_offset=k_off, kernel="simt", grad_dtype=torch.float32)
+    for name, g, s_, w in zip(("dq", "dk", "dv"), got, simt, want):
+        g, s_ = f(g), f(s_)
+        assert np.isfinite(g).all(), name
+        assert _rel(g, w) < 3e-2, (name, _rel(g, w))
+        assert _rel(g, s_) < 2e-2, (name, _rel(g, s_))
+    # bitwise reproducible
+    again = tpa_b200.tpa.bwd_device(tq, tk, tv, h, dqs, dks, scale, causal, o, lse, do, q_offset=q_off,
+                                    k_offset=k_off, kernel="sm100", grad_dtype=torch.float32)
+    for g, a in zip(got, again):
+        assert torch.equal(g, a)
