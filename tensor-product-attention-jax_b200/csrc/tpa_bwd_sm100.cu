@@ -25,8 +25,9 @@
 // serves as a K-major operand of the first two GEMMs and as an MN-major operand of the
 // accumulating ones; only the descriptor differs.
 //
-// Roles, by warp: 0-7 element-wise (two threads per TMEM lane, 64 columns each) and the
-// epilogue; 8: one thread issues the bulk copies; 9: one thread issues tcgen05.mma.
+// Roles, by warp: 0-15 element-wise (four threads per TMEM lane, 32 columns each; the two column
+// halves of a tile are separate pipeline phases) and the epilogue; 16: one thread issues the
+// bulk copies; 17: one thread issues tcgen05.mma.
 // TMEM columns: T1 [0,128) (S, then p as bf16), T2 [128,256) (dP, then ds as bf16),
 // accumulators from 256 (dQ, or dK and dV).  Dense fp32 dQ / dK / dV go to scratch; the
 // factor contraction (tpa_bwd_contract_kernel) is shared with the SIMT path.
@@ -48,7 +49,7 @@ constexpr int kRows = 128;  // rows of every tile (queries or keys)
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr long long kWaitCycles = 1ll << 28;
-constexpr int kEwWarps = 8;
+constexpr int kEwWarps = 16;
 constexpr int kProducerWarp = kEwWarps;
 constexpr int kMmaWarp = kEwWarps + 1;
 constexpr int kThreads = (kMmaWarp + 1) * 32;
@@ -56,7 +57,7 @@ constexpr int kThreads = (kMmaWarp + 1) * 32;
 struct BwdBarriers {
   uint64_t x_full;                   // the CTA's own two tiles have landed
   uint64_t y_full[2], y_empty[2];    // streamed tiles (+ row statistics), double buffered
-  uint64_t t_full, p_ready, acc_done;
+  uint64_t t_full[2], p_ready[2], acc_done;  // per column half of T1 / T2
   uint32_t tmem_base;
   volatile uint32_t abort;
   alignas(16) float stats[2][2][kRows];  // [stage][log2e*lse | delta][query row] (KV_OWNER)
@@ -159,7 +160,7 @@ tpa_bwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
                      const uint8_t* ws_do, const float* stats, float* dense0, float* dense1,
                      const int own_tiles, const int group) {
   constexpr int kTileBytes = kRows * D * 2;
-  constexpr uint32_t kIdescT = make_idesc(128, kRows, false, false);
+  constexpr uint32_t kIdescT = make_idesc(128, 64, false, false);  // half a tile of moving rows
   constexpr uint32_t kIdescAcc = make_idesc(128, D, false, true);
   constexpr int kT2 = 128, kAcc = 256;
 
@@ -202,8 +203,10 @@ tpa_bwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
       mbar_init(&bars->y_full[s], 1);
       mbar_init(&bars->y_empty[s], 1);
     }
-    mbar_init(&bars->t_full, 1);
-    mbar_init(&bars->p_ready, kEwWarps);
+    for (int h = 0; h < 2; ++h) {
+      mbar_init(&bars->t_full[h], 1);
+      mbar_init(&bars->p_ready[h], kEwWarps / 2);
+    }
     mbar_init(&bars->acc_done, 1);
     bars->abort = 0;
     fence_mbar_init();
@@ -221,11 +224,14 @@ tpa_bwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
 
   if (warp < kEwWarps) {
     // ------------------------------------------------------------------ element-wise + epilogue
-    const int quarter = warp & 3, half = warp >> 2;
+    // Four threads per TMEM lane: warp w serves lanes 32 (w & 3)... and the 32 columns
+    // (moving rows) 32 (w >> 2)...; column halves [0,64) and [64,128) are separate phases with
+    // their own barriers, so that the MMAs of one half run under the arithmetic of the other.
+    const int quarter = warp & 3, colq = warp >> 2, hf = colq >> 1;
     const int row = quarter * 32 + lane;  // TMEM lane = row of the own tile
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-    const uint32_t tT1 = tmem + lane_base + half * 64;
-    const uint32_t tT2 = tmem + lane_base + kT2 + half * 64;
+    const uint32_t tT1 = tmem + lane_base + colq * 32;
+    const uint32_t tT2 = tmem + lane_base + kT2 + colq * 32;
     const int own_idx = own0 + row;
     const bool own_ok = own_idx < (KV_OWNER ? p.lk : p.lq);
     const int64_t own_pos = (int64_t)own_idx + (KV_OWNER ? p.k_offset : p.q_offset);
@@ -250,34 +256,34 @@ tpa_bwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
 
     for (int n = 0; n < n_tiles; ++n) {
       const int s = n & 1;
-      const int m0 = (t_lo + n) * kRows + half * 64;  // first moving row of this thread's columns
-      wait(&bars->t_full, n & 1, 0x100);
+      const int m0 = (t_lo + n) * kRows + colq * 32;  // first moving row of this thread's columns
+      wait(&bars->t_full[hf], n & 1, 0x100 + hf);
       tc_fence_after();
-      if (KV_OWNER) wait(&bars->y_full[s], (n >> 1) & 1, 0x101);  // the statistics have landed
-      const float* sl2 = bars->stats[s][0] + half * 64;
-      const float* sdl = bars->stats[s][1] + half * 64;
-      // does any pair of these 32 lanes x 64 columns need the element-wise test?
+      if (KV_OWNER) wait(&bars->y_full[s], (n >> 1) & 1, 0x102);  // the statistics have landed
+      const float* sl2 = bars->stats[s][0] + colq * 32;
+      const float* sdl = bars->stats[s][1] + colq * 32;
+      // does any pair of these 32 lanes x 32 columns need the element-wise test?
       bool masked = has_seg;
       if (causal) {
         const int64_t lane0_pos = (int64_t)own0 + quarter * 32 + (KV_OWNER ? p.k_offset : p.q_offset);
         if (KV_OWNER) masked = masked || ((int64_t)m0 + mov_off < lane0_pos + 31);      // min q < max key
-        else masked = masked || ((int64_t)m0 + 63 + mov_off > lane0_pos);                // max key > min q
+        else masked = masked || ((int64_t)m0 + 31 + mov_off > lane0_pos);                // max key > min q
       }
-      if (!KV_OWNER) masked = masked || (m0 + 64 > p.lk);  // padded keys of a ragged last tile
+      if (!KV_OWNER) masked = masked || (m0 + 32 > p.lk);  // padded keys of a ragged last tile
 
-      uint32_t ppk[32], dpk[32];
+      uint32_t ppk[16], dpk[16];
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
-        uint32_t t1[32], t2[32];
-        tmem_ld32(tT1 + c * 32, t1);
-        tmem_ld32(tT2 + c * 32, t2);
+        uint32_t t1[16], t2[16];
+        tmem_ld16(tT1 + c * 16, t1);
+        tmem_ld16(tT2 + c * 16, t2);
         tmem_ld_wait();
 #pragma unroll
-        for (int e = 0; e < 32; e += 2) {
+        for (int e = 0; e < 16; e += 2) {
           float pe[2], de[2];
 #pragma unroll
           for (int k = 0; k < 2; ++k) {
-            const int col = c * 32 + e + k;
+            const int col = c * 16 + e + k;
             const float l2 = KV_OWNER ? sl2[col] : my_l2;
             const float dl = KV_OWNER ? sdl[col] : my_dl;
             float pr = ex2(__uint_as_float(t1[e + k]) - l2);
@@ -292,18 +298,18 @@ tpa_bwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
             pe[k] = pr;
             de[k] = pr * fmaf(__uint_as_float(t2[e + k]), inv_rk, -dl);
           }
-          ppk[c * 16 + e / 2] = pack_bf16(pe[0], pe[1]);
-          dpk[c * 16 + e / 2] = pack_bf16(de[0], de[1]);
+          ppk[c * 8 + e / 2] = pack_bf16(pe[0], pe[1]);
+          dpk[c * 8 + e / 2] = pack_bf16(de[0], de[1]);
         }
       }
-      // bf16 p / ds of this half overwrite the first 32 columns of its own 64 fp32 columns:
-      // moving row k of the tile is at column (k / 64) * 64 + (k % 64) / 2 of T1 / T2
-      if (KV_OWNER) tmem_st32(tT1, ppk);
-      tmem_st32(tT2, dpk);
+      // bf16 p / ds overwrite the first 16 of the thread's own 32 fp32 columns: moving row k of
+      // the tile is at column (k / 32) * 32 + (k % 32) / 2 of T1 / T2
+      if (KV_OWNER) tmem_st16(tT1, ppk);
+      tmem_st16(tT2, dpk);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->p_ready);
+      if (lane == 0) mbar_arrive(&bars->p_ready[hf]);
     }
 
     // epilogue: accumulators -> dense fp32 rows (zeros when nothing was visible)
@@ -316,22 +322,22 @@ tpa_bwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
 #pragma unroll
     for (int a = 0; a < (KV_OWNER ? 2 : 1); ++a) {
       float* dst = (a == 0 ? dense0 : dense1) +
-                   (((int64_t)batch * own_len + own_idx) * p.heads + head) * D + half * (D / 2);
+                   (((int64_t)batch * own_len + own_idx) * p.heads + head) * D + colq * (D / 4);
       const float scale = a == 0 ? scale0 : 1.f;
 #pragma unroll
       for (int c = 0; c < D / 64; ++c) {
-        uint32_t r[32];
+        uint32_t r[16];
         if (n_tiles > 0) {
-          tmem_ld32(tmem + lane_base + kAcc + a * D + half * (D / 2) + c * 32, r);
+          tmem_ld16(tmem + lane_base + kAcc + a * D + colq * (D / 4) + c * 16, r);
           tmem_ld_wait();
         } else {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) r[e] = 0u;
+          for (int e = 0; e < 16; ++e) r[e] = 0u;
         }
         if (own_ok) {
 #pragma unroll
-          for (int e = 0; e < 32; e += 4)
-            *reinterpret_cast<float4*>(dst + c * 32 + e) =
+          for (int e = 0; e < 16; e += 4)
+            *reinterpret_cast<float4*>(dst + c * 16 + e) =
                 make_float4(__uint_as_float(r[e]) * scale, __uint_as_float(r[e + 1]) * scale,
                             __uint_as_float(r[e + 2]) * scale, __uint_as_float(r[e + 3]) * scale);
         }
@@ -363,34 +369,58 @@ tpa_bwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
     // ------------------------------------------------------------------ MMA issue (one thread)
     if (lane == 0 && n_tiles > 0) {
       const uint32_t aX = smem_u32(sX), aY = smem_u32(sY);
-      wait(&bars->x_full, 0, 0x600);
-      tc_fence_after();
-      for (int n = 0; n < n_tiles; ++n) {
-        const int s = n & 1;
-        const uint32_t y0 = aY + s * 2 * kTileBytes, y1 = y0 + kTileBytes;
-        wait(&bars->y_full[s], (n >> 1) & 1, 0x601);
-        tc_fence_after();
+      // T1 / T2 columns [64 h, 64 h + 64) of tile n: own0 moving0[64 h ...]^T and own1 moving1[...]^T
+      auto issue_t = [&](int n, int h) {
+        const uint32_t yb0 = aY + (n & 1) * 2 * kTileBytes + h * 64 * 128;  // rows 64 h ... of each sub-tile
 #pragma unroll
         for (int g = 0; g < 2; ++g) {
-          const uint32_t xb = aX + g * kTileBytes, yb = g == 0 ? y0 : y1;
+          const uint32_t xb = aX + g * kTileBytes, yb = yb0 + g * kTileBytes;
 #pragma unroll
           for (int ks = 0; ks < D / 16; ++ks) {
             const uint32_t off = (ks >> 2) * (kRows * 128) + (ks & 3) * 32;
-            mma_ss(tmem + g * kT2, make_desc(xb + off, 16, 1024), make_desc(yb + off, 16, 1024), kIdescT, ks > 0);
+            mma_ss(tmem + g * kT2 + h * 64, make_desc(xb + off, 16, 1024), make_desc(yb + off, 16, 1024),
+                   kIdescT, ks > 0);
           }
         }
-        tc_commit(&bars->t_full);
-        wait(&bars->p_ready, n & 1, 0x610);
-        tc_fence_after();
+        tc_commit(&bars->t_full[h]);
+      };
+      // accumulators += (ds | p)[:, 64 h ...] moving[64 h ...]: four K steps of 16 moving rows
+      auto issue_acc = [&](int n, int h) {
+        const uint32_t y0 = aY + (n & 1) * 2 * kTileBytes, y1 = y0 + kTileBytes;
 #pragma unroll
-        for (int ks = 0; ks < kRows / 16; ++ks) {
-          const uint32_t acol = (ks >> 2) * 64 + (ks & 3) * 8;
+        for (int ks = h * 4; ks < h * 4 + 4; ++ks) {
+          const uint32_t acol = (ks >> 1) * 32 + (ks & 1) * 8;  // where the element-wise role put row 16 ks
           const uint32_t accum = (n > 0 || ks > 0) ? 1u : 0u;
           mma_ts(tmem + kAcc, tmem + kT2 + acol, make_desc(y0 + ks * 2048, kRows * 128, 1024), kIdescAcc, accum);
           if (KV_OWNER)
             mma_ts(tmem + kAcc + D, tmem + acol, make_desc(y1 + ks * 2048, kRows * 128, 1024), kIdescAcc, accum);
         }
-        tc_commit(&bars->y_empty[s]);
+      };
+      // Order: T(n,0) T(n,1) | acc(n,0) T(n+1,0) | acc(n,1) T(n+1,1) | ...  T(n+1,h) overwrites the
+      // columns acc(n,h) reads; the tensor pipe executes in issue order, so that is safe, and the
+      // element-wise warps of half h get their next input as early as the TMEM budget allows.
+      wait(&bars->x_full, 0, 0x600);
+      tc_fence_after();
+      wait(&bars->y_full[0], 0, 0x601);
+      tc_fence_after();
+      issue_t(0, 0);
+      issue_t(0, 1);
+      for (int n = 0; n < n_tiles; ++n) {
+        const bool more = n + 1 < n_tiles;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          wait(&bars->p_ready[h], n & 1, 0x610 + h);
+          tc_fence_after();
+          issue_acc(n, h);
+          if (more) {
+            if (h == 0) {
+              wait(&bars->y_full[(n + 1) & 1], ((n + 1) >> 1) & 1, 0x602);
+              tc_fence_after();
+            }
+            issue_t(n + 1, h);
+          }
+        }
+        tc_commit(&bars->y_empty[n & 1]);
       }
       tc_commit(&bars->acc_done);
     }
