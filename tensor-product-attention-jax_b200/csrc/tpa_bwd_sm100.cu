@@ -25,8 +25,8 @@
 // serves as a K-major operand of the first two GEMMs and as an MN-major operand of the
 // accumulating ones; only the descriptor differs.
 //
-// Roles, by warp: 0-15 element-wise (four threads per TMEM lane, 32 columns each; the two column
-// halves of a tile are separate pipeline phases) and the epilogue; 16: one thread issues the
+// Roles, by warp: 0-15 element-wise (four threads per TMEM lane; the two 64-column halves of a
+// tile are separate pipeline phases, each worked on by all 16 warps) and the epilogue; 16: one thread issues the
 // bulk copies; 17: one thread issues tcgen05.mma.
 // TMEM columns: T1 [0,128) (S, then p as bf16), T2 [128,256) (dP, then ds as bf16),
 // accumulators from 256 (dQ, or dK and dV).  Dense fp32 dQ / dK / dV go to scratch; the
@@ -56,11 +56,11 @@ constexpr int kThreads = (kMmaWarp + 1) * 32;
 
 struct BwdBarriers {
   uint64_t x_full;                   // the CTA's own two tiles have landed
-  uint64_t y_full[2], y_empty[2];    // streamed tiles (+ row statistics), double buffered
+  uint64_t y_full[3], y_empty[3];    // streamed tiles (+ row statistics), two or three stages
   uint64_t t_full[2], p_ready[2], acc_done;  // per column half of T1 / T2
   uint32_t tmem_base;
   volatile uint32_t abort;
-  alignas(16) float stats[2][2][kRows];  // [stage][log2e*lse | delta][query row] (KV_OWNER)
+  alignas(16) float stats[3][2][kRows];  // [stage][log2e*lse | delta][query row] (KV_OWNER)
 };
 
 struct BoundedWait {
@@ -160,16 +160,25 @@ tpa_bwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
                      const uint8_t* ws_do, const float* stats, float* dense0, float* dense1,
                      const int own_tiles, const int group) {
   constexpr int kTileBytes = kRows * D * 2;
-  constexpr uint32_t kIdescT = make_idesc(128, 64, false, false);  // half a tile of moving rows
+  constexpr uint32_t kIdescT = make_idesc(128, kRows, false, false);
   constexpr uint32_t kIdescAcc = make_idesc(128, D, false, true);
   constexpr int kT2 = 128, kAcc = 256;
+  // Where TMEM has room (all but the key-owner pass at head_dim 128) the CTA's own two tiles live
+  // there as the A operands of the first two GEMMs: an operand in TMEM is not re-read from shared
+  // memory by every MMA (an M128 N128 K16 MMA with both operands in shared memory needs all of
+  // its 128 B/clk, leaving nothing for the bulk copies), and the 2 tiles of shared memory it
+  // frees hold a third stage of streamed tiles.
+  constexpr bool kOwnTmem = !KV_OWNER || D == 64;
+  constexpr int kStages = kOwnTmem ? 3 : 2;
+  constexpr int kOwnCol = kAcc + (KV_OWNER ? 2 : 1) * D;  // own tile g: columns kOwnCol + g * D/2
+  static_assert(kOwnCol + (kOwnTmem ? D : 0) <= 512, "TMEM budget");
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint8_t* sX = smem;                   // own tiles: [0] K or Q, [1] V or dO
-  uint8_t* sY = smem + 2 * kTileBytes;  // moving tiles: stage s at s * 2 tiles: [0] Q or K, [1] dO or V
-  BwdBarriers* bars = reinterpret_cast<BwdBarriers*>(smem + 6 * kTileBytes);
+  uint8_t* sX = smem;                   // own tiles (unless in TMEM): [0] K or Q, [1] V or dO
+  uint8_t* sY = smem + (kOwnTmem ? 0 : 2) * kTileBytes;  // moving tiles: stage s at s * 2 tiles: [0] Q or K, [1] dO or V
+  BwdBarriers* bars = reinterpret_cast<BwdBarriers*>(sY + kStages * 2 * kTileBytes);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nq = (p.lq + kRows - 1) / kRows, nk = (p.lk + kRows - 1) / kRows;
@@ -198,14 +207,14 @@ tpa_bwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
   const int n_tiles = max(0, t_hi - t_lo);
 
   if (threadIdx.x == 0) {
-    mbar_init(&bars->x_full, 1);
-    for (int s = 0; s < 2; ++s) {
+    mbar_init(&bars->x_full, kOwnTmem ? kEwWarps : 1);
+    for (int s = 0; s < kStages; ++s) {
       mbar_init(&bars->y_full[s], 1);
       mbar_init(&bars->y_empty[s], 1);
     }
     for (int h = 0; h < 2; ++h) {
       mbar_init(&bars->t_full[h], 1);
-      mbar_init(&bars->p_ready[h], kEwWarps / 2);
+      mbar_init(&bars->p_ready[h], kEwWarps);
     }
     mbar_init(&bars->acc_done, 1);
     bars->abort = 0;
@@ -224,14 +233,13 @@ tpa_bwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
 
   if (warp < kEwWarps) {
     // ------------------------------------------------------------------ element-wise + epilogue
-    // Four threads per TMEM lane: warp w serves lanes 32 (w & 3)... and the 32 columns
-    // (moving rows) 32 (w >> 2)...; column halves [0,64) and [64,128) are separate phases with
-    // their own barriers, so that the MMAs of one half run under the arithmetic of the other.
-    const int quarter = warp & 3, colq = warp >> 2, hf = colq >> 1;
+    // Four threads per TMEM lane: warp w serves lanes 32 (w & 3)... and, in each column half
+    // [64 h, 64 h + 64) of a tile, the 16 columns (moving rows) 64 h + 16 (w >> 2)...  The halves
+    // are separate pipeline phases with their own barriers: all 16 warps work on one half while
+    // the tensor pipe consumes the other.
+    const int quarter = warp & 3, cq = warp >> 2;
     const int row = quarter * 32 + lane;  // TMEM lane = row of the own tile
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-    const uint32_t tT1 = tmem + lane_base + colq * 32;
-    const uint32_t tT2 = tmem + lane_base + kT2 + colq * 32;
     const int own_idx = own0 + row;
     const bool own_ok = own_idx < (KV_OWNER ? p.lk : p.lq);
     const int64_t own_pos = (int64_t)own_idx + (KV_OWNER ? p.k_offset : p.q_offset);
@@ -253,40 +261,75 @@ tpa_bwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
       my_dl = st[kRows + row];
     }
     const float inv_rk = 1.f / (float)p.rank_k;
+    const int64_t lane0_pos = (int64_t)own0 + quarter * 32 + (KV_OWNER ? p.k_offset : p.q_offset);
+
+    if (kOwnTmem && n_tiles > 0) {
+      // own tiles -> TMEM in the layout of a tcgen05.mma A operand: lane = row, one 32-bit column
+      // per two consecutive bf16 of the row.  Read straight from the staged (swizzled) images.
+#pragma unroll
+      for (int g = 0; g < 2; ++g) {
+        const uint8_t* src = KV_OWNER ? (g == 0 ? ws_k : ws_v) + (bh * nk + own) * kTileBytes
+                                      : (g == 0 ? ws_q : ws_do) + (bh * nq + own) * kTileBytes;
+#pragma unroll
+        for (int i = 0; i < D / 64; ++i) {  // this thread: D/4 elements = D/32 chunks of 16 bytes, 4 at a time
+          uint32_t w[8];
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            const int chunk = cq * (D / 32) + i * 2 + j;
+            const uint4 v = __ldg(reinterpret_cast<const uint4*>(src + (chunk >> 3) * (kRows * 128) +
+                                                                 sw128_offset(row, chunk & 7)));
+            w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
+          }
+          tmem_st8(tmem + lane_base + kOwnCol + g * (D / 2) + cq * (D / 8) + i * 8, w);
+        }
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->x_full);
+    }
 
     for (int n = 0; n < n_tiles; ++n) {
-      const int s = n & 1;
-      const int m0 = (t_lo + n) * kRows + colq * 32;  // first moving row of this thread's columns
-      wait(&bars->t_full[hf], n & 1, 0x100 + hf);
-      tc_fence_after();
-      if (KV_OWNER) wait(&bars->y_full[s], (n >> 1) & 1, 0x102);  // the statistics have landed
-      const float* sl2 = bars->stats[s][0] + colq * 32;
-      const float* sdl = bars->stats[s][1] + colq * 32;
-      // does any pair of these 32 lanes x 32 columns need the element-wise test?
-      bool masked = has_seg;
-      if (causal) {
-        const int64_t lane0_pos = (int64_t)own0 + quarter * 32 + (KV_OWNER ? p.k_offset : p.q_offset);
-        if (KV_OWNER) masked = masked || ((int64_t)m0 + mov_off < lane0_pos + 31);      // min q < max key
-        else masked = masked || ((int64_t)m0 + 31 + mov_off > lane0_pos);                // max key > min q
-      }
-      if (!KV_OWNER) masked = masked || (m0 + 32 > p.lk);  // padded keys of a ragged last tile
-
-      uint32_t ppk[16], dpk[16];
+      const int s = n % kStages;
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t t1[16], t2[16];
-        tmem_ld16(tT1 + c * 16, t1);
-        tmem_ld16(tT2 + c * 16, t2);
+      for (int h = 0; h < 2; ++h) {
+        const int c0 = h * 64 + cq * 16;               // this thread's 16 columns of the half
+        const int m0 = (t_lo + n) * kRows + c0;        // their first moving row
+        wait(&bars->t_full[h], n & 1, 0x100 + h);
+        tc_fence_after();
+        if (KV_OWNER && h == 0) wait(&bars->y_full[s], (n / kStages) & 1, 0x102);  // the statistics have landed
+        // does any pair of these 32 lanes x 16 columns need the element-wise test?
+        bool masked = has_seg;
+        if (causal) {
+          if (KV_OWNER) masked = masked || ((int64_t)m0 + mov_off < lane0_pos + 31);  // min q < max key
+          else masked = masked || ((int64_t)m0 + 15 + mov_off > lane0_pos);            // max key > min q
+        }
+        if (!KV_OWNER) masked = masked || (m0 + 16 > p.lk);  // padded keys of a ragged last tile
+
+        uint32_t t1[16], t2[16], ppk[8], dpk[8];
+        tmem_ld16(tmem + lane_base + c0, t1);
+        tmem_ld16(tmem + lane_base + kT2 + c0, t2);
+        float l2v[16], dlv[16];
+        if (KV_OWNER) {
+          const float4* a4 = reinterpret_cast<const float4*>(bars->stats[s][0] + c0);
+          const float4* b4 = reinterpret_cast<const float4*>(bars->stats[s][1] + c0);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float4 a = a4[i], b = b4[i];
+            l2v[4 * i] = a.x; l2v[4 * i + 1] = a.y; l2v[4 * i + 2] = a.z; l2v[4 * i + 3] = a.w;
+            dlv[4 * i] = b.x; dlv[4 * i + 1] = b.y; dlv[4 * i + 2] = b.z; dlv[4 * i + 3] = b.w;
+          }
+        }
         tmem_ld_wait();
 #pragma unroll
         for (int e = 0; e < 16; e += 2) {
           float pe[2], de[2];
 #pragma unroll
           for (int k = 0; k < 2; ++k) {
-            const int col = c * 16 + e + k;
-            const float l2 = KV_OWNER ? sl2[col] : my_l2;
-            const float dl = KV_OWNER ? sdl[col] : my_dl;
-            float pr = ex2(__uint_as_float(t1[e + k]) - l2);
+            const int col = e + k;
+            const float l2 = KV_OWNER ? l2v[col] : my_l2;
+            const float dl = KV_OWNER ? dlv[col] : my_dl;
+            float pr = ex2(__uint_as_float(t1[col]) - l2);
             if (masked) {
               const int mi = m0 + col;
               const int64_t mpos = (int64_t)mi + mov_off;
@@ -296,20 +339,20 @@ tpa_bwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
               if (!keep) pr = 0.f;
             }
             pe[k] = pr;
-            de[k] = pr * fmaf(__uint_as_float(t2[e + k]), inv_rk, -dl);
+            de[k] = pr * fmaf(__uint_as_float(t2[col]), inv_rk, -dl);
           }
-          ppk[c * 8 + e / 2] = pack_bf16(pe[0], pe[1]);
-          dpk[c * 8 + e / 2] = pack_bf16(de[0], de[1]);
+          ppk[e / 2] = pack_bf16(pe[0], pe[1]);
+          dpk[e / 2] = pack_bf16(de[0], de[1]);
         }
+        // bf16 p / ds overwrite the first 8 of the thread's own 16 fp32 columns: moving row k of
+        // the tile is at column (k / 16) * 16 + (k % 16) / 2 of T1 / T2
+        if (KV_OWNER) tmem_st8(tmem + lane_base + c0, ppk);
+        tmem_st8(tmem + lane_base + kT2 + c0, dpk);
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->p_ready[h]);
       }
-      // bf16 p / ds overwrite the first 16 of the thread's own 32 fp32 columns: moving row k of
-      // the tile is at column (k / 32) * 32 + (k % 32) / 2 of T1 / T2
-      if (KV_OWNER) tmem_st16(tT1, ppk);
-      tmem_st16(tT2, dpk);
-      tmem_st_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->p_ready[hf]);
     }
 
     // epilogue: accumulators -> dense fp32 rows (zeros when nothing was visible)
@@ -322,13 +365,13 @@ tpa_bwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
 #pragma unroll
     for (int a = 0; a < (KV_OWNER ? 2 : 1); ++a) {
       float* dst = (a == 0 ? dense0 : dense1) +
-                   (((int64_t)batch * own_len + own_idx) * p.heads + head) * D + colq * (D / 4);
+                   (((int64_t)batch * own_len + own_idx) * p.heads + head) * D + cq * (D / 4);
       const float scale = a == 0 ? scale0 : 1.f;
 #pragma unroll
       for (int c = 0; c < D / 64; ++c) {
         uint32_t r[16];
         if (n_tiles > 0) {
-          tmem_ld16(tmem + lane_base + kAcc + a * D + colq * (D / 4) + c * 16, r);
+          tmem_ld16(tmem + lane_base + kAcc + a * D + cq * (D / 4) + c * 16, r);
           tmem_ld_wait();
         } else {
 #pragma unroll
@@ -348,13 +391,15 @@ tpa_bwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
     if (lane == 0 && n_tiles > 0) {  // every copy issued here is waited for by the MMA thread
       const uint8_t* gx0 = (KV_OWNER ? ws_k + (bh * nk + own) * kTileBytes : ws_q + (bh * nq + own) * kTileBytes);
       const uint8_t* gx1 = (KV_OWNER ? ws_v + (bh * nk + own) * kTileBytes : ws_do + (bh * nq + own) * kTileBytes);
-      mbar_arrive_expect_tx(&bars->x_full, 2 * kTileBytes);
-      bulk_g2s(sX, gx0, kTileBytes, &bars->x_full);
-      bulk_g2s(sX + kTileBytes, gx1, kTileBytes, &bars->x_full);
+      if (!kOwnTmem) {
+        mbar_arrive_expect_tx(&bars->x_full, 2 * kTileBytes);
+        bulk_g2s(sX, gx0, kTileBytes, &bars->x_full);
+        bulk_g2s(sX + kTileBytes, gx1, kTileBytes, &bars->x_full);
+      }
       for (int n = 0; n < n_tiles; ++n) {
-        const int s = n & 1;
+        const int s = n % kStages;
         const int64_t t = t_lo + n;
-        if (n >= 2) wait(&bars->y_empty[s], ((n >> 1) - 1) & 1, 0x400);
+        if (n >= kStages) wait(&bars->y_empty[s], ((n / kStages) - 1) & 1, 0x400);
         const uint8_t* gy0 = KV_OWNER ? ws_q + (bh * nq + t) * kTileBytes : ws_k + (bh * nk + t) * kTileBytes;
         const uint8_t* gy1 = KV_OWNER ? ws_do + (bh * nq + t) * kTileBytes : ws_v + (bh * nk + t) * kTileBytes;
         mbar_arrive_expect_tx(&bars->y_full[s], 2 * kTileBytes + (KV_OWNER ? 2 * kRows * 4 : 0));
@@ -369,42 +414,57 @@ tpa_bwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
     // ------------------------------------------------------------------ MMA issue (one thread)
     if (lane == 0 && n_tiles > 0) {
       const uint32_t aX = smem_u32(sX), aY = smem_u32(sY);
-      // T1 / T2 columns [64 h, 64 h + 64) of tile n: own0 moving0[64 h ...]^T and own1 moving1[...]^T
+      // Descriptors are built once; an MMA then only adds its byte offset (>> 4) to the address field.
+      const uint64_t dX0 = make_desc(aX, 16, 1024), dX1 = make_desc(aX + kTileBytes, 16, 1024);
+      const uint64_t dYk0 = make_desc(aY, 16, 1024);            // moving tiles as K-major operands
+      const uint64_t dYm0 = make_desc(aY, kRows * 128, 1024);   // ... and as MN-major operands
+      constexpr uint32_t kIdescHalf = make_idesc(128, 64, false, false);
+      auto stage_off = [&](int n) { return (uint32_t)(((n % kStages) * 2 * kTileBytes) >> 4); };
+      // T1 = own0 moving0^T, T2 = own1 moving1^T of tile n.
+      //  own tiles in TMEM: one column half (64 moving rows) at a time, so that T(n+1,h) can follow
+      //  acc(n,h) at once; own tiles in shared memory: the whole tile (at N = 64 the A operand
+      //  would be re-read from shared memory twice as often).
       auto issue_t = [&](int n, int h) {
-        const uint32_t yb0 = aY + (n & 1) * 2 * kTileBytes + h * 64 * 128;  // rows 64 h ... of each sub-tile
 #pragma unroll
         for (int g = 0; g < 2; ++g) {
-          const uint32_t xb = aX + g * kTileBytes, yb = yb0 + g * kTileBytes;
+          const uint64_t dy = dYk0 + stage_off(n) + ((g * kTileBytes) >> 4) + (kOwnTmem ? (h * 64 * 128) >> 4 : 0);
 #pragma unroll
           for (int ks = 0; ks < D / 16; ++ks) {
-            const uint32_t off = (ks >> 2) * (kRows * 128) + (ks & 3) * 32;
-            mma_ss(tmem + g * kT2 + h * 64, make_desc(xb + off, 16, 1024), make_desc(yb + off, 16, 1024),
-                   kIdescT, ks > 0);
+            const uint32_t off = ((ks >> 2) * (kRows * 128) + (ks & 3) * 32) >> 4;
+            if (kOwnTmem)
+              mma_ts(tmem + g * kT2 + h * 64, tmem + kOwnCol + g * (D / 2) + ks * 8, dy + off, kIdescHalf, ks > 0);
+            else
+              mma_ss(tmem + g * kT2, (g == 0 ? dX0 : dX1) + off, dy + off, kIdescT, ks > 0);
           }
         }
-        tc_commit(&bars->t_full[h]);
+        if (kOwnTmem) {
+          tc_commit(&bars->t_full[h]);
+        } else {
+          tc_commit(&bars->t_full[0]);
+          tc_commit(&bars->t_full[1]);
+        }
       };
       // accumulators += (ds | p)[:, 64 h ...] moving[64 h ...]: four K steps of 16 moving rows
       auto issue_acc = [&](int n, int h) {
-        const uint32_t y0 = aY + (n & 1) * 2 * kTileBytes, y1 = y0 + kTileBytes;
+        const uint64_t dy0 = dYm0 + stage_off(n), dy1 = dy0 + (kTileBytes >> 4);
 #pragma unroll
         for (int ks = h * 4; ks < h * 4 + 4; ++ks) {
-          const uint32_t acol = (ks >> 1) * 32 + (ks & 1) * 8;  // where the element-wise role put row 16 ks
+          const uint32_t acol = ks * 16;  // where the element-wise role put rows 16 ks ... 16 ks + 15
           const uint32_t accum = (n > 0 || ks > 0) ? 1u : 0u;
-          mma_ts(tmem + kAcc, tmem + kT2 + acol, make_desc(y0 + ks * 2048, kRows * 128, 1024), kIdescAcc, accum);
-          if (KV_OWNER)
-            mma_ts(tmem + kAcc + D, tmem + acol, make_desc(y1 + ks * 2048, kRows * 128, 1024), kIdescAcc, accum);
+          mma_ts(tmem + kAcc, tmem + kT2 + acol, dy0 + ((ks * 2048) >> 4), kIdescAcc, accum);
+          if (KV_OWNER) mma_ts(tmem + kAcc + D, tmem + acol, dy1 + ((ks * 2048) >> 4), kIdescAcc, accum);
         }
       };
-      // Order: T(n,0) T(n,1) | acc(n,0) T(n+1,0) | acc(n,1) T(n+1,1) | ...  T(n+1,h) overwrites the
-      // columns acc(n,h) reads; the tensor pipe executes in issue order, so that is safe, and the
-      // element-wise warps of half h get their next input as early as the TMEM budget allows.
+      // Order, own tiles in TMEM:   T(0,0) T(0,1) | acc(n,0) T(n+1,0) | acc(n,1) T(n+1,1) | ...
+      //        own tiles in smem:   T(0) | acc(n,0) | acc(n,1) | T(n+1) | ...
+      // T(n+1,.) overwrites the columns acc(n,.) reads; the tensor pipe executes in issue order, so
+      // that is safe.  The element-wise warps work on one column half while the pipe consumes the other.
       wait(&bars->x_full, 0, 0x600);
       tc_fence_after();
       wait(&bars->y_full[0], 0, 0x601);
       tc_fence_after();
       issue_t(0, 0);
-      issue_t(0, 1);
+      if (kOwnTmem) issue_t(0, 1);
       for (int n = 0; n < n_tiles; ++n) {
         const bool more = n + 1 < n_tiles;
 #pragma unroll
@@ -412,15 +472,15 @@ tpa_bwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
           wait(&bars->p_ready[h], n & 1, 0x610 + h);
           tc_fence_after();
           issue_acc(n, h);
-          if (more) {
-            if (h == 0) {
-              wait(&bars->y_full[(n + 1) & 1], ((n + 1) >> 1) & 1, 0x602);
+          if (more && (kOwnTmem || h == 1)) {
+            if (h == 0 || !kOwnTmem) {
+              wait(&bars->y_full[(n + 1) % kStages], ((n + 1) / kStages) & 1, 0x602);
               tc_fence_after();
             }
             issue_t(n + 1, h);
           }
+          if (h == 1) tc_commit(&bars->y_empty[n % kStages]);
         }
-        tc_commit(&bars->y_empty[n & 1]);
       }
       tc_commit(&bars->acc_done);
     }
@@ -448,7 +508,7 @@ cudaError_t launch_pairs(const Params& p, const uint8_t* wq, const uint8_t* wk, 
   const size_t per_slice = (size_t)(KV_OWNER ? p.lq : p.lk) * D * 4;
   int group = slices;
   while (group > 1 && ((size_t)group * per_slice > ((size_t)72 << 20) || slices % group != 0)) --group;
-  const size_t smem = 6 * (size_t)kRows * D * 2 + sizeof(BwdBarriers) + 1024;
+  const size_t smem = 6 * (size_t)kRows * D * 2 + sizeof(BwdBarriers) + 1024;  // 2 own + 2 x 2 streamed tiles, or 3 x 2 streamed
   auto kern = tpa_bwd_sm100_kernel<D, KV_OWNER>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
