@@ -200,6 +200,9 @@ def main():
     ap.add_argument("--kernel", default="auto", choices=["auto", "simt", "sm100"])
     ap.add_argument("--seq-len", type=int, default=None,
                     help="override T of the workload (profiling on a small case; not a headline number)")
+    ap.add_argument("--pass", dest="which", default="fwd", choices=["fwd", "bwd"],
+                    help="bwd: time tpa_bwd on the forward's results instead (single GPU; 2.5x the forward's "
+                         "algorithmic FLOPs: five tile GEMMs instead of two); not the headline metric")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
@@ -231,8 +234,18 @@ def main():
     ring = world > 1
     q, k, v = make_inputs(name, device, shard=(rank, world) if ring else None)
     ids = torch.zeros((b, q.shape[1]), dtype=torch.int32, device=device) if ring else None
+    bwd = args.which == "bwd"
+    if bwd:
+        assert not ring, "--pass bwd is a single-GPU measurement"
+        o_fwd, lse_fwd = tpa_b200.tpa.fwd_device(q, k, v, h, None, None, sm_scale, causal)
+        gen = torch.Generator(device=device).manual_seed(1234)
+        d_o = torch.randn(o_fwd.shape, generator=gen, device=device, dtype=torch.float32).to(q.dtype)
+        grads = tuple(torch.empty_like(x) for x in (q, k, v))
 
     def step():
+        if bwd:
+            return tpa_b200.tpa.bwd_device(q, k, v, h, None, None, sm_scale, causal, o_fwd, lse_fwd, d_o,
+                                           out=grads, kernel=args.kernel)
         if ring:
             return tpa_b200.ring_tpa.ring_tpa(q, k, v, ids, ids, None, h, sm_scale=sm_scale, causal=causal,
                                               mask_mode=args.mask_mode)
@@ -279,13 +292,13 @@ def main():
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         total_ms = float(tt.item())
     ms = total_ms / args.steps
-    fl = flops(b, t, h, d, causal)
+    fl = flops(b, t, h, d, causal) * (2.5 if bwd else 1.0)
     value = fl / (ms * 1e-3) / 1e12
     toks = b * t / (ms * 1e-3)
 
     # ------------------------------------------------------------- end to end on pinned host arrays
     e2e = None
-    if not args.no_e2e:
+    if not args.no_e2e and not bwd:
         hq, hk, hv = (x.cpu().pin_memory() for x in (q, k, v))
         hid = ids.cpu().pin_memory() if ring else None
         out_host = torch.empty((b, q.shape[1], h, d), dtype=q.dtype).pin_memory()
@@ -330,6 +343,8 @@ def main():
     kernel_ms = statistics.median(per_step) / (world if ring else 1)
     fl_launch = fl / (world * world) if ring else fl
     achieved = fl_launch / (kernel_ms * 1e-3) / 1e12
+    if bwd:
+        info = dict(info, kernel="bwd:" + ("simt" if args.kernel == "simt" or info["kernel"] == "simt" else "sm100"))
     roofline = {"bound": "tensor", "achieved": achieved, "peak": burst, "unit": "TFLOP/s", "frac": achieved / burst,
                 "frac_of_sustained": achieved / sustained if sustained else None, "peak_source": src,
                 "traffic": NCU_TRAFFIC.get(name), "kernel": info["kernel"],
@@ -337,12 +352,12 @@ def main():
                 + b * q.shape[1] * h * d * q.element_size() + b * q.shape[1] * h * 4,
                 "hbm_peak_gbs": hbm}
     cpu = None
-    if not args.no_cpu_baseline and world == 1:
+    if not args.no_cpu_baseline and world == 1 and not bwd:
         tf, ctoks, cdt, sample = time_cpu(name, 1, 0)
         cpu = {"value": tf, "unit": "TFLOP/s", "tokens_per_s": ctoks, "cores": torch.get_num_threads(), "kind": "port",
                "sample": sample}
     line = {
-        "metric": METRIC, "value": value, "unit": "TFLOP/s", "tokens_per_s": toks, "n_gpus": world, "steps": args.steps,
+        "metric": METRIC if not bwd else "TPA bwd algorithmic TFLOP/s per B200 (2.5x the forward's FLOPs)", "value": value, "unit": "TFLOP/s", "tokens_per_s": toks, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": dtn, "data": "synthetic",
         "config": {"workload": name, "shape": f"B{b} T{t} h{h} d{d} R{rq}/{rk}/{rk} causal={causal}",
