@@ -212,6 +212,29 @@ def tpa_bwd_reference(
     24 shapes of its backward test.
     Returns (dq, dk, dv) shaped like q, k, v.
     """
+    return tpa_bwd_block(q, k, v, do, None, None, num_heads, q_segment_ids, kv_segment_ids, sm_scale,
+                         causal, dtype, q_offset, k_offset)
+
+
+def tpa_bwd_block(
+    q,
+    k,
+    v,
+    do,
+    o,
+    l,
+    num_heads,
+    q_segment_ids=None,
+    kv_segment_ids=None,
+    sm_scale=1.0,
+    causal=False,
+    dtype=np.float64,
+    q_offset=0,
+    k_offset=0,
+):
+    """One block of the backward for given residuals `o` [b,lq,h,dv] and `l` [b,lq,h] (the
+    operands of _bwd, tpa/tpa.py:823-839): what a ring step computes with the LSE of the whole
+    ring (tpa/ring_tpa.py:147-156).  `o = l = None`: residuals of this block's own forward."""
     qa, qb = split_factors(np.asarray(q, dtype), num_heads)
     ka, kb = split_factors(np.asarray(k, dtype), num_heads)
     va, vb = split_factors(np.asarray(v, dtype), num_heads)
@@ -224,11 +247,12 @@ def tpa_bwd_reference(
     keep = _mask(b, lq, lk, q_segment_ids, kv_segment_ids, causal, q_offset, k_offset)
     x = np.where(keep[:, None], x, -np.inf)
     with np.errstate(invalid="ignore", divide="ignore"):
-        l = lse(x)[..., None]  # [b, h, lq, 1]
-        p = np.exp(x - l)
+        lcol = lse(x)[..., None] if l is None else np.transpose(np.asarray(l, dtype), (0, 2, 1))[..., None]
+        p = np.exp(x - lcol)  # [b, h, lq, lk]
     p = np.where(np.isnan(p), 0.0, p)
-    o = np.einsum("bhqk,bkhd->bqhd", p, v_)
-    delta = np.einsum("bqhd,bqhd->bhq", o, do)[..., None]
+    if o is None:
+        o = np.einsum("bhqk,bkhd->bqhd", p, v_)
+    delta = np.nansum(np.asarray(o, dtype) * do, axis=-1).transpose(0, 2, 1)[..., None]  # tpa/tpa.py:979
     dp = np.einsum("bqhd,bkhd->bhqk", do, v_) - delta
     ds = p * dp * dtype(sm_scale)
     dq_ = np.einsum("bhqk,bkhd->bqhd", ds, k_)
@@ -383,6 +407,53 @@ def ring_tpa_reference(
             l = l_next
         out[:, qs] = np.where(np.isneginf(l)[..., None], np.nan, o)
     return out
+
+
+def ring_tpa_bwd_reference(
+    q,
+    k,
+    v,
+    q_segment_ids,
+    kv_segment_ids,
+    do,
+    num_heads,
+    n_shards,
+    sm_scale=1.0,
+    causal=False,
+    mask_mode="reference_local",
+    dtype=np.float64,
+):
+    """Restatement of _ring_tpa_bwd over `n_shards` simulated ranks (tpa/ring_tpa.py:115-172):
+    every (query shard r, key shard src) block runs the block backward with the o and LSE of the
+    whole ring forward; dq sums on r, dk / dv travel with the K/V shard and sum on src."""
+    b, lq = q.shape[:2]
+    lk = k.shape[1]
+    sq, sk = lq // n_shards, lk // n_shards
+    o = ring_tpa_reference(q, k, v, q_segment_ids, kv_segment_ids, num_heads, n_shards, sm_scale, causal,
+                           mask_mode, dtype)
+    # LSE of the whole ring: lse_accum over the steps (tpa/ring_tpa.py:82)
+    l = np.full((b, lq, num_heads), -np.inf, dtype=dtype)
+    blocks = []
+    for r in range(n_shards):
+        for src in range(n_shards):
+            qs, ks = slice(r * sq, (r + 1) * sq), slice(src * sk, (src + 1) * sk)
+            offs = (r * sq, src * sk) if mask_mode == "global" else (0, 0)
+            blocks.append((qs, ks, offs))
+            _, l_ = tpa_reference(q[:, qs], k[:, ks], v[:, ks], num_heads,
+                                  None if q_segment_ids is None else q_segment_ids[:, qs],
+                                  None if kv_segment_ids is None else kv_segment_ids[:, ks],
+                                  sm_scale, causal, dtype, offs[0], offs[1], return_lse=True)
+            l[:, qs] = lse_accum(l[:, qs], l_)
+    dq, dk, dv = (np.zeros(x.shape, dtype=dtype) for x in (q, k, v))
+    for qs, ks, offs in blocks:
+        g = tpa_bwd_block(q[:, qs], k[:, ks], v[:, ks], do[:, qs], o[:, qs], l[:, qs], num_heads,
+                          None if q_segment_ids is None else q_segment_ids[:, qs],
+                          None if kv_segment_ids is None else kv_segment_ids[:, ks],
+                          sm_scale, causal, dtype, offs[0], offs[1])
+        dq[:, qs] += g[0]
+        dk[:, ks] += g[1]
+        dv[:, ks] += g[2]
+    return dq, dk, dv
 
 
 # --------------------------------------------------------------------------- torch variant (large cases, CPU baseline)

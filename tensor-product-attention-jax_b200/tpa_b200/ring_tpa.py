@@ -1,9 +1,10 @@
-"""Ring (sequence-parallel) Tensor Product Attention forward, one process per GPU.
+"""Ring (sequence-parallel) Tensor Product Attention, one process per GPU.
 
-Mirrors tpa/ring_tpa.py of jondeaton/tensor-product-attention-jax for the forward path:
+Mirrors tpa/ring_tpa.py of jondeaton/tensor-product-attention-jax:
 
     _rotate_block()            tpa/ring_tpa.py:24-38    -> grouped NCCL send/recv to rank+1
     _ring_tpa_fwd()            tpa/ring_tpa.py:41-112   -> ring_tpa() below (steps + merge)
+    _ring_tpa_bwd()            tpa/ring_tpa.py:115-172  -> ring_tpa_bwd() below
     ring_tpa()                 tpa/ring_tpa.py:209-287
     ring_tp_self_attention()   tpa/ring_tpa.py:290-338
 
@@ -22,7 +23,7 @@ import torch.distributed as dist
 
 from . import tpa as _tpa
 
-__all__ = ["ring_tpa", "ring_tp_self_attention", "register_axis"]
+__all__ = ["ring_tpa", "ring_tpa_bwd", "ring_tp_self_attention", "register_axis"]
 
 _AXES: dict = {}
 _side_streams: dict = {}
@@ -56,10 +57,10 @@ def _rotate_block(tensors, recv_into, group, rank, size):
 
 
 def _device_block(q, k, v, qs, ks, num_heads, sm_scale, causal, q_offset, k_offset, state,
-                  load_state, store_state, out, reuse_q=True):
+                  load_state, store_state, out, reuse_q=True, lse=None):
     return _tpa.fwd_device(
         q, k, v, num_heads, qs, ks, sm_scale, causal, q_offset=q_offset, k_offset=k_offset,
-        state=state, load_state=load_state, store_state=store_state, out=out, want_lse=False,
+        state=state, load_state=load_state, store_state=store_state, out=out, lse=lse, want_lse=False,
         # q and the workspace are those of the previous step (not so when two query chunks alternate)
         reuse_staged_q=load_state and reuse_q,
     )[0]
@@ -210,9 +211,14 @@ def ring_tpa(
     interpret: bool = False,
     *,
     mask_mode: str = "reference_local",
+    return_lse: bool = False,
     _block_fn=None,
 ):
     """Ring TPA forward on this rank's shard; arguments as tpa/ring_tpa.py:209-222.
+
+    Differentiable: when q, k or v requires grad the call goes through torch autograd with
+    ring_tpa_bwd as its backward (the custom_vjp of tpa/ring_tpa.py:175-206).
+    `return_lse=True` (keyword only) also returns the fp32 LSE of the whole ring, [b, l/N, h].
 
     q[b, l/N, rq, h+dk], k, v, and the two int32 id arrays are this rank's contiguous
     shard; returns this rank's o[b, l/N, h, dv].  `impl="pallas"` is the reference's name
@@ -232,6 +238,10 @@ def ring_tpa(
         raise ValueError(f"Unknown implementaiton: {impl}")
     if mask_mode not in MASK_MODES:
         raise ValueError(f"mask_mode must be one of {MASK_MODES}")
+    if (_block_fn is None and not return_lse and torch.is_grad_enabled()
+            and (q.requires_grad or k.requires_grad or v.requires_grad)):
+        return _RingTpaFunction.apply(q, k, v, q_segment_ids, kv_segment_ids, axis_name, num_heads,
+                                      sm_scale, causal, mask_mode)
     block = _block_fn or _device_block
     if _block_fn is None and not q.is_cuda:
         raise RuntimeError("tpa_b200 needs a CUDA device: there is no CPU implementation")
@@ -251,13 +261,15 @@ def ring_tpa(
     kseg = kv_segment_ids.to(torch.int32).contiguous()
     qseg = q_segment_ids.to(torch.int32).contiguous()
 
-    if causal and mask_mode == "global" and size > 1 and lq == lk and lq % 2 == 0:
+    # (the balanced exchange does not carry the LSE back; with return_lse the contiguous walk runs)
+    if causal and mask_mode == "global" and size > 1 and lq == lk and lq % 2 == 0 and not return_lse:
         zz_block = _device_block_fresh_q if _block_fn is None else _block_fn
         return _ring_global_zigzag(q, k.contiguous(), v.contiguous(), qseg, kseg, group, size, rank,
                                    num_heads, sm_scale, zz_block)
 
     use_streams = q.is_cuda
     out = torch.empty((b, lq, num_heads, dv), dtype=q.dtype, device=q.device)
+    lse = torch.empty((b, lq, num_heads), dtype=torch.float32, device=q.device) if return_lse else None
     state = None
     if size > 1:
         state = (
@@ -296,9 +308,10 @@ def ring_tpa(
                 reqs = _rotate_block(cur, nxt, group, rank, size)
         if visible(src):
             q_off, k_off = (rank * lq, src * lk) if mask_mode == "global" else (0, 0)
+            extra = {"lse": lse} if (return_lse and s == last_compute) else {}
             block(
                 q, cur[0], cur[1], qseg, cur[2], num_heads, sm_scale, causal, q_off, k_off, state,
-                started, s != last_compute, out,
+                started, s != last_compute, out, **extra,
             )
             started = True
         if s < size - 1:
@@ -315,7 +328,129 @@ def ring_tpa(
                 for r in reqs:
                     r.wait()
             cur = nxt
-    return out
+    return (out, lse) if return_lse else out
+
+
+def _device_bwd_block(q, k, v, qs, ks, num_heads, sm_scale, causal, q_offset, k_offset, o, lse, do,
+                      grads, accumulate_dq):
+    """One ring step of the backward: dq (+)= , travelling dk, dv += (fp32 buffers in `grads`)."""
+    _tpa.bwd_device(q, k, v, num_heads, qs, ks, sm_scale, causal, o, lse, do, q_offset=q_offset,
+                    k_offset=k_offset, grad_dtype=torch.float32, out=grads,
+                    accumulate_dq=accumulate_dq, accumulate_dkv=True)
+
+
+def ring_tpa_bwd(
+    q,
+    k,
+    v,
+    q_segment_ids,
+    kv_segment_ids,
+    o,
+    lse,
+    do,
+    axis_name,
+    num_heads: int,
+    sm_scale: float = 1.0,
+    causal: bool = False,
+    *,
+    mask_mode: str = "reference_local",
+    _block_fn=None,
+):
+    """Ring TPA backward on this rank's shard (_ring_tpa_bwd, tpa/ring_tpa.py:115-172).
+
+    `o`, `lse` are the ring forward's results for this rank's rows (lse of the whole ring, fp32),
+    `do` the incoming gradient.  Every step runs the block backward against the visiting K/V
+    shard, adds into the local dq and into the dk / dv accumulators that travel with that shard
+    (tpa/ring_tpa.py:147-160); after N rotations the accumulators are home again.  Gradients are
+    accumulated in fp32 and returned in the dtype of q, k, v.  The K/V factors of the next step
+    move on a side stream while the current step computes; the accumulators can only follow it.
+    """
+    if mask_mode not in MASK_MODES:
+        raise ValueError(f"mask_mode must be one of {MASK_MODES}")
+    block = _block_fn or _device_bwd_block
+    if _block_fn is None and not q.is_cuda:
+        raise RuntimeError("tpa_b200 needs a CUDA device: there is no CPU implementation")
+    group = _group_of(axis_name)
+    if dist.is_available() and dist.is_initialized():
+        size, rank = dist.get_world_size(group), dist.get_rank(group)
+    else:
+        size, rank = 1, 0
+    lq, lk = q.shape[1], k.shape[1]
+    kseg = kv_segment_ids.to(torch.int32).contiguous()
+    qseg = q_segment_ids.to(torch.int32).contiguous()
+    f32 = torch.float32
+    dq = torch.zeros(q.shape, dtype=f32, device=q.device)
+    cur = [k.contiguous(), v.contiguous(), kseg]
+    acc = [torch.zeros(k.shape, dtype=f32, device=q.device), torch.zeros(v.shape, dtype=f32, device=q.device)]
+    spare = [[torch.empty_like(t) for t in cur] for _ in range(min(2, size - 1))]
+    acc_spare = [torch.empty_like(t) for t in acc] if size > 1 else None
+    use_streams = q.is_cuda
+    if use_streams:
+        main = torch.cuda.current_stream(q.device)
+        side = _side_streams.get(q.device) or _side_streams.setdefault(q.device, torch.cuda.Stream(q.device))
+        ready = torch.cuda.Event()
+        ready.record(main)
+
+    def visible(src):
+        return not (causal and mask_mode == "global" and src * lk > rank * lq + lq - 1)
+
+    started = False
+    for s in range(size):
+        src = (rank - s) % size
+        reqs = None
+        if s < size - 1:  # the factors of the next step leave while this step computes
+            nxt = spare[s % 2]
+            if use_streams:
+                side.wait_event(ready)
+                with torch.cuda.stream(side):
+                    reqs = _rotate_block(cur, nxt, group, rank, size)
+            else:
+                reqs = _rotate_block(cur, nxt, group, rank, size)
+        if visible(src):
+            q_off, k_off = (rank * lq, src * lk) if mask_mode == "global" else (0, 0)
+            block(q, cur[0], cur[1], qseg, cur[2], num_heads, sm_scale, causal, q_off, k_off, o, lse, do,
+                  (dq, acc[0], acc[1]), started)
+            started = True
+        if size > 1:
+            if s < size - 1:
+                if use_streams:
+                    ready = torch.cuda.Event()
+                    ready.record(main)
+                    with torch.cuda.stream(side):
+                        for r in reqs:
+                            r.wait()
+                        arrived = torch.cuda.Event()
+                        arrived.record(side)
+                    main.wait_event(arrived)
+                else:
+                    for r in reqs:
+                        r.wait()
+                cur = nxt
+            # the accumulators follow their shard (every step, so that they end at home)
+            for r in _rotate_block(acc, acc_spare, group, rank, size):
+                r.wait()
+            acc, acc_spare = acc_spare, acc
+    return dq.to(q.dtype), acc[0].to(k.dtype), acc[1].to(v.dtype)
+
+
+class _RingTpaFunction(torch.autograd.Function):
+    """custom_vjp of the reference (tpa/ring_tpa.py:175-206): forward keeps (o, lse of the ring)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, q_segment_ids, kv_segment_ids, axis_name, num_heads, sm_scale, causal, mask_mode):
+        o, lse = ring_tpa(q, k, v, q_segment_ids, kv_segment_ids, axis_name, num_heads, sm_scale, causal,
+                          mask_mode=mask_mode, return_lse=True)
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.rest = (q_segment_ids, kv_segment_ids, axis_name, num_heads, sm_scale, causal, mask_mode)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, lse = ctx.saved_tensors
+        qs, ks, axis_name, num_heads, sm_scale, causal, mask_mode = ctx.rest
+        dq, dk, dv = ring_tpa_bwd(q, k, v, qs, ks, o, lse, do.contiguous(), axis_name, num_heads, sm_scale,
+                                  causal, mask_mode=mask_mode)
+        return (dq, dk, dv) + (None,) * 7
 
 
 def ring_tp_self_attention(

@@ -14,7 +14,7 @@ from conftest import ROOT, PKG_DIR  # noqa: F401  (puts the package on sys.path)
 from oracle import tpa_oracle as orc
 
 
-def oracle_block(q, k, v, qs, ks, num_heads, sm_scale, causal, q_off, k_off, state, load, store, out):
+def oracle_block(q, k, v, qs, ks, num_heads, sm_scale, causal, q_off, k_off, state, load, store, out, lse=None):
     """CPU stand-in for one tpa_fwd call with the TPA_FLAG_STATE_* contract."""
     o_, l_ = orc.tpa_reference(q.numpy(), k.numpy(), v.numpy(), num_heads, qs.numpy(), ks.numpy(),
                                sm_scale=sm_scale, causal=causal, q_offset=q_off, k_offset=k_off,
@@ -32,6 +32,17 @@ def oracle_block(q, k, v, qs, ks, num_heads, sm_scale, causal, q_off, k_off, sta
     else:
         o_ = np.where(np.isneginf(l_)[..., None], np.nan, o_)
         out.copy_(torch.from_numpy(o_).to(out.dtype))
+        if lse is not None:
+            lse.copy_(torch.from_numpy(l_).float())
+
+
+def oracle_bwd_block(q, k, v, qs, ks, num_heads, sm_scale, causal, q_off, k_off, o, lse, do, grads, accumulate_dq):
+    """CPU stand-in for one tpa_bwd call (fp32 gradients, dk / dv always accumulate)."""
+    g = orc.tpa_bwd_block(q.numpy(), k.numpy(), v.numpy(), do.numpy(), o.numpy(), lse.numpy(), num_heads,
+                          qs.numpy(), ks.numpy(), sm_scale, causal, np.float64, q_off, k_off)
+    for buf, new, acc in zip(grads, g, (accumulate_dq, True, True)):
+        new = torch.from_numpy(new).to(buf.dtype)
+        buf.copy_(buf + new if acc else new)
 
 
 def _free_port():
@@ -85,3 +96,47 @@ def test_ring_host_logic_gloo(world, case):
     assert ret["shape"] == (case[1], case[2], case[5], case[7])
     assert ret["nan_equal"]
     assert ret["err"] < 1e-5, ret["err"]
+
+
+def _bwd_worker(rank, world, port, case, ret):
+    import sys
+    for p in (ROOT, PKG_DIR):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    import tpa_b200
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        seed, b, l, rq, rk, h, dk, dv, seg, sm, causal, mode = case
+        q, k, v = orc.make_factors(seed, b, l, l, rq, rk, h, dk, dv)
+        ids = orc.segment_ids(b, l, seg) if seg else np.zeros((b, l), np.int32)
+        do = np.random.default_rng(seed).standard_normal((b, l, h, dv)).astype(np.float32)
+        sh = slice(rank * (l // world), (rank + 1) * (l // world))
+        tq, tk, tv, tid, tdo = (torch.from_numpy(np.ascontiguousarray(x[:, sh])) for x in (q, k, v, ids, do))
+        o, lse = tpa_b200.ring_tpa.ring_tpa(tq, tk, tv, tid, tid, None, h, sm_scale=sm, causal=causal,
+                                            mask_mode=mode, return_lse=True, _block_fn=oracle_block)
+        grads = tpa_b200.ring_tpa.ring_tpa_bwd(tq, tk, tv, tid, tid, o, lse, tdo, None, h, sm_scale=sm,
+                                               causal=causal, mask_mode=mode, _block_fn=oracle_bwd_block)
+        full = []
+        for g in grads:
+            parts = [torch.empty_like(g) for _ in range(world)]
+            dist.all_gather(parts, g.contiguous())
+            full.append(torch.cat(parts, 1).numpy())
+        if rank == 0:
+            ref = orc.ring_tpa_bwd_reference(q, k, v, ids, ids, do, h, world, sm, causal, mode)
+            ret["err"] = max(float(np.max(np.abs(a - r))) for a, r in zip(full, ref))
+            ret["scale"] = max(float(np.max(np.abs(r))) for r in ref)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("case", CASES)
+def test_ring_backward_host_logic_gloo(world, case):
+    """dq stays, dk / dv travel with their shard and come home after N rotations (tpa/ring_tpa.py:147-160)."""
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_bwd_worker, args=(world, _free_port(), case, ret), nprocs=world, join=True)
+    assert ret["err"] < 1e-5 * max(1.0, ret["scale"]), (ret["err"], ret["scale"])
