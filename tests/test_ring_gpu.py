@@ -54,6 +54,37 @@ for (dtype, b, l, h, d, rq, rk, seg, mode, causal) in [
         print(f"ring {dtype} l={l} d={d} {mode} causal={causal}: max {np.nanmax(diff):.2e} mean {np.nanmean(diff):.2e} status {st} {'OK' if ok else 'FAIL'}", flush=True)
     if not ok:
         fails.append((dtype, l, mode))
+# backward: autograd through ring_tpa on every rank's shard, gradients gathered and compared on rank 0
+for (dtype, b, l, h, d, rq, rk, seg, mode, causal) in [
+    ("f32", 1, 128 * world, 4, 32, 3, 2, 100, "reference_local", True),
+    ("bf16", 1, 256 * world, 8, 128, 4, 2, 0, "global", True),
+    ("bf16", 1, 256 * world, 8, 64, 2, 2, 200, "reference_local", False),
+]:
+    q, k, v = orc.make_factors(78, b, l, l, rq, rk, h, d, d)
+    ids = orc.segment_ids(b, l, seg) if seg else np.zeros((b, l), np.int32)
+    w = np.random.default_rng(5).standard_normal((b, l, h, d)).astype(np.float32)
+    td = torch.float32 if dtype == "f32" else torch.bfloat16
+    sh = slice(rank * (l // world), (rank + 1) * (l // world))
+    tq, tk, tv = (torch.from_numpy(np.ascontiguousarray(x[:, sh])).cuda().to(td).requires_grad_() for x in (q, k, v))
+    tid = torch.from_numpy(np.ascontiguousarray(ids[:, sh])).cuda()
+    tw = torch.from_numpy(np.ascontiguousarray(w[:, sh])).cuda().to(td)
+    o = tpa_b200.ring_tpa.ring_tpa(tq, tk, tv, tid, tid, None, h, sm_scale=d ** -0.5, causal=causal, mask_mode=mode)
+    torch.nansum(o.float() * tw.float()).backward()
+    st = tpa_b200.tpa.device_status_bwd()[0]
+    full = []
+    for g in (tq.grad, tk.grad, tv.grad):
+        parts = [torch.empty_like(g) for _ in range(world)]
+        dist.all_gather(parts, g.contiguous())
+        full.append(torch.cat(parts, 1).float().cpu().numpy())
+    if rank != 0:
+        continue
+    rnd = lambda x: torch.from_numpy(x).to(td).float().numpy()
+    ref = orc.ring_tpa_bwd_reference(rnd(q), rnd(k), rnd(v), ids, ids, rnd(w), h, world, d ** -0.5, causal, mode)
+    rel = max(float(np.max(np.abs(a - r)) / max(1e-6, np.max(np.abs(r)))) for a, r in zip(full, ref))
+    ok = rel < (1e-4 if dtype == "f32" else 3e-2) and st == 0 and all(np.isfinite(a).all() for a in full)
+    print(f"ring backward {dtype} l={l} d={d} {mode} causal={causal}: rel {rel:.2e} status {st} {'OK' if ok else 'FAIL'}", flush=True)
+    if not ok:
+        fails.append(("bwd", dtype, l, mode))
 dist.barrier()
 dist.destroy_process_group()
 sys.exit(1 if fails else 0)
