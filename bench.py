@@ -197,7 +197,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
     ap.add_argument("--mask-mode", default="reference_local", choices=["reference_local", "global"])
-    ap.add_argument("--kernel", default="auto", choices=["auto", "simt", "sm100"])
+    ap.add_argument("--kernel", default="auto", choices=["auto", "simt", "sm100", "sm100_fused", "sm100_staged"])
     ap.add_argument("--seq-len", type=int, default=None,
                     help="override T of the workload (profiling on a small case; not a headline number)")
     ap.add_argument("--pass", dest="which", default="fwd", choices=["fwd", "bwd"],
@@ -243,9 +243,9 @@ def main():
         grads = tuple(torch.empty_like(x) for x in (q, k, v))
 
     def step():
-        if bwd:
+        if bwd:  # the backward knows "auto", "simt" and "sm100"
             return tpa_b200.tpa.bwd_device(q, k, v, h, None, None, sm_scale, causal, o_fwd, lse_fwd, d_o,
-                                           out=grads, kernel=args.kernel)
+                                           out=grads, kernel=args.kernel.split("_")[0])
         if ring:
             return tpa_b200.ring_tpa.ring_tpa(q, k, v, ids, ids, None, h, sm_scale=sm_scale, causal=causal,
                                               mask_mode=args.mask_mode)
@@ -347,7 +347,7 @@ def main():
         info = dict(info, kernel="bwd:" + ("simt" if args.kernel == "simt" or info["kernel"] == "simt" else "sm100"))
     roofline = {"bound": "tensor", "achieved": achieved, "peak": burst, "unit": "TFLOP/s", "frac": achieved / burst,
                 "frac_of_sustained": achieved / sustained if sustained else None, "peak_source": src,
-                "traffic": NCU_TRAFFIC.get(name), "kernel": info["kernel"],
+                "traffic": None if bwd else NCU_TRAFFIC.get(name), "kernel": info["kernel"],
                 "hbm_algorithmic_bytes": sum(x.numel() * x.element_size() for x in (q, k, v))
                 + b * q.shape[1] * h * d * q.element_size() + b * q.shape[1] * h * 4,
                 "hbm_peak_gbs": hbm}
