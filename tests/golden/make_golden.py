@@ -2,7 +2,7 @@
 
 Run where the reference checkout is readable:
 
-    python tests/golden/make_golden.py [--reference /path/to/tensor-product-attention-jax]
+    python tests/golden/make_golden.py --reference /path/to/tensor-product-attention-jax [--only bwd]
 
 jax is not installed there, so the reference files (tpa/tpa.py, tpa/mha.py,
 tpa/ring_tpa.py, tpa/tpa_test.py) are imported unmodified on top of the numpy
@@ -121,7 +121,8 @@ def make_backward(tpa, ttest):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("TPA_REFERENCE", "/root/reference"))
+    ap.add_argument("--reference", default=os.environ.get("TPA_REFERENCE"), required="TPA_REFERENCE" not in os.environ,
+                    help="checkout of jondeaton/tensor-product-attention-jax (or set TPA_REFERENCE)")
     ap.add_argument("--only", choices=["all", "bwd"], default="all",
                     help="bwd: regenerate bwd_matrix.npz only")
     args = ap.parse_args()
