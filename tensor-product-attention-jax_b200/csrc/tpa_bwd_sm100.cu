@@ -25,9 +25,14 @@
 // serves as a K-major operand of the first two GEMMs and as an MN-major operand of the
 // accumulating ones; only the descriptor differs.
 //
-// Roles, by warp: 0-15 element-wise (four threads per TMEM lane; the two 64-column halves of a
-// tile are separate pipeline phases, each worked on by all 16 warps) and the epilogue; 16: one thread issues the
-// bulk copies; 17: one thread issues tcgen05.mma.
+// Roles, by warp: 0-15 element-wise (four threads per TMEM lane, 32 columns each) and the epilogue;
+// 16: one thread issues the bulk copies; 17: one thread issues tcgen05.mma.
+//
+// Pipeline.  A tile has two dependency chains, T1 -> p -> (dV) and T2 -> ds -> (dK | dQ).  A
+// commit -> waiter -> arrive -> issuer round trip costs about 500 cycles on top of the MMAs, and
+// TMEM is full, so there is no second tile to hide it behind; instead the chains are interleaved:
+// the element-wise warps turn T1 into p while the tensor pipe computes T2, and T2 into ds while
+// it runs the accumulating GEMM fed by p and the next tile's T1.
 // TMEM columns: T1 [0,128) (S, then p as bf16), T2 [128,256) (dP, then ds as bf16),
 // accumulators from 256 (dQ, or dK and dV).  Dense fp32 dQ / dK / dV go to scratch; the
 // factor contraction (tpa_bwd_contract_kernel) is shared with the SIMT path.
@@ -57,7 +62,7 @@ constexpr int kThreads = (kMmaWarp + 1) * 32;
 struct BwdBarriers {
   uint64_t x_full;                   // the CTA's own two tiles have landed
   uint64_t y_full[3], y_empty[3];    // streamed tiles (+ row statistics), two or three stages
-  uint64_t t_full[2], p_ready[2], acc_done;  // per column half of T1 / T2
+  uint64_t t_full[2], p_ready[2], acc_done;  // [0]: T1 written / read (p stored); [1]: T2 written / ds stored
   uint32_t tmem_base;
   volatile uint32_t abort;
   alignas(16) float stats[3][2][kRows];  // [stage][log2e*lse | delta][query row] (KV_OWNER)
@@ -233,10 +238,9 @@ tpa_bwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
 
   if (warp < kEwWarps) {
     // ------------------------------------------------------------------ element-wise + epilogue
-    // Four threads per TMEM lane: warp w serves lanes 32 (w & 3)... and, in each column half
-    // [64 h, 64 h + 64) of a tile, the 16 columns (moving rows) 64 h + 16 (w >> 2)...  The halves
-    // are separate pipeline phases with their own barriers: all 16 warps work on one half while
-    // the tensor pipe consumes the other.
+    // Four threads per TMEM lane: warp w serves lanes 32 (w & 3)... and the 32 columns (moving
+    // rows) 32 (w >> 2)... of T1 and T2.  Per tile: phase 1 turns T1 into p, phase 2 turns T2
+    // into ds; each has its own pair of barriers.
     const int quarter = warp & 3, cq = warp >> 2;
     const int row = quarter * 32 + lane;  // TMEM lane = row of the own tile
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
@@ -289,47 +293,44 @@ tpa_bwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
       if (lane == 0) mbar_arrive(&bars->x_full);
     }
 
+    const int c0 = cq * 32;  // this thread's 32 columns (moving rows) of every tile
     for (int n = 0; n < n_tiles; ++n) {
       const int s = n % kStages;
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int c0 = h * 64 + cq * 16;               // this thread's 16 columns of the half
-        const int m0 = (t_lo + n) * kRows + c0;        // their first moving row
-        wait(&bars->t_full[h], n & 1, 0x100 + h);
-        tc_fence_after();
-        if (KV_OWNER && h == 0) wait(&bars->y_full[s], (n / kStages) & 1, 0x102);  // the statistics have landed
-        // does any pair of these 32 lanes x 16 columns need the element-wise test?
-        bool masked = has_seg;
-        if (causal) {
-          if (KV_OWNER) masked = masked || ((int64_t)m0 + mov_off < lane0_pos + 31);  // min q < max key
-          else masked = masked || ((int64_t)m0 + 15 + mov_off > lane0_pos);            // max key > min q
-        }
-        if (!KV_OWNER) masked = masked || (m0 + 16 > p.lk);  // padded keys of a ragged last tile
+      const int m0 = (t_lo + n) * kRows + c0;  // first moving row of those columns
+      // does any pair of these 32 lanes x 32 columns need the element-wise test?
+      bool masked = has_seg;
+      if (causal) {
+        if (KV_OWNER) masked = masked || ((int64_t)m0 + mov_off < lane0_pos + 31);  // min q < max key
+        else masked = masked || ((int64_t)m0 + 31 + mov_off > lane0_pos);            // max key > min q
+      }
+      if (!KV_OWNER) masked = masked || (m0 + 32 > p.lk);  // padded keys of a ragged last tile
 
-        uint32_t t1[16], t2[16], ppk[8], dpk[8];
-        tmem_ld16(tmem + lane_base + c0, t1);
-        tmem_ld16(tmem + lane_base + kT2 + c0, t2);
-        float l2v[16], dlv[16];
+      // ---- phase 1: p = 2^(T1 - log2e lse), as soon as the first GEMM is done (the second runs meanwhile)
+      wait(&bars->t_full[0], n & 1, 0x100);
+      tc_fence_after();
+      if (KV_OWNER) wait(&bars->y_full[s], (n / kStages) & 1, 0x102);  // the statistics have landed
+      uint32_t ppk[16];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t t1[16];
+        tmem_ld16(tmem + lane_base + c0 + c * 16, t1);
+        float l2v[16];
         if (KV_OWNER) {
-          const float4* a4 = reinterpret_cast<const float4*>(bars->stats[s][0] + c0);
-          const float4* b4 = reinterpret_cast<const float4*>(bars->stats[s][1] + c0);
+          const float4* a4 = reinterpret_cast<const float4*>(bars->stats[s][0] + c0 + c * 16);
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            const float4 a = a4[i], b = b4[i];
+            const float4 a = a4[i];
             l2v[4 * i] = a.x; l2v[4 * i + 1] = a.y; l2v[4 * i + 2] = a.z; l2v[4 * i + 3] = a.w;
-            dlv[4 * i] = b.x; dlv[4 * i + 1] = b.y; dlv[4 * i + 2] = b.z; dlv[4 * i + 3] = b.w;
           }
         }
         tmem_ld_wait();
 #pragma unroll
         for (int e = 0; e < 16; e += 2) {
-          float pe[2], de[2];
+          float pe[2];
 #pragma unroll
           for (int k = 0; k < 2; ++k) {
-            const int col = e + k;
-            const float l2 = KV_OWNER ? l2v[col] : my_l2;
-            const float dl = KV_OWNER ? dlv[col] : my_dl;
-            float pr = ex2(__uint_as_float(t1[col]) - l2);
+            const int col = c * 16 + e + k;
+            float pr = ex2(__uint_as_float(t1[e + k]) - (KV_OWNER ? l2v[e + k] : my_l2));
             if (masked) {
               const int mi = m0 + col;
               const int64_t mpos = (int64_t)mi + mov_off;
@@ -339,20 +340,52 @@ tpa_bwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
               if (!keep) pr = 0.f;
             }
             pe[k] = pr;
-            de[k] = pr * fmaf(__uint_as_float(t2[col]), inv_rk, -dl);
           }
-          ppk[e / 2] = pack_bf16(pe[0], pe[1]);
-          dpk[e / 2] = pack_bf16(de[0], de[1]);
+          ppk[c * 8 + e / 2] = pack_bf16(pe[0], pe[1]);
         }
-        // bf16 p / ds overwrite the first 8 of the thread's own 16 fp32 columns: moving row k of
-        // the tile is at column (k / 16) * 16 + (k % 16) / 2 of T1 / T2
-        if (KV_OWNER) tmem_st8(tmem + lane_base + c0, ppk);
-        tmem_st8(tmem + lane_base + kT2 + c0, dpk);
-        tmem_st_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bars->p_ready[h]);
       }
+      // bf16 p overwrites the first 16 of the thread's own 32 fp32 columns: moving row k of the
+      // tile is at column (k / 32) * 32 + (k % 32) / 2.  The query-owner pass needs p only here.
+      if (KV_OWNER) {
+        tmem_st16(tmem + lane_base + c0, ppk);
+        tmem_st_wait();
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->p_ready[0]);  // T1 has been read (and holds p)
+
+      // ---- phase 2: ds = p (T2 / R_k - delta), p as rounded to bf16 above
+      wait(&bars->t_full[1], n & 1, 0x101);
+      tc_fence_after();
+      uint32_t dpk[16];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t t2[16];
+        tmem_ld16(tmem + lane_base + kT2 + c0 + c * 16, t2);
+        float dlv[16];
+        if (KV_OWNER) {
+          const float4* b4 = reinterpret_cast<const float4*>(bars->stats[s][1] + c0 + c * 16);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float4 b = b4[i];
+            dlv[4 * i] = b.x; dlv[4 * i + 1] = b.y; dlv[4 * i + 2] = b.z; dlv[4 * i + 3] = b.w;
+          }
+        }
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 16; e += 2) {
+          const uint32_t pw = ppk[c * 8 + e / 2];
+          const float p0 = __uint_as_float(pw << 16), p1 = __uint_as_float(pw & 0xffff0000u);
+          const float d0 = p0 * fmaf(__uint_as_float(t2[e]), inv_rk, -(KV_OWNER ? dlv[e] : my_dl));
+          const float d1 = p1 * fmaf(__uint_as_float(t2[e + 1]), inv_rk, -(KV_OWNER ? dlv[e + 1] : my_dl));
+          dpk[c * 8 + e / 2] = pack_bf16(d0, d1);
+        }
+      }
+      tmem_st16(tmem + lane_base + kT2 + c0, dpk);
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->p_ready[1]);  // T2 holds ds
     }
 
     // epilogue: accumulators -> dense fp32 rows (zeros when nothing was visible)
@@ -418,69 +451,55 @@ tpa_bwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
       const uint64_t dX0 = make_desc(aX, 16, 1024), dX1 = make_desc(aX + kTileBytes, 16, 1024);
       const uint64_t dYk0 = make_desc(aY, 16, 1024);            // moving tiles as K-major operands
       const uint64_t dYm0 = make_desc(aY, kRows * 128, 1024);   // ... and as MN-major operands
-      constexpr uint32_t kIdescHalf = make_idesc(128, 64, false, false);
       auto stage_off = [&](int n) { return (uint32_t)(((n % kStages) * 2 * kTileBytes) >> 4); };
-      // T1 = own0 moving0^T, T2 = own1 moving1^T of tile n.
-      //  own tiles in TMEM: one column half (64 moving rows) at a time, so that T(n+1,h) can follow
-      //  acc(n,h) at once; own tiles in shared memory: the whole tile (at N = 64 the A operand
-      //  would be re-read from shared memory twice as often).
-      auto issue_t = [&](int n, int h) {
+      // g = 0: T1 = own0 moving0^T;  g = 1: T2 = own1 moving1^T  (M128 N128, D/16 K steps)
+      auto issue_t = [&](int n, int g) {
+        const uint64_t dy = dYk0 + stage_off(n) + ((g * kTileBytes) >> 4);
 #pragma unroll
-        for (int g = 0; g < 2; ++g) {
-          const uint64_t dy = dYk0 + stage_off(n) + ((g * kTileBytes) >> 4) + (kOwnTmem ? (h * 64 * 128) >> 4 : 0);
-#pragma unroll
-          for (int ks = 0; ks < D / 16; ++ks) {
-            const uint32_t off = ((ks >> 2) * (kRows * 128) + (ks & 3) * 32) >> 4;
-            if (kOwnTmem)
-              mma_ts(tmem + g * kT2 + h * 64, tmem + kOwnCol + g * (D / 2) + ks * 8, dy + off, kIdescHalf, ks > 0);
-            else
-              mma_ss(tmem + g * kT2, (g == 0 ? dX0 : dX1) + off, dy + off, kIdescT, ks > 0);
-          }
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t off = ((ks >> 2) * (kRows * 128) + (ks & 3) * 32) >> 4;
+          if (kOwnTmem) mma_ts(tmem + g * kT2, tmem + kOwnCol + g * (D / 2) + ks * 8, dy + off, kIdescT, ks > 0);
+          else mma_ss(tmem + g * kT2, (g == 0 ? dX0 : dX1) + off, dy + off, kIdescT, ks > 0);
         }
-        if (kOwnTmem) {
-          tc_commit(&bars->t_full[h]);
-        } else {
-          tc_commit(&bars->t_full[0]);
-          tc_commit(&bars->t_full[1]);
+        tc_commit(&bars->t_full[g]);
+      };
+      // a = 0: acc0 += ds moving0 (ds in T2);  a = 1: acc1 += p moving1 (p in T1); eight K steps of 16 rows
+      auto issue_acc = [&](int n, int a) {
+        const uint64_t dy = dYm0 + stage_off(n) + ((a * kTileBytes) >> 4);
+#pragma unroll
+        for (int ks = 0; ks < kRows / 16; ++ks) {
+          const uint32_t acol = (ks >> 1) * 32 + (ks & 1) * 8;  // where the element-wise role put rows 16 ks ...
+          mma_ts(tmem + kAcc + a * D, tmem + (a == 0 ? kT2 : 0) + acol, dy + ((ks * 2048) >> 4), kIdescAcc,
+                 (n > 0 || ks > 0) ? 1u : 0u);
         }
       };
-      // accumulators += (ds | p)[:, 64 h ...] moving[64 h ...]: four K steps of 16 moving rows
-      auto issue_acc = [&](int n, int h) {
-        const uint64_t dy0 = dYm0 + stage_off(n), dy1 = dy0 + (kTileBytes >> 4);
-#pragma unroll
-        for (int ks = h * 4; ks < h * 4 + 4; ++ks) {
-          const uint32_t acol = ks * 16;  // where the element-wise role put rows 16 ks ... 16 ks + 15
-          const uint32_t accum = (n > 0 || ks > 0) ? 1u : 0u;
-          mma_ts(tmem + kAcc, tmem + kT2 + acol, dy0 + ((ks * 2048) >> 4), kIdescAcc, accum);
-          if (KV_OWNER) mma_ts(tmem + kAcc + D, tmem + acol, dy1 + ((ks * 2048) >> 4), kIdescAcc, accum);
-        }
-      };
-      // Order, own tiles in TMEM:   T(0,0) T(0,1) | acc(n,0) T(n+1,0) | acc(n,1) T(n+1,1) | ...
-      //        own tiles in smem:   T(0) | acc(n,0) | acc(n,1) | T(n+1) | ...
-      // T(n+1,.) overwrites the columns acc(n,.) reads; the tensor pipe executes in issue order, so
-      // that is safe.  The element-wise warps work on one column half while the pipe consumes the other.
+      // The two chains of a tile (T1 -> p -> acc1, T2 -> ds -> acc0) interleave, so that every wait
+      // for the element-wise warps is covered by an independent GEMM already in the queue:
+      //   T1(0) T2(0) | [p(n)] acc1(n) T1(n+1) | [ds(n)] acc0(n) T2(n+1) | ...
+      // T1(n+1) overwrites p(n) after acc1(n) has read it, T2(n+1) overwrites ds(n) after acc0(n):
+      // the tensor pipe executes in issue order.  (The query-owner pass has no acc1; there [p(n)]
+      // only says that T1(n) has been read.)
       wait(&bars->x_full, 0, 0x600);
       tc_fence_after();
       wait(&bars->y_full[0], 0, 0x601);
       tc_fence_after();
       issue_t(0, 0);
-      if (kOwnTmem) issue_t(0, 1);
+      issue_t(0, 1);
       for (int n = 0; n < n_tiles; ++n) {
         const bool more = n + 1 < n_tiles;
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          wait(&bars->p_ready[h], n & 1, 0x610 + h);
+        wait(&bars->p_ready[0], n & 1, 0x610);
+        tc_fence_after();
+        if (KV_OWNER) issue_acc(n, 1);
+        if (more) {
+          wait(&bars->y_full[(n + 1) % kStages], ((n + 1) / kStages) & 1, 0x602);
           tc_fence_after();
-          issue_acc(n, h);
-          if (more && (kOwnTmem || h == 1)) {
-            if (h == 0 || !kOwnTmem) {
-              wait(&bars->y_full[(n + 1) % kStages], ((n + 1) / kStages) & 1, 0x602);
-              tc_fence_after();
-            }
-            issue_t(n + 1, h);
-          }
-          if (h == 1) tc_commit(&bars->y_empty[n % kStages]);
+          issue_t(n + 1, 0);
         }
+        wait(&bars->p_ready[1], n & 1, 0x611);
+        tc_fence_after();
+        issue_acc(n, 0);
+        tc_commit(&bars->y_empty[n % kStages]);
+        if (more) issue_t(n + 1, 1);
       }
       tc_commit(&bars->acc_done);
     }

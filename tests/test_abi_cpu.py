@@ -71,6 +71,39 @@ def test_query_kernel_and_validation_without_gpu():
         _capi.check(_capi.TPA_ERR_UNSUPPORTED)
 
 
+def test_backward_validation_without_gpu():
+    def bargs(fwd_over=None, **over):
+        a = _capi.TpaBwdArgs()
+        a.struct_size = C.sizeof(_capi.TpaBwdArgs)
+        a.grad_dtype = _capi.DTYPE_F32
+        a.fwd = _args(**{"lse": 4096, **(fwd_over or {})})
+        a.d_o, a.dq, a.dk, a.dv = 4096, 4096, 4096, 4096
+        for key, val in over.items():
+            setattr(a, key, val)
+        return a
+
+    # fp32: delta + dense fp32 dQ, dK, dV behind the 256-byte status block, each rounded to 256 bytes
+    want = 256 + 1 * 64 * 4 * 4 + 3 * (1 * 64 * 4 * 16 * 4)
+    assert _capi.lib.tpa_bwd_workspace_bytes(C.byref(bargs())) == want
+    bad = [
+        (bargs(struct_size=8), _capi.TPA_ERR_BAD_ARG),
+        (bargs(d_o=None), _capi.TPA_ERR_BAD_ARG),
+        (bargs(dk=None), _capi.TPA_ERR_BAD_ARG),
+        (bargs({"lse": None}), _capi.TPA_ERR_BAD_ARG),                      # the forward's LSE is an input
+        (bargs({"flags": _capi.FLAG_STATE_LOAD, "state_o": 4096, "state_lse": 4096}), _capi.TPA_ERR_BAD_ARG),
+        (bargs(bwd_flags=8), _capi.TPA_ERR_BAD_ARG),
+        (bargs(grad_dtype=_capi.DTYPE_BF16), _capi.TPA_ERR_UNSUPPORTED),    # bf16 gradients of fp32 factors
+        (bargs({"kernel": _capi.KERNEL_SM100}), _capi.TPA_ERR_KERNEL_FORCED),  # fp32 has no tensor-core passes
+        (bargs({"kernel": _capi.KERNEL_SM100_FUSED}), _capi.TPA_ERR_KERNEL_FORCED),
+    ]
+    for a, code in bad:
+        assert _capi.lib.tpa_bwd(C.byref(a), 4096, 1 << 30, None) == code  # returns before any CUDA call
+        assert _capi.lib.tpa_bwd_workspace_bytes(C.byref(a)) == 0
+    # a workspace that is missing, too small or misaligned is refused before anything is enqueued
+    for ws, nbytes in ((None, want), (4096, want - 1), (4096 + 64, want)):
+        assert _capi.lib.tpa_bwd(C.byref(bargs()), ws, nbytes, None) == _capi.TPA_ERR_WORKSPACE
+
+
 def test_python_signature_errors_match_reference():
     q = torch.zeros(1, 256, 2, 4 + 8)
     k = torch.zeros(1, 256, 2, 4 + 8)
