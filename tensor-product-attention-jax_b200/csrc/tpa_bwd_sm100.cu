@@ -324,24 +324,22 @@ tpa_bwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
           }
         }
         tmem_ld_wait();
+        if (masked) {  // rare (diagonal and ragged tiles, segment ids): -inf logits give p = 0 below
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            const int mi = m0 + c * 16 + e;
+            const int64_t mpos = (int64_t)mi + mov_off;
+            bool keep = mi < mov_len;
+            if (causal) keep = keep && (KV_OWNER ? (mpos >= own_pos) : (own_pos >= mpos));
+            if (has_seg && keep) keep = mov_seg[mi] == own_seg;
+            if (!keep) t1[e] = 0xff800000u;
+          }
+        }
 #pragma unroll
         for (int e = 0; e < 16; e += 2) {
-          float pe[2];
-#pragma unroll
-          for (int k = 0; k < 2; ++k) {
-            const int col = c * 16 + e + k;
-            float pr = ex2(__uint_as_float(t1[e + k]) - (KV_OWNER ? l2v[e + k] : my_l2));
-            if (masked) {
-              const int mi = m0 + col;
-              const int64_t mpos = (int64_t)mi + mov_off;
-              bool keep = mi < mov_len;
-              if (causal) keep = keep && (KV_OWNER ? (mpos >= own_pos) : (own_pos >= mpos));
-              if (has_seg && keep) keep = mov_seg[mi] == own_seg;
-              if (!keep) pr = 0.f;
-            }
-            pe[k] = pr;
-          }
-          ppk[c * 8 + e / 2] = pack_bf16(pe[0], pe[1]);
+          const float p0 = ex2(__uint_as_float(t1[e]) - (KV_OWNER ? l2v[e] : my_l2));
+          const float p1 = ex2(__uint_as_float(t1[e + 1]) - (KV_OWNER ? l2v[e + 1] : my_l2));
+          ppk[c * 8 + e / 2] = pack_bf16(p0, p1);
         }
       }
       // bf16 p overwrites the first 16 of the thread's own 32 fp32 columns: moving row k of the
