@@ -65,7 +65,7 @@ struct BwdBarriers {
   uint64_t t_full[2], p_ready[2], acc_done;  // [0]: T1 written / read (p stored); [1]: T2 written / ds stored
   uint32_t tmem_base;
   volatile uint32_t abort;
-  alignas(16) float stats[3][2][kRows];  // [stage][log2e*lse | delta][query row] (KV_OWNER)
+  alignas(16) float stats[3][2][kRows];  // [stage][-log2e*lse | -delta][query row] (KV_OWNER)
 };
 
 struct BoundedWait {
@@ -90,6 +90,30 @@ struct BoundedWait {
   }
 };
 
+// two fp32 values in one 64-bit register for the packed add / mul / fma (half the issue slots)
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -98,10 +122,11 @@ __device__ __forceinline__ float ex2(float x) {
 
 // ---------------------------------------------------------------------------------------------
 // Row statistics, one warp per (batch, padded row, head):
-//   stats[((batch*heads + head) * tiles + row/128) * 256 + row%128]       = log2(e) * lse
-//   stats[...                                       + 128 + row%128]      = delta
-// delta = nansum(o * do) (tpa/tpa.py:976-980).  Rows that saw no key (lse = -inf) and the
-// padding rows of a ragged last tile get lse = +inf, so that p = 2^(s - inf) = 0 for them.
+//   stats[((batch*heads + head) * tiles + row/128) * 256 + row%128]       = -log2(e) * lse
+//   stats[...                                       + 128 + row%128]      = -delta
+// (negated: the pair kernel only ever adds them).  delta = nansum(o * do) (tpa/tpa.py:976-980).
+// Rows that saw no key (lse = -inf) and the padding rows of a ragged last tile get -inf in the
+// first slot, so that p = 2^(s - inf) = 0 for them.
 __global__ void __launch_bounds__(256) tpa_bwd_stats_kernel(const Params p, const __nv_bfloat16* d_o,
                                                             float* stats, int tiles) {
   const int lane = threadIdx.x & 31;
@@ -112,7 +137,7 @@ __global__ void __launch_bounds__(256) tpa_bwd_stats_kernel(const Params p, cons
   const int64_t rest = w / p.heads;
   const int row = (int)(rest % ((int64_t)tiles * kRows));
   const int batch = (int)(rest / ((int64_t)tiles * kRows));
-  float acc = 0.f, l2 = CUDART_INF_F;
+  float acc = 0.f, nl2 = -CUDART_INF_F;
   if (row < p.lq) {
     const int64_t rh = ((int64_t)batch * p.lq + row) * p.heads + head;
     const __nv_bfloat16* o = static_cast<const __nv_bfloat16*>(p.o) + rh * p.dv;
@@ -124,12 +149,12 @@ __global__ void __launch_bounds__(256) tpa_bwd_stats_kernel(const Params p, cons
 #pragma unroll
     for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
     const float lse = p.lse[rh];
-    if (lse != -CUDART_INF_F) l2 = lse * kLog2e;
+    if (lse != -CUDART_INF_F) nl2 = -lse * kLog2e;
   }
   if (lane == 0) {
     float* dst = stats + (((int64_t)batch * p.heads + head) * tiles + row / kRows) * (2 * kRows) + row % kRows;
-    dst[0] = l2;
-    dst[kRows] = acc;
+    dst[0] = nl2;
+    dst[kRows] = -acc;
   }
 }
 
@@ -258,13 +283,14 @@ tpa_bwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
                          : p.kv_seg + (int64_t)batch * p.kv_seg_bstride;
       if (own_ok) own_seg = own_ids[own_idx];
     }
-    float my_l2 = CUDART_INF_F, my_dl = 0.f;  // !KV_OWNER: this lane's query row
+    float my_nl2 = -CUDART_INF_F, my_ndl = 0.f;  // !KV_OWNER: this lane's query row
     if (!KV_OWNER) {
       const float* st = stats + (bh * nq + own) * (2 * kRows);
-      my_l2 = st[row];
-      my_dl = st[kRows + row];
+      my_nl2 = st[row];
+      my_ndl = st[kRows + row];
     }
     const float inv_rk = 1.f / (float)p.rank_k;
+    const uint64_t my_nl2_2 = pack2(my_nl2, my_nl2), my_ndl_2 = pack2(my_ndl, my_ndl), inv_rk_2 = pack2(inv_rk, inv_rk);
     const int64_t lane0_pos = (int64_t)own0 + quarter * 32 + (KV_OWNER ? p.k_offset : p.q_offset);
 
     if (kOwnTmem && n_tiles > 0) {
@@ -305,7 +331,7 @@ tpa_bwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
       }
       if (!KV_OWNER) masked = masked || (m0 + 32 > p.lk);  // padded keys of a ragged last tile
 
-      // ---- phase 1: p = 2^(T1 - log2e lse), as soon as the first GEMM is done (the second runs meanwhile)
+      // ---- phase 1: p = 2^(T1 + (-log2e lse)), as soon as the first GEMM is done (the second runs meanwhile)
       wait(&bars->t_full[0], n & 1, 0x100);
       tc_fence_after();
       if (KV_OWNER) wait(&bars->y_full[s], (n / kStages) & 1, 0x102);  // the statistics have landed
@@ -337,9 +363,10 @@ tpa_bwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
         }
 #pragma unroll
         for (int e = 0; e < 16; e += 2) {
-          const float p0 = ex2(__uint_as_float(t1[e]) - (KV_OWNER ? l2v[e] : my_l2));
-          const float p1 = ex2(__uint_as_float(t1[e + 1]) - (KV_OWNER ? l2v[e + 1] : my_l2));
-          ppk[c * 8 + e / 2] = pack_bf16(p0, p1);
+          float x0, x1;
+          unpack2(add2(pack2(__uint_as_float(t1[e]), __uint_as_float(t1[e + 1])),
+                       KV_OWNER ? pack2(l2v[e], l2v[e + 1]) : my_nl2_2), x0, x1);
+          ppk[c * 8 + e / 2] = pack_bf16(ex2(x0), ex2(x1));
         }
       }
       // bf16 p overwrites the first 16 of the thread's own 32 fp32 columns: moving row k of the
@@ -352,7 +379,7 @@ tpa_bwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->p_ready[0]);  // T1 has been read (and holds p)
 
-      // ---- phase 2: ds = p (T2 / R_k - delta), p as rounded to bf16 above
+      // ---- phase 2: ds = p (T2 / R_k + (-delta)), p as rounded to bf16 above
       wait(&bars->t_full[1], n & 1, 0x101);
       tc_fence_after();
       uint32_t dpk[16];
@@ -373,9 +400,10 @@ tpa_bwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
 #pragma unroll
         for (int e = 0; e < 16; e += 2) {
           const uint32_t pw = ppk[c * 8 + e / 2];
-          const float p0 = __uint_as_float(pw << 16), p1 = __uint_as_float(pw & 0xffff0000u);
-          const float d0 = p0 * fmaf(__uint_as_float(t2[e]), inv_rk, -(KV_OWNER ? dlv[e] : my_dl));
-          const float d1 = p1 * fmaf(__uint_as_float(t2[e + 1]), inv_rk, -(KV_OWNER ? dlv[e + 1] : my_dl));
+          const uint64_t p2 = pack2(__uint_as_float(pw << 16), __uint_as_float(pw & 0xffff0000u));
+          float d0, d1;
+          unpack2(mul2(p2, fma2(pack2(__uint_as_float(t2[e]), __uint_as_float(t2[e + 1])), inv_rk_2,
+                                KV_OWNER ? pack2(dlv[e], dlv[e + 1]) : my_ndl_2)), d0, d1);
           dpk[c * 8 + e / 2] = pack_bf16(d0, d1);
         }
       }
