@@ -52,7 +52,12 @@ enum {
   TPA_KERNEL_SIMT = 1,
   TPA_KERNEL_SM100 = 2,
   TPA_KERNEL_SM100_FUSED = 3,
-  TPA_KERNEL_SM100_STAGED = 4
+  TPA_KERNEL_SM100_STAGED = 4,
+  TPA_KERNEL_DECODE = 5 /* at most 8 query rows against >= 256 keys, bf16, heads <= 64 (a multiple
+                           of 8), head dims <= 128 (multiples of 8), 16-byte aligned factors:
+                           K and V are never materialised (rank-space logits, tpa/tpa.py:333-359);
+                           AUTO picks it for a single query row with rank_k <= 3, where it is
+                           measured faster than the staged path                              */
 };
 
 /* flags */
@@ -106,7 +111,8 @@ typedef struct TpaFwdArgs {
 } TpaFwdArgs;
 
 typedef struct TpaKernelInfo {
-  int32_t kernel;       /* TPA_KERNEL_SIMT, TPA_KERNEL_SM100_FUSED or TPA_KERNEL_SM100_STAGED */
+  int32_t kernel;       /* TPA_KERNEL_SIMT, TPA_KERNEL_SM100_FUSED, TPA_KERNEL_SM100_STAGED or
+                           TPA_KERNEL_DECODE                                                */
   int32_t block_q, block_kv; /* tile sizes the kernel will use                             */
   int32_t threads;      /* threads per CTA                                                 */
   int32_t grid[3];

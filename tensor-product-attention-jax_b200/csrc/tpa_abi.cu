@@ -42,7 +42,7 @@ static int validate(const TpaFwdArgs* a, Params* p) {
   if (a->flags & ~(uint32_t)(TPA_FLAG_CAUSAL | TPA_FLAG_STATE_LOAD | TPA_FLAG_STATE_STORE |
                              TPA_FLAG_REUSE_STAGED_Q))
     return TPA_ERR_BAD_ARG;
-  if (a->kernel < TPA_KERNEL_AUTO || a->kernel > TPA_KERNEL_SM100_STAGED) return TPA_ERR_BAD_ARG;
+  if (a->kernel < TPA_KERNEL_AUTO || a->kernel > TPA_KERNEL_DECODE) return TPA_ERR_BAD_ARG;
   if (a->heads > 65535 || a->batch > 65535) return TPA_ERR_UNSUPPORTED;
   if (a->dk > 256 || a->dv > 256) return TPA_ERR_UNSUPPORTED;
   p->dtype = a->dtype;
@@ -60,8 +60,14 @@ static int validate(const TpaFwdArgs* a, Params* p) {
 }
 
 static int choose(const TpaFwdArgs* a, const Params& p, int* kernel) {
+  const bool dec = decode_supported(p);
+  if (a->kernel == TPA_KERNEL_DECODE && !dec) return TPA_ERR_KERNEL_FORCED;
+  if (a->kernel == TPA_KERNEL_DECODE || (a->kernel == TPA_KERNEL_AUTO && decode_preferred(p))) {
+    *kernel = TPA_KERNEL_DECODE;
+    return TPA_OK;
+  }
   const bool tc = sm100_supported(p);
-  if (a->kernel >= TPA_KERNEL_SM100 && !tc) return TPA_ERR_KERNEL_FORCED;
+  if (a->kernel >= TPA_KERNEL_SM100 && a->kernel <= TPA_KERNEL_SM100_STAGED && !tc) return TPA_ERR_KERNEL_FORCED;
   if (a->kernel == TPA_KERNEL_SIMT || !tc) *kernel = TPA_KERNEL_SIMT;
   else if (a->kernel == TPA_KERNEL_SM100_FUSED || a->kernel == TPA_KERNEL_SM100_STAGED) *kernel = a->kernel;
   else *kernel = sm100_pick_variant(p);
@@ -98,8 +104,7 @@ static int validate_bwd(const TpaBwdArgs* a, BwdParams* bp) {
     return TPA_ERR_BAD_ARG;
   if (a->bwd_flags & ~(uint32_t)(TPA_BWD_ACCUMULATE_DQ | TPA_BWD_ACCUMULATE_DKV)) return TPA_ERR_BAD_ARG;
   if (a->grad_dtype != TPA_DTYPE_F32 && a->grad_dtype != a->fwd.dtype) return TPA_ERR_UNSUPPORTED;
-  if (a->fwd.kernel == TPA_KERNEL_SM100_FUSED || a->fwd.kernel == TPA_KERNEL_SM100_STAGED)
-    return TPA_ERR_KERNEL_FORCED;
+  if (a->fwd.kernel >= TPA_KERNEL_SM100_FUSED) return TPA_ERR_KERNEL_FORCED;
   bp->d_o = a->d_o;
   bp->dq = a->dq; bp->dk = a->dk; bp->dv = a->dv;
   bp->grad_dtype = a->grad_dtype;
@@ -148,6 +153,7 @@ size_t tpa_fwd_workspace_bytes(const TpaFwdArgs* args) {
   int kernel;
   if (validate(args, &p) != TPA_OK || choose(args, p, &kernel) != TPA_OK) return 0;
   if (kernel == TPA_KERNEL_SIMT) return 0;
+  if (kernel == TPA_KERNEL_DECODE) return kStatusBytes + decode_workspace_bytes(p);
   return kStatusBytes + sm100_workspace_bytes(p, kernel);
 }
 
@@ -160,7 +166,8 @@ int tpa_query_kernel(const TpaFwdArgs* args, TpaKernelInfo* info) {
   if (st != TPA_OK) return st;
   st = choose(args, p, &kernel);
   if (st != TPA_OK) return st;
-  cudaError_t e = (kernel != TPA_KERNEL_SIMT) ? launch_sm100(p, kernel, nullptr, info, true, nullptr)
+  cudaError_t e = kernel == TPA_KERNEL_DECODE ? launch_decode(p, nullptr, info, true, nullptr)
+                  : kernel != TPA_KERNEL_SIMT ? launch_sm100(p, kernel, nullptr, info, true, nullptr)
                                               : launch_simt(p, info, true, nullptr);
   return e == cudaSuccess ? TPA_OK : fail_cuda(e);
 }
@@ -175,14 +182,17 @@ int tpa_fwd(const TpaFwdArgs* args, void* workspace, size_t workspace_bytes, voi
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   cudaError_t e;
   if (kernel != TPA_KERNEL_SIMT) {
-    const size_t need = kStatusBytes + sm100_workspace_bytes(p, kernel);
+    const size_t need = kStatusBytes + (kernel == TPA_KERNEL_DECODE ? decode_workspace_bytes(p)
+                                                                     : sm100_workspace_bytes(p, kernel));
     if (workspace == nullptr || workspace_bytes < need ||
         (reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
       return TPA_ERR_WORKSPACE;
     p.status = static_cast<uint32_t*>(workspace);
     e = cudaMemsetAsync(workspace, 0, kStatusBytes, s);
     if (e != cudaSuccess) return fail_cuda(e);
-    e = launch_sm100(p, kernel, static_cast<char*>(workspace) + kStatusBytes, nullptr, false, s);
+    e = kernel == TPA_KERNEL_DECODE
+            ? launch_decode(p, static_cast<char*>(workspace) + kStatusBytes, nullptr, false, s)
+            : launch_sm100(p, kernel, static_cast<char*>(workspace) + kStatusBytes, nullptr, false, s);
   } else {
     e = launch_simt(p, nullptr, false, s);
   }

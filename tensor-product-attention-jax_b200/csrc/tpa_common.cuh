@@ -60,6 +60,15 @@ size_t sm100_workspace_bytes(const Params& p, int variant);
 cudaError_t launch_sm100(const Params& p, int variant, void* workspace, TpaKernelInfo* info,
                          bool dry_run, cudaStream_t stream);
 
+// few query rows against a long factor cache (tpa_fwd_decode.cu); scratch = per-split partials
+bool decode_supported(const Params& p);   // the kernel can run this call
+bool decode_preferred(const Params& p);   // ... and is measured faster than the staged path
+size_t decode_workspace_bytes(const Params& p);
+cudaError_t launch_decode(const Params& p, void* workspace, TpaKernelInfo* info, bool dry_run, cudaStream_t stream);
+// merges per-split partial (o, lse) (and the carried state) into the output or the state
+cudaError_t launch_combine_splits(const Params& p, const float* part_o, const float* part_lse, int splits,
+                                  cudaStream_t stream);
+
 void count_launch(int n);
 
 __device__ __forceinline__ float to_float(float x) { return x; }

@@ -1,0 +1,314 @@
+// TPA forward for a handful of query rows against a long key/value factor cache (decode and
+// cross shapes, tpa/tpa_test.py:67-70; bf16 factors).  K and V are never materialised:
+//
+//   logits  s[h, j] = c * sum_{rq, rk} qa[rq, h] ka[j, rk, h] (qb[rq, :] . kb[j, rk, :])
+//           the rank-space form of the reference's `nomat` branch (tpa/tpa.py:333-359):
+//           R_q R_k (d + h) multiply-adds per key instead of R_k h d
+//   output  o[h, :] = (1 / R_k) sum_{j, rk} (p[h, j] va[j, rk, h]) vb[j, rk, :]
+//
+// so every factor byte is read from HBM exactly once per query row and nothing else is: the
+// staged tensor-core path rebuilds and writes all heads' dense K/V tiles first (h d / (R_k (h+d))
+// = 12.8x the factor bytes at h = 32, d = 128, R_k = 2), which is what a single decode row cannot
+// amortise.  fp32 math on CUDA cores: measured 340-360 GB/s of factor stream (1.8x the staged
+// path for one row), i.e. bound by its own instruction stream and load latency, not yet by HBM.
+//
+// grid = (key splits, query rows, batch); 256 threads.  A CTA walks its share of the keys in tiles
+// of 64 (key, rank) rows, keeps a running (max, sum) per head and the h x dv accumulator in
+// registers (warp w owns heads w, w + 8, ...; lane l owns value columns 4 l .. 4 l + 3), and leaves
+// a normalised partial (o, lse) per split that tpa_combine_splits_kernel merges (with the caller's
+// carried state, if any) exactly as a ring step's partials are merged (tpa/ring_tpa.py:82-91).
+#include <math_constants.h>
+
+#include "tpa_common.cuh"
+
+namespace tpa {
+namespace {
+
+constexpr int DEC_THREADS = 256;
+constexpr int DEC_JR = 64;  // (key, rank) rows per tile
+
+__device__ __forceinline__ void bf16x8_to_float(const uint4 v, float* dst) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    dst[2 * e] = __uint_as_float(w[e] << 16);
+    dst[2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u);
+  }
+}
+
+// rows [0, n_rows) of `dst` (pitch ld floats) = 8-element chunks of the factor rows jr -> (key0 + jr / rank, jr % rank)
+__device__ __forceinline__ void load_factor_rows(float* dst, int ld, const __nv_bfloat16* f, const int64_t* st,
+                                                 int key0, int key_end, int rank, int cols, int tid) {
+  const int chunks = cols >> 3;
+  for (int idx = tid; idx < DEC_JR * chunks; idx += DEC_THREADS) {
+    const int jr = idx / chunks, c = idx - jr * chunks;
+    const int key = key0 + jr / rank, rk = jr % rank;
+    float v[8];
+    if (key < key_end && jr < (DEC_JR / rank) * rank) {
+      bf16x8_to_float(__ldg(reinterpret_cast<const uint4*>(f + (int64_t)key * st[1] + (int64_t)rk * st[2] + c * 8)), v);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] = 0.f;
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) dst[jr * ld + c * 8 + e] = v[e];
+  }
+}
+
+template <int NH>
+__global__ void __launch_bounds__(DEC_THREADS)
+tpa_fwd_decode_kernel(const Params p, float* part_o, float* part_lse, const int keys_per_split) {
+  extern __shared__ float smem[];
+  const int h = p.heads, dk = p.dk, dv = p.dv, rq = p.rank_q, rk = p.rank_k;
+  const int KT = DEC_JR / rk;  // keys per tile
+  const int ldk = dk + 1;      // +1: rows of a tile land in different banks
+  float* qbS = smem;                       // [rq][dk]
+  float* qaS = qbS + rq * dk;              // [rq][h], times sm_scale / (R_q R_k)
+  float* kbS = qaS + rq * h;               // [JR][dk + 1]
+  float* vbS = kbS + DEC_JR * ldk;         // [JR][dv]
+  float* kaS = vbS + DEC_JR * dv;          // [JR][h]
+  float* vaS = kaS + DEC_JR * h;           // [JR][h]
+  float* dots = vaS + DEC_JR * h;          // [JR][rq]
+  float* sS = dots + DEC_JR * rq;          // [h][KT + 1] logits, then p
+  float* wS = sS + h * (DEC_JR + 1);       // [JR][h] p * va
+  float* mS = wS + h * DEC_JR;             // [h] running maximum
+  float* lS = mS + h;                      // [h] running sum
+  float* cS = lS + h;                      // [h] correction of this tile
+  int* ksegS = reinterpret_cast<int*>(cS + h);  // [KT]
+
+  const int split = blockIdx.x, qi = blockIdx.y, b = blockIdx.z;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const bool causal = (p.flags & TPA_FLAG_CAUSAL) != 0;
+  const bool has_seg = p.q_seg != nullptr;
+  const __nv_bfloat16* qa = static_cast<const __nv_bfloat16*>(p.qa.ptr) + (int64_t)b * p.qa.stride[0] + (int64_t)qi * p.qa.stride[1];
+  const __nv_bfloat16* qb = static_cast<const __nv_bfloat16*>(p.qb.ptr) + (int64_t)b * p.qb.stride[0] + (int64_t)qi * p.qb.stride[1];
+  const __nv_bfloat16* ka = static_cast<const __nv_bfloat16*>(p.ka.ptr) + (int64_t)b * p.ka.stride[0];
+  const __nv_bfloat16* kb = static_cast<const __nv_bfloat16*>(p.kb.ptr) + (int64_t)b * p.kb.stride[0];
+  const __nv_bfloat16* va = static_cast<const __nv_bfloat16*>(p.va.ptr) + (int64_t)b * p.va.stride[0];
+  const __nv_bfloat16* vb = static_cast<const __nv_bfloat16*>(p.vb.ptr) + (int64_t)b * p.vb.stride[0];
+  const int32_t* kseg_g = has_seg ? p.kv_seg + (int64_t)b * p.kv_seg_bstride : nullptr;
+  const int qseg = has_seg ? p.q_seg[(int64_t)b * p.q_seg_bstride + qi] : 0;
+
+  // this CTA's keys, cut at the causal diagonal (tpa/tpa.py:376-379 with global offsets)
+  int k_begin = split * keys_per_split;
+  int k_end = min(p.lk, k_begin + keys_per_split);
+  if (causal) {
+    const int64_t last = (int64_t)qi + p.q_offset - p.k_offset;  // last visible local key
+    k_end = (int)max((int64_t)k_begin, min((int64_t)k_end, last + 1));
+  }
+
+  const float c = p.sm_scale / ((float)rq * (float)rk);
+  for (int idx = tid; idx < rq * dk; idx += DEC_THREADS)
+    qbS[idx] = to_float(qb[(idx / dk) * p.qb.stride[2] + idx % dk]);
+  for (int idx = tid; idx < rq * h; idx += DEC_THREADS)
+    qaS[idx] = c * to_float(qa[(idx / h) * p.qa.stride[2] + idx % h]);
+  for (int idx = tid; idx < h; idx += DEC_THREADS) {
+    mS[idx] = -CUDART_INF_F;
+    lS[idx] = 0.f;
+  }
+  float acc[NH][4];
+#pragma unroll
+  for (int i = 0; i < NH; ++i)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[i][e] = 0.f;
+
+  for (int k0 = k_begin; k0 < k_end; k0 += KT) {
+    __syncthreads();  // the previous tile's readers are done (and the query factors are written)
+    load_factor_rows(kbS, ldk, kb, p.kb.stride, k0, k_end, rk, dk, tid);
+    load_factor_rows(vbS, dv, vb, p.vb.stride, k0, k_end, rk, dv, tid);
+    load_factor_rows(kaS, h, ka, p.ka.stride, k0, k_end, rk, h, tid);
+    load_factor_rows(vaS, h, va, p.va.stride, k0, k_end, rk, h, tid);
+    if (has_seg && tid < KT) ksegS[tid] = (k0 + tid < k_end) ? kseg_g[k0 + tid] : 0;
+    __syncthreads();
+
+    // dots[jr][r] = qb[r, :] . kb[jr, :]: thread (jr = tid % 64) takes r = tid / 64, + 4, ...
+    {
+      const int jr = tid & (DEC_JR - 1);
+      const float* kr = kbS + jr * ldk;
+      for (int r = tid >> 6; r < rq; r += DEC_THREADS / DEC_JR) {
+        const float* qr = qbS + r * dk;
+        float d0 = 0.f, d1 = 0.f;
+        for (int t = 0; t < dk; t += 2) {
+          d0 = fmaf(kr[t], qr[t], d0);
+          d1 = fmaf(kr[t + 1], qr[t + 1], d1);
+        }
+        dots[jr * rq + r] = d0 + d1;
+      }
+    }
+    __syncthreads();
+
+    // logits s[hh][key] = sum_rk ka[jr][hh] * sum_r qa[r][hh] dots[jr][r]; masked entries -inf
+    for (int idx = tid; idx < h * KT; idx += DEC_THREADS) {
+      const int key = idx / h, hh = idx - key * h;
+      float s = 0.f;
+      for (int q = 0; q < rk; ++q) {
+        const int jr = key * rk + q;
+        float e = 0.f;
+        for (int r = 0; r < rq; ++r) e = fmaf(qaS[r * h + hh], dots[jr * rq + r], e);
+        s = fmaf(kaS[jr * h + hh], e, s);
+      }
+      bool keep = k0 + key < k_end;
+      if (has_seg && keep) keep = ksegS[key] == qseg;
+      sS[hh * (DEC_JR + 1) + key] = keep ? s : -CUDART_INF_F;
+    }
+    __syncthreads();
+
+    // running softmax per head: warp w takes heads w, w + 8, ...; lanes over the tile's keys
+    for (int hh = warp; hh < h; hh += DEC_THREADS / 32) {
+      float* srow = sS + hh * (DEC_JR + 1);
+      const float x0 = lane < KT ? srow[lane] : -CUDART_INF_F;
+      const float x1 = lane + 32 < KT ? srow[lane + 32] : -CUDART_INF_F;
+      float tmax = fmaxf(x0, x1);
+#pragma unroll
+      for (int s = 16; s > 0; s >>= 1) tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, s));
+      const float m_old = mS[hh], m_new = fmaxf(m_old, tmax);
+      float p0 = 0.f, p1 = 0.f, corr = 1.f;
+      if (m_new != -CUDART_INF_F) {
+        corr = (m_old == -CUDART_INF_F) ? 0.f : expf(m_old - m_new);
+        p0 = expf(x0 - m_new);  // exp(-inf) = 0 for masked entries
+        p1 = expf(x1 - m_new);
+      }
+      float psum = p0 + p1;
+#pragma unroll
+      for (int s = 16; s > 0; s >>= 1) psum += __shfl_xor_sync(0xffffffffu, psum, s);
+      if (lane < KT) srow[lane] = p0;
+      if (lane + 32 < KT) srow[lane + 32] = p1;
+      if (lane == 0) {
+        mS[hh] = m_new;
+        lS[hh] = lS[hh] * corr + psum;
+        cS[hh] = corr;
+      }
+    }
+    __syncthreads();
+
+    // w[hh][jr] = p[hh][key] * va[jr][hh]
+    for (int idx = tid; idx < h * DEC_JR; idx += DEC_THREADS) {
+      const int jr = idx / h, hh = idx - jr * h;
+      const int key = jr / rk;
+      wS[jr * h + hh] = key < KT ? sS[hh * (DEC_JR + 1) + key] * vaS[jr * h + hh] : 0.f;
+    }
+    __syncthreads();
+
+    // acc[hh][:] = acc * corr + sum_jr w[hh][jr] vb[jr][:]
+    if (lane * 4 < dv) {
+#pragma unroll
+      for (int i = 0; i < NH; ++i) {
+        const int hh = warp + 8 * i;
+        const float corr = hh < h ? cS[hh] : 1.f;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[i][e] *= corr;
+      }
+      const int n_jr = KT * rk;
+      for (int jr = 0; jr < n_jr; ++jr) {
+        const float4 v = *reinterpret_cast<const float4*>(vbS + jr * dv + lane * 4);
+#pragma unroll
+        for (int i = 0; i < NH; ++i) {
+          const int hh = warp + 8 * i;
+          const float w = hh < h ? wS[jr * h + hh] : 0.f;
+          acc[i][0] = fmaf(w, v.x, acc[i][0]);
+          acc[i][1] = fmaf(w, v.y, acc[i][1]);
+          acc[i][2] = fmaf(w, v.z, acc[i][2]);
+          acc[i][3] = fmaf(w, v.w, acc[i][3]);
+        }
+      }
+    }
+  }
+  __syncthreads();
+
+  // normalised partial of this split: 0 / -inf where nothing was visible
+  const int64_t rows = (int64_t)p.batch * p.lq * h;
+  const int64_t rh0 = ((int64_t)b * p.lq + qi) * h;
+#pragma unroll
+  for (int i = 0; i < NH; ++i) {
+    const int hh = warp + 8 * i;
+    if (hh >= h) continue;
+    const float l = lS[hh];
+    const bool empty = !(l > 0.f);
+    const float inv = empty ? 0.f : 1.f / (l * (float)rk);
+    if (lane * 4 < dv)
+      *reinterpret_cast<float4*>(part_o + ((int64_t)split * rows + rh0 + hh) * dv + lane * 4) =
+          make_float4(acc[i][0] * inv, acc[i][1] * inv, acc[i][2] * inv, acc[i][3] * inv);
+    if (lane == 0) part_lse[(int64_t)split * rows + rh0 + hh] = empty ? -CUDART_INF_F : mS[hh] + logf(l);
+  }
+}
+
+inline bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; }
+inline bool vec_ok(const TpaFactor& f) {
+  return aligned16(f.ptr) && f.stride[0] % 8 == 0 && f.stride[1] % 8 == 0 && f.stride[2] % 8 == 0;
+}
+inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
+
+size_t decode_smem_bytes(const Params& p) {
+  const size_t floats = (size_t)p.rank_q * (p.dk + p.heads) + (size_t)DEC_JR * (p.dk + 1 + p.dv + 2 * p.heads + p.rank_q) +
+                        (size_t)p.heads * (DEC_JR + 1 + DEC_JR + 3) + DEC_JR;
+  return floats * sizeof(float);
+}
+
+}  // namespace
+
+// A few query rows against many keys: bf16, vector-loadable factors, h <= 64 and d <= 128.
+bool decode_supported(const Params& p) {
+  if (p.dtype != TPA_DTYPE_BF16 || p.lq > 8 || p.lk < 256) return false;
+  if (p.heads > 64 || p.heads % 8 != 0 || p.dk > 128 || p.dv > 128 || p.dk % 8 != 0 || p.dv % 8 != 0) return false;
+  if (p.rank_q > 16 || p.rank_k > 8) return false;
+  if (!vec_ok(p.ka) || !vec_ok(p.kb) || !vec_ok(p.va) || !vec_ok(p.vb)) return false;
+  if (!(p.flags & TPA_FLAG_STATE_STORE) && !aligned16(p.o)) return false;
+  if ((p.flags & (TPA_FLAG_STATE_STORE | TPA_FLAG_STATE_LOAD)) && !aligned16(p.state_o)) return false;
+  return decode_smem_bytes(p) <= 200 * 1024;
+}
+
+// Measured (h = 32, d = 128, batch 16 x 32768 keys): one row, R_k = 2: 1.98 ms against 3.57 ms for the
+// staged tensor-core path; R_k = 4: 3.88 against 3.75; four rows: 7.4 against 3.57 (the rows are
+// walked one after the other here, the staged path shares its tiles among them).
+bool decode_preferred(const Params& p) { return decode_supported(p) && p.lq == 1 && p.rank_k <= 3; }
+
+int decode_pick_splits(const Params& p) {
+  const int KT = DEC_JR / p.rank_k;
+  const int64_t ctas = (int64_t)p.lq * p.batch;
+  int splits = (int)((2 * 148 + ctas - 1) / ctas);            // about two waves of CTAs
+  const int max_splits = (p.lk + 4 * KT - 1) / (4 * KT);      // at least four tiles each
+  if (splits > max_splits) splits = max_splits;
+  if (splits > 64) splits = 64;
+  return splits < 1 ? 1 : splits;
+}
+
+size_t decode_workspace_bytes(const Params& p) {
+  return align256((size_t)decode_pick_splits(p) * p.batch * p.lq * p.heads * (p.dv + 1) * sizeof(float));
+}
+
+cudaError_t launch_decode(const Params& p, void* workspace, TpaKernelInfo* info, bool dry_run, cudaStream_t stream) {
+  const int splits = decode_pick_splits(p);
+  const int KT = DEC_JR / p.rank_k;
+  int keys_per_split = (p.lk + splits - 1) / splits;
+  keys_per_split = (keys_per_split + KT - 1) / KT * KT;  // whole tiles
+  const size_t smem = decode_smem_bytes(p);
+  dim3 grid(splits, p.lq, p.batch);
+  if (info) {
+    info->kernel = TPA_KERNEL_DECODE;
+    info->block_q = 1;
+    info->block_kv = KT;
+    info->threads = DEC_THREADS;
+    info->grid[0] = grid.x; info->grid[1] = grid.y; info->grid[2] = grid.z;
+    info->smem_bytes = (int)smem;
+    info->launches = 2;
+  }
+  if (dry_run) return cudaSuccess;
+  float* part_o = static_cast<float*>(workspace);
+  float* part_lse = part_o + (size_t)splits * p.batch * p.lq * p.heads * p.dv;
+  auto launch = [&](auto kern) -> cudaError_t {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    kern<<<grid, DEC_THREADS, smem, stream>>>(p, part_o, part_lse, keys_per_split);
+    return cudaGetLastError();
+  };
+  cudaError_t e;
+  if (p.heads <= 8) e = launch(tpa_fwd_decode_kernel<1>);
+  else if (p.heads <= 16) e = launch(tpa_fwd_decode_kernel<2>);
+  else if (p.heads <= 32) e = launch(tpa_fwd_decode_kernel<4>);
+  else e = launch(tpa_fwd_decode_kernel<8>);
+  if (e != cudaSuccess) return e;
+  count_launch(1);
+  return launch_combine_splits(p, part_o, part_lse, splits, stream);
+}
+
+}  // namespace tpa

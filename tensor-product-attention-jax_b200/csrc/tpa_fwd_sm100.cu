@@ -1113,6 +1113,14 @@ cudaError_t launch_attn(const Params& p, const uint8_t* wq, const uint8_t* wk, c
 
 }  // namespace
 
+cudaError_t launch_combine_splits(const Params& p, const float* part_o, const float* part_lse, int splits,
+                                  cudaStream_t stream) {
+  const int64_t threads = (int64_t)p.batch * p.lq * p.heads * (p.dv / 4);
+  tpa_combine_splits_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(p, part_o, part_lse, splits);
+  count_launch(1);
+  return cudaGetLastError();
+}
+
 // Rebuilds every 128-row tile of Q (times qscale), K and V of all heads into the three arrays
 // (the staging launch of the STAGED forward; the backward reads the same images).
 cudaError_t launch_stage_tiles(const Params& p, uint8_t* wq, uint8_t* wk, uint8_t* wv, float qscale,

@@ -24,10 +24,11 @@ TPA_ERR_STATIC_SCRATCH = -7
 STATIC_SCRATCH_BYTES = 64 << 20
 
 DTYPE_F32, DTYPE_BF16 = 0, 1
-KERNEL_AUTO, KERNEL_SIMT, KERNEL_SM100, KERNEL_SM100_FUSED, KERNEL_SM100_STAGED = 0, 1, 2, 3, 4
+KERNEL_AUTO, KERNEL_SIMT, KERNEL_SM100, KERNEL_SM100_FUSED, KERNEL_SM100_STAGED, KERNEL_DECODE = 0, 1, 2, 3, 4, 5
 KERNELS = {"auto": KERNEL_AUTO, "simt": KERNEL_SIMT, "sm100": KERNEL_SM100,
-           "sm100_fused": KERNEL_SM100_FUSED, "sm100_staged": KERNEL_SM100_STAGED}
-KERNEL_NAMES = {KERNEL_SIMT: "simt", KERNEL_SM100_FUSED: "sm100_fused", KERNEL_SM100_STAGED: "sm100_staged"}
+           "sm100_fused": KERNEL_SM100_FUSED, "sm100_staged": KERNEL_SM100_STAGED, "decode": KERNEL_DECODE}
+KERNEL_NAMES = {KERNEL_SIMT: "simt", KERNEL_SM100_FUSED: "sm100_fused", KERNEL_SM100_STAGED: "sm100_staged",
+                KERNEL_DECODE: "decode"}
 FLAG_CAUSAL, FLAG_STATE_LOAD, FLAG_STATE_STORE, FLAG_REUSE_STAGED_Q = 1, 2, 4, 8
 BWD_ACCUMULATE_DQ, BWD_ACCUMULATE_DKV = 1, 2
 

@@ -340,3 +340,56 @@ def test_ragged_lengths_on_tensor_cores(kernel, lq, lk, seg, causal):
     assert diff.max() <= 2e-2 and diff.mean() <= 5e-3, (float(diff.max()), float(diff.mean()))
     fin = ~torch.isinf(wl)
     assert ((lse - wl)[fin].abs() <= 2e-2).all()
+
+
+DECODE_CASES = [
+    # b, lq, lk, rq, rk, h, dk, dv, seg, causal, q_off
+    (2, 1, 4096, 6, 2, 32, 128, 128, 0, False, 0),
+    (3, 1, 1000, 6, 2, 32, 128, 128, 0, True, 999),     # the newest token sees the whole cache
+    (1, 4, 2050, 2, 4, 16, 64, 64, 0, True, 2046),      # a few speculative rows, ragged last tile
+    (2, 8, 777, 3, 3, 8, 64, 128, 100, True, 700),      # rank 3 (tiles of 21 keys), packed ids, dk != dv
+    (1, 2, 3000, 12, 8, 64, 128, 128, 0, True, 10),     # 64 heads, rank 8; most keys above the diagonal
+    (1, 3, 512, 1, 1, 8, 8, 8, 0, False, 0),
+]
+
+
+@pytest.mark.parametrize("case", DECODE_CASES)
+def test_decode_kernel(case):
+    """Few query rows against a long factor cache: the rank-space kernel (K, V never materialised)
+    (the dispatcher picks it for a single row); against the oracle, the generic kernel, and chained through the
+    carried state in two halves."""
+    b, lq, lk, rq, rk, h, dk, dv, seg, causal, q_off = case
+    q, k, v = orc.make_factors(33, b, lq, lk, rq, rk, h, dk, dv)
+    tq, tk, tv = (dev(x, torch.bfloat16) for x in (q, k, v))
+    qs = dev(orc.segment_ids(b, lq, seg) + (q_off // seg if seg else 0)) if seg else None
+    ks = dev(orc.segment_ids(b, lk, seg)) if seg else None
+    scale = dk**-0.5
+    info = tpa_b200.tpa.query_kernel(tq, tk, tv, h, kernel="decode", causal=causal, segments=bool(seg))
+    assert info["kernel"] == "decode" and info["launches"] == 2, info
+    auto = tpa_b200.tpa.query_kernel(tq, tk, tv, h, causal=causal, segments=bool(seg))["kernel"]
+    assert (auto == "decode") == (lq == 1 and rk <= 3), auto  # the dispatcher takes it where it wins
+    n0 = _capi.lib.tpa_launch_count()
+    o, lse = tpa_b200.tpa.fwd_device(tq, tk, tv, h, qs, ks, scale, causal, q_offset=q_off, kernel="decode")
+    torch.cuda.synchronize()
+    assert _capi.lib.tpa_launch_count() - n0 == 2
+    f = lambda t: t.float().cpu()
+    ref, lref = orc.tpa_reference_torch(f(tq), f(tk), f(tv), h, None if qs is None else qs.cpu(),
+                                        None if ks is None else ks.cpu(), sm_scale=scale, causal=causal,
+                                        q_offset=q_off, return_lse=True)
+    assert torch.equal(torch.isnan(f(o)), torch.isnan(ref))
+    diff = torch.nan_to_num(f(o) - ref).abs()
+    assert diff.max() <= 2e-2 and diff.mean() <= 5e-3
+    assert torch.nan_to_num(lse.cpu() - lref, nan=0.0, posinf=0.0, neginf=0.0).abs().max() <= 1e-2
+    gen, _ = tpa_b200.tpa.fwd_device(tq, tk, tv, h, qs, ks, scale, causal, q_offset=q_off, kernel="simt")
+    assert torch.nan_to_num(f(o) - f(gen)).abs().max() <= 2e-2
+    # two halves of the cache chained through the carried state (what a ring step does)
+    half = (lk // 2) // 8 * 8
+    state = (torch.empty(b, lq, h, dv, device="cuda"), torch.empty(b, lq, h, device="cuda"))
+    ks1, ks2 = (None, None) if ks is None else (ks[:, :half].contiguous(), ks[:, half:].contiguous())
+    tpa_b200.tpa.fwd_device(tq, tk[:, :half], tv[:, :half], h, qs, ks1, scale, causal, q_offset=q_off,
+                            state=state, store_state=True, kernel="decode")
+    o2, _ = tpa_b200.tpa.fwd_device(tq, tk[:, half:], tv[:, half:], h, qs, ks2, scale, causal, q_offset=q_off,
+                                    k_offset=half, state=state, load_state=True, kernel="decode")
+    assert torch.nan_to_num(f(o2) - ref).abs().max() <= 2e-2
+    with pytest.raises(ValueError):  # forced on a shape it does not take
+        tpa_b200.tpa.fwd_device(tq.float(), tk.float(), tv.float(), h, kernel="decode")
