@@ -9,12 +9,12 @@
 // so every factor byte is read from HBM exactly once per query row and nothing else is: the
 // staged tensor-core path rebuilds and writes all heads' dense K/V tiles first (h d / (R_k (h+d))
 // = 12.8x the factor bytes at h = 32, d = 128, R_k = 2), which is what a single decode row cannot
-// amortise.  fp32 math on CUDA cores: measured 340-360 GB/s of factor stream (1.8x the staged
-// path for one row), i.e. bound by its own instruction stream and load latency, not yet by HBM.
+// amortise.  fp32 math on CUDA cores: measured 650-750 GB/s of factor stream (3.8x the staged
+// path for one row), i.e. still bound by its own instruction stream and block-wide syncs, not by HBM.
 //
 // grid = (key splits, query rows, batch); 256 threads.  A CTA walks its share of the keys in tiles
 // of 64 (key, rank) rows, keeps a running (max, sum) per head and the h x dv accumulator in
-// registers (warp w owns heads w, w + 8, ...; lane l owns value columns 4 l .. 4 l + 3), and leaves
+// registers (warp w owns value columns 16 w ...; lane l heads (h / 8)(l / 4) ... and 4 of those columns), and leaves
 // a normalised partial (o, lse) per split that tpa_combine_splits_kernel merges (with the caller's
 // carried state, if any) exactly as a ring step's partials are merged (tpa/ring_tpa.py:82-91).
 #include <math_constants.h>
@@ -27,51 +27,79 @@ namespace {
 constexpr int DEC_THREADS = 256;
 constexpr int DEC_JR = 64;  // (key, rank) rows per tile
 
-__device__ __forceinline__ void bf16x8_to_float(const uint4 v, float* dst) {
-  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-  for (int e = 0; e < 4; ++e) {
-    dst[2 * e] = __uint_as_float(w[e] << 16);
-    dst[2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u);
-  }
+__device__ __forceinline__ void bf16x8_to_float4(const uint4 v, float4& lo, float4& hi) {
+  lo = make_float4(__uint_as_float(v.x << 16), __uint_as_float(v.x & 0xffff0000u),
+                   __uint_as_float(v.y << 16), __uint_as_float(v.y & 0xffff0000u));
+  hi = make_float4(__uint_as_float(v.z << 16), __uint_as_float(v.z & 0xffff0000u),
+                   __uint_as_float(v.w << 16), __uint_as_float(v.w & 0xffff0000u));
 }
 
-// rows [0, n_rows) of `dst` (pitch ld floats) = 8-element chunks of the factor rows jr -> (key0 + jr / rank, jr % rank)
-__device__ __forceinline__ void load_factor_rows(float* dst, int ld, const __nv_bfloat16* f, const int64_t* st,
-                                                 int key0, int key_end, int rank, int cols, int tid) {
-  const int chunks = cols >> 3;
-  for (int idx = tid; idx < DEC_JR * chunks; idx += DEC_THREADS) {
-    const int jr = idx / chunks, c = idx - jr * chunks;
-    const int key = key0 + jr / rank, rk = jr % rank;
-    float v[8];
-    if (key < key_end && jr < (DEC_JR / rank) * rank) {
-      bf16x8_to_float(__ldg(reinterpret_cast<const uint4*>(f + (int64_t)key * st[1] + (int64_t)rk * st[2] + c * 8)), v);
-    } else {
+// One factor array of a tile: 16-byte chunks (8 bf16) of the rows jr -> (key0 + jr / rank, jr % rank),
+// fetched into registers while the previous tile is being computed and written to shared
+// memory (as fp32, row pitch ld) at the start of the next iteration.  Thread t owns chunk
+// t % CPR of the rows t / CPR + i * (256 / CPR), i < N (CPR = 16 or 8 chunks per row at most),
+// so that nothing has to be divided inside the key loop.
+template <int N, int CPR>
+struct TileLoad {
+  uint4 v[N];
+  int goff[N];    // element offset of the chunk relative to the tile's first key, -1: no such chunk
+  int keyrel[N];  // its key relative to the tile's first key
+  __device__ __forceinline__ void init(const int64_t* st, int rank, int cols, int tid) {
+    const int c = tid % CPR;
 #pragma unroll
-      for (int e = 0; e < 8; ++e) v[e] = 0.f;
+    for (int i = 0; i < N; ++i) {
+      const int jr = tid / CPR + i * (DEC_THREADS / CPR);
+      keyrel[i] = jr / rank;
+      const bool exists = c * 8 < cols && jr < (DEC_JR / rank) * rank;
+      goff[i] = exists ? (int)(keyrel[i] * st[1] + (jr % rank) * st[2] + c * 8) : -1;
     }
-#pragma unroll
-    for (int e = 0; e < 8; ++e) dst[jr * ld + c * 8 + e] = v[e];
   }
-}
+  __device__ __forceinline__ void fetch(const __nv_bfloat16* f, const int64_t* st, int key0, int key_end) {
+    const __nv_bfloat16* base = f + (int64_t)key0 * st[1];
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+      v[i] = make_uint4(0u, 0u, 0u, 0u);
+      if (goff[i] >= 0 && key0 + keyrel[i] < key_end) v[i] = __ldg(reinterpret_cast<const uint4*>(base + goff[i]));
+    }
+  }
+  __device__ __forceinline__ void store(float* dst, int ld, int cols, int tid) const {
+    const int c = tid % CPR;
+    if (c * 8 >= cols) return;
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+      const int jr = tid / CPR + i * (DEC_THREADS / CPR);
+      float4 lo, hi;
+      bf16x8_to_float4(v[i], lo, hi);
+      float2* d = reinterpret_cast<float2*>(dst + jr * ld + c * 8);  // ld is even, not always a multiple of 4
+      d[0] = make_float2(lo.x, lo.y);
+      d[1] = make_float2(lo.z, lo.w);
+      d[2] = make_float2(hi.x, hi.y);
+      d[3] = make_float2(hi.z, hi.w);
+    }
+  }
+};
 
+// NH = heads / 8: lane (hg = lane / 4, c = lane % 4) of warp w accumulates heads NH hg .. NH hg + NH - 1,
+// value columns 16 w + 4 c .. + 3 (a warp reads 64 bytes of a vb row and 32 NH bytes of w per step).
 template <int NH>
 __global__ void __launch_bounds__(DEC_THREADS)
 tpa_fwd_decode_kernel(const Params p, float* part_o, float* part_lse, const int keys_per_split) {
-  extern __shared__ float smem[];
+  extern __shared__ float4 smem4[];
+  float* smem = reinterpret_cast<float*>(smem4);
   const int h = p.heads, dk = p.dk, dv = p.dv, rq = p.rank_q, rk = p.rank_k;
   const int KT = DEC_JR / rk;  // keys per tile
-  const int ldk = dk + 1;      // +1: rows of a tile land in different banks
+  const int ldk = dk + 2;      // row pitch = 2 (mod 32) floats: the 64-bit reads of 32 rows hit every bank once
   float* qbS = smem;                       // [rq][dk]
   float* qaS = qbS + rq * dk;              // [rq][h], times sm_scale / (R_q R_k)
-  float* kbS = qaS + rq * h;               // [JR][dk + 1]
+  float* kbS = qaS + rq * h;               // [JR][dk + 2]
   float* vbS = kbS + DEC_JR * ldk;         // [JR][dv]
   float* kaS = vbS + DEC_JR * dv;          // [JR][h]
   float* vaS = kaS + DEC_JR * h;           // [JR][h]
-  float* dots = vaS + DEC_JR * h;          // [JR][rq]
-  float* sS = dots + DEC_JR * rq;          // [h][KT + 1] logits, then p
-  float* wS = sS + h * (DEC_JR + 1);       // [JR][h] p * va
-  float* mS = wS + h * DEC_JR;             // [h] running maximum
+  float* wS = vaS + DEC_JR * h;            // [JR][h] p * va
+  float* dotsP = wS + DEC_JR * h;          // [4][JR][rq] partial dots over a quarter of dk
+  float* dots = dotsP + 4 * DEC_JR * rq;   // [JR][rq]
+  float* sS = dots + DEC_JR * rq;          // [h][JR + 1] logits, then p
+  float* mS = sS + h * (DEC_JR + 1);       // [h] running maximum
   float* lS = mS + h;                      // [h] running sum
   float* cS = lS + h;                      // [h] correction of this tile
   int* ksegS = reinterpret_cast<int*>(cS + h);  // [KT]
@@ -106,35 +134,58 @@ tpa_fwd_decode_kernel(const Params p, float* part_o, float* part_lse, const int 
     mS[idx] = -CUDART_INF_F;
     lS[idx] = 0.f;
   }
+  const int hg = lane >> 2, col0 = warp * 16 + (lane & 3) * 4;
   float acc[NH][4];
 #pragma unroll
   for (int i = 0; i < NH; ++i)
 #pragma unroll
     for (int e = 0; e < 4; ++e) acc[i][e] = 0.f;
 
+  // 64 rows x (dk | dv <= 128: 16 chunks per row) = 4 chunks per thread, x (h <= 64: 8 chunks) = 2
+  TileLoad<4, 16> t_kb, t_vb;
+  TileLoad<2, 8> t_ka, t_va;
+  t_kb.init(p.kb.stride, rk, dk, tid);
+  t_vb.init(p.vb.stride, rk, dv, tid);
+  t_ka.init(p.ka.stride, rk, h, tid);
+  t_va.init(p.va.stride, rk, h, tid);
+  auto fetch = [&](int k0) {
+    t_kb.fetch(kb, p.kb.stride, k0, k_end);
+    t_vb.fetch(vb, p.vb.stride, k0, k_end);
+    t_ka.fetch(ka, p.ka.stride, k0, k_end);
+    t_va.fetch(va, p.va.stride, k0, k_end);
+  };
+  if (k_begin < k_end) fetch(k_begin);
+
   for (int k0 = k_begin; k0 < k_end; k0 += KT) {
     __syncthreads();  // the previous tile's readers are done (and the query factors are written)
-    load_factor_rows(kbS, ldk, kb, p.kb.stride, k0, k_end, rk, dk, tid);
-    load_factor_rows(vbS, dv, vb, p.vb.stride, k0, k_end, rk, dv, tid);
-    load_factor_rows(kaS, h, ka, p.ka.stride, k0, k_end, rk, h, tid);
-    load_factor_rows(vaS, h, va, p.va.stride, k0, k_end, rk, h, tid);
+    t_kb.store(kbS, ldk, dk, tid);
+    t_vb.store(vbS, dv, dv, tid);
+    t_ka.store(kaS, h, h, tid);
+    t_va.store(vaS, h, h, tid);
     if (has_seg && tid < KT) ksegS[tid] = (k0 + tid < k_end) ? kseg_g[k0 + tid] : 0;
+    if (k0 + KT < k_end) fetch(k0 + KT);  // in flight while this tile is computed
     __syncthreads();
 
-    // dots[jr][r] = qb[r, :] . kb[jr, :]: thread (jr = tid % 64) takes r = tid / 64, + 4, ...
+    // partial dots over a quarter of dk: thread (jr = tid % 64, g = tid / 64), all ranks of q
     {
-      const int jr = tid & (DEC_JR - 1);
+      const int jr = tid & (DEC_JR - 1), g = tid >> 6;
+      const int t0 = g * (dk >> 2), t1 = t0 + (dk >> 2);  // dk % 8 == 0: whole float2 steps
       const float* kr = kbS + jr * ldk;
-      for (int r = tid >> 6; r < rq; r += DEC_THREADS / DEC_JR) {
+      for (int r = 0; r < rq; ++r) {
         const float* qr = qbS + r * dk;
         float d0 = 0.f, d1 = 0.f;
-        for (int t = 0; t < dk; t += 2) {
-          d0 = fmaf(kr[t], qr[t], d0);
-          d1 = fmaf(kr[t + 1], qr[t + 1], d1);
+        for (int t = t0; t < t1; t += 2) {
+          const float2 kv = *reinterpret_cast<const float2*>(kr + t);
+          const float2 qv = *reinterpret_cast<const float2*>(qr + t);
+          d0 = fmaf(kv.x, qv.x, d0);
+          d1 = fmaf(kv.y, qv.y, d1);
         }
-        dots[jr * rq + r] = d0 + d1;
+        dotsP[(g * DEC_JR + jr) * rq + r] = d0 + d1;
       }
     }
+    __syncthreads();
+    for (int idx = tid; idx < DEC_JR * rq; idx += DEC_THREADS)
+      dots[idx] = (dotsP[idx] + dotsP[DEC_JR * rq + idx]) + (dotsP[2 * DEC_JR * rq + idx] + dotsP[3 * DEC_JR * rq + idx]);
     __syncthreads();
 
     // logits s[hh][key] = sum_rk ka[jr][hh] * sum_r qa[r][hh] dots[jr][r]; masked entries -inf
@@ -181,34 +232,44 @@ tpa_fwd_decode_kernel(const Params p, float* part_o, float* part_lse, const int 
     }
     __syncthreads();
 
-    // w[hh][jr] = p[hh][key] * va[jr][hh]
+    // w[jr][hh] = p[hh][key] * va[jr][hh]
     for (int idx = tid; idx < h * DEC_JR; idx += DEC_THREADS) {
       const int jr = idx / h, hh = idx - jr * h;
       const int key = jr / rk;
-      wS[jr * h + hh] = key < KT ? sS[hh * (DEC_JR + 1) + key] * vaS[jr * h + hh] : 0.f;
+      wS[idx] = key < KT ? sS[hh * (DEC_JR + 1) + key] * vaS[idx] : 0.f;
     }
     __syncthreads();
 
-    // acc[hh][:] = acc * corr + sum_jr w[hh][jr] vb[jr][:]
-    if (lane * 4 < dv) {
+    // acc[heads of hg][4 columns] = acc * corr + sum_jr w[jr][head] vb[jr][columns]
+    if (col0 < dv) {
 #pragma unroll
       for (int i = 0; i < NH; ++i) {
-        const int hh = warp + 8 * i;
-        const float corr = hh < h ? cS[hh] : 1.f;
+        const float corr = cS[hg * NH + i];
 #pragma unroll
         for (int e = 0; e < 4; ++e) acc[i][e] *= corr;
       }
       const int n_jr = KT * rk;
+      const float* wp = wS + hg * NH;
+      const float* vp = vbS + col0;
       for (int jr = 0; jr < n_jr; ++jr) {
-        const float4 v = *reinterpret_cast<const float4*>(vbS + jr * dv + lane * 4);
+        const float4 v = *reinterpret_cast<const float4*>(vp + jr * dv);
+        float w[NH];
+        if constexpr (NH % 4 == 0) {
+#pragma unroll
+          for (int i = 0; i < NH; i += 4) {
+            const float4 w4 = *reinterpret_cast<const float4*>(wp + jr * h + i);
+            w[i] = w4.x; w[i + 1] = w4.y; w[i + 2] = w4.z; w[i + 3] = w4.w;
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < NH; ++i) w[i] = wp[jr * h + i];
+        }
 #pragma unroll
         for (int i = 0; i < NH; ++i) {
-          const int hh = warp + 8 * i;
-          const float w = hh < h ? wS[jr * h + hh] : 0.f;
-          acc[i][0] = fmaf(w, v.x, acc[i][0]);
-          acc[i][1] = fmaf(w, v.y, acc[i][1]);
-          acc[i][2] = fmaf(w, v.z, acc[i][2]);
-          acc[i][3] = fmaf(w, v.w, acc[i][3]);
+          acc[i][0] = fmaf(w[i], v.x, acc[i][0]);
+          acc[i][1] = fmaf(w[i], v.y, acc[i][1]);
+          acc[i][2] = fmaf(w[i], v.z, acc[i][2]);
+          acc[i][3] = fmaf(w[i], v.w, acc[i][3]);
         }
       }
     }
@@ -220,15 +281,14 @@ tpa_fwd_decode_kernel(const Params p, float* part_o, float* part_lse, const int 
   const int64_t rh0 = ((int64_t)b * p.lq + qi) * h;
 #pragma unroll
   for (int i = 0; i < NH; ++i) {
-    const int hh = warp + 8 * i;
-    if (hh >= h) continue;
+    const int hh = hg * NH + i;
     const float l = lS[hh];
     const bool empty = !(l > 0.f);
     const float inv = empty ? 0.f : 1.f / (l * (float)rk);
-    if (lane * 4 < dv)
-      *reinterpret_cast<float4*>(part_o + ((int64_t)split * rows + rh0 + hh) * dv + lane * 4) =
+    if (col0 < dv)
+      *reinterpret_cast<float4*>(part_o + ((int64_t)split * rows + rh0 + hh) * dv + col0) =
           make_float4(acc[i][0] * inv, acc[i][1] * inv, acc[i][2] * inv, acc[i][3] * inv);
-    if (lane == 0) part_lse[(int64_t)split * rows + rh0 + hh] = empty ? -CUDART_INF_F : mS[hh] + logf(l);
+    if (warp == 0 && (lane & 3) == 0) part_lse[(int64_t)split * rows + rh0 + hh] = empty ? -CUDART_INF_F : mS[hh] + logf(l);
   }
 }
 
@@ -239,8 +299,8 @@ inline bool vec_ok(const TpaFactor& f) {
 inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
 
 size_t decode_smem_bytes(const Params& p) {
-  const size_t floats = (size_t)p.rank_q * (p.dk + p.heads) + (size_t)DEC_JR * (p.dk + 1 + p.dv + 2 * p.heads + p.rank_q) +
-                        (size_t)p.heads * (DEC_JR + 1 + DEC_JR + 3) + DEC_JR;
+  const size_t floats = (size_t)p.rank_q * (p.dk + p.heads) + (size_t)DEC_JR * (p.dk + 2 + p.dv + 3 * p.heads + 5 * p.rank_q) +
+                        (size_t)p.heads * (DEC_JR + 1 + 3) + DEC_JR;
   return floats * sizeof(float);
 }
 
@@ -257,15 +317,15 @@ bool decode_supported(const Params& p) {
   return decode_smem_bytes(p) <= 200 * 1024;
 }
 
-// Measured (h = 32, d = 128, batch 16 x 32768 keys): one row, R_k = 2: 1.98 ms against 3.57 ms for the
-// staged tensor-core path; R_k = 4: 3.88 against 3.75; four rows: 7.4 against 3.57 (the rows are
+// Measured (h = 32, d = 128, batch 16 x 32768 keys): one row, R_k = 2: 0.93 ms against 3.57 ms for the
+// staged tensor-core path; R_k = 4: 1.80 against 3.75; four rows: 3.93 against 3.57 (the rows are
 // walked one after the other here, the staged path shares its tiles among them).
-bool decode_preferred(const Params& p) { return decode_supported(p) && p.lq == 1 && p.rank_k <= 3; }
+bool decode_preferred(const Params& p) { return decode_supported(p) && p.lq <= 2; }
 
 int decode_pick_splits(const Params& p) {
   const int KT = DEC_JR / p.rank_k;
   const int64_t ctas = (int64_t)p.lq * p.batch;
-  int splits = (int)((2 * 148 + ctas - 1) / ctas);            // about two waves of CTAs
+  int splits = (int)(2 * 148 / ctas);                          // two CTAs fit an SM: fill them once, no second wave
   const int max_splits = (p.lk + 4 * KT - 1) / (4 * KT);      // at least four tiles each
   if (splits > max_splits) splits = max_splits;
   if (splits > 64) splits = 64;
@@ -302,10 +362,16 @@ cudaError_t launch_decode(const Params& p, void* workspace, TpaKernelInfo* info,
     return cudaGetLastError();
   };
   cudaError_t e;
-  if (p.heads <= 8) e = launch(tpa_fwd_decode_kernel<1>);
-  else if (p.heads <= 16) e = launch(tpa_fwd_decode_kernel<2>);
-  else if (p.heads <= 32) e = launch(tpa_fwd_decode_kernel<4>);
-  else e = launch(tpa_fwd_decode_kernel<8>);
+  switch (p.heads / 8) {
+    case 1: e = launch(tpa_fwd_decode_kernel<1>); break;
+    case 2: e = launch(tpa_fwd_decode_kernel<2>); break;
+    case 3: e = launch(tpa_fwd_decode_kernel<3>); break;
+    case 4: e = launch(tpa_fwd_decode_kernel<4>); break;
+    case 5: e = launch(tpa_fwd_decode_kernel<5>); break;
+    case 6: e = launch(tpa_fwd_decode_kernel<6>); break;
+    case 7: e = launch(tpa_fwd_decode_kernel<7>); break;
+    default: e = launch(tpa_fwd_decode_kernel<8>); break;
+  }
   if (e != cudaSuccess) return e;
   count_launch(1);
   return launch_combine_splits(p, part_o, part_lse, splits, stream);
