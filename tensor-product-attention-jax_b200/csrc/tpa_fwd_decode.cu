@@ -174,6 +174,7 @@ tpa_fwd_decode_kernel(const Params p, float* part_o, float* part_lse, const int 
       for (int r = 0; r < rq; ++r) {
         const float* qr = qbS + r * dk;
         float d0 = 0.f, d1 = 0.f;
+#pragma unroll 4
         for (int t = t0; t < t1; t += 2) {
           const float2 kv = *reinterpret_cast<const float2*>(kr + t);
           const float2 qv = *reinterpret_cast<const float2*>(qr + t);
@@ -251,6 +252,7 @@ tpa_fwd_decode_kernel(const Params p, float* part_o, float* part_lse, const int 
       const int n_jr = KT * rk;
       const float* wp = wS + hg * NH;
       const float* vp = vbS + col0;
+#pragma unroll 4
       for (int jr = 0; jr < n_jr; ++jr) {
         const float4 v = *reinterpret_cast<const float4*>(vp + jr * dv);
         float w[NH];
