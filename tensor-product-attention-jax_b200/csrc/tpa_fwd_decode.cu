@@ -171,17 +171,23 @@ tpa_fwd_decode_kernel(const Params p, float* part_o, float* part_lse, const int 
       const int jr = tid & (DEC_JR - 1), g = tid >> 6;
       const int t0 = g * (dk >> 2), t1 = t0 + (dk >> 2);  // dk % 8 == 0: whole float2 steps
       const float* kr = kbS + jr * ldk;
-      for (int r = 0; r < rq; ++r) {
-        const float* qr = qbS + r * dk;
-        float d0 = 0.f, d1 = 0.f;
-#pragma unroll 4
+      for (int r0 = 0; r0 < rq; r0 += 4) {  // four ranks at a time: one k load feeds eight independent FMA chains
+        float d[4][2];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) d[i][0] = d[i][1] = 0.f;
+#pragma unroll 2
         for (int t = t0; t < t1; t += 2) {
           const float2 kv = *reinterpret_cast<const float2*>(kr + t);
-          const float2 qv = *reinterpret_cast<const float2*>(qr + t);
-          d0 = fmaf(kv.x, qv.x, d0);
-          d1 = fmaf(kv.y, qv.y, d1);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 qv = *reinterpret_cast<const float2*>(qbS + min(r0 + i, rq - 1) * dk + t);
+            d[i][0] = fmaf(kv.x, qv.x, d[i][0]);
+            d[i][1] = fmaf(kv.y, qv.y, d[i][1]);
+          }
         }
-        dotsP[(g * DEC_JR + jr) * rq + r] = d0 + d1;
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          if (r0 + i < rq) dotsP[(g * DEC_JR + jr) * rq + r0 + i] = d[i][0] + d[i][1];
       }
     }
     __syncthreads();
@@ -190,55 +196,90 @@ tpa_fwd_decode_kernel(const Params p, float* part_o, float* part_lse, const int 
     __syncthreads();
 
     // logits s[hh][key] = sum_rk ka[jr][hh] * sum_r qa[r][hh] dots[jr][r]; masked entries -inf
-    for (int idx = tid; idx < h * KT; idx += DEC_THREADS) {
-      const int key = idx / h, hh = idx - key * h;
-      float s = 0.f;
-      for (int q = 0; q < rk; ++q) {
-        const int jr = key * rk + q;
-        float e = 0.f;
-        for (int r = 0; r < rq; ++r) e = fmaf(qaS[r * h + hh], dots[jr * rq + r], e);
-        s = fmaf(kaS[jr * h + hh], e, s);
+    // (warp w takes keys w, w + 8, ..., four of them in flight; lanes over heads)
+    for (int kbase = warp; kbase < KT; kbase += 32) {
+      for (int hh = lane; hh < h; hh += 32) {
+        float sv[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int q = 0; q < rk; ++q) {
+          float e[4] = {0.f, 0.f, 0.f, 0.f};
+          for (int r = 0; r < rq; ++r) {
+            const float a = qaS[r * h + hh];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) e[i] = fmaf(a, dots[(min(kbase + 8 * i, KT - 1) * rk + q) * rq + r], e[i]);
+          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) sv[i] = fmaf(kaS[(min(kbase + 8 * i, KT - 1) * rk + q) * h + hh], e[i], sv[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int key = kbase + 8 * i;
+          if (key < KT) {
+            bool keep = k0 + key < k_end;
+            if (has_seg && keep) keep = ksegS[key] == qseg;
+            sS[hh * (DEC_JR + 1) + key] = keep ? sv[i] : -CUDART_INF_F;
+          }
+        }
       }
-      bool keep = k0 + key < k_end;
-      if (has_seg && keep) keep = ksegS[key] == qseg;
-      sS[hh * (DEC_JR + 1) + key] = keep ? s : -CUDART_INF_F;
     }
     __syncthreads();
 
-    // running softmax per head: warp w takes heads w, w + 8, ...; lanes over the tile's keys
-    for (int hh = warp; hh < h; hh += DEC_THREADS / 32) {
-      float* srow = sS + hh * (DEC_JR + 1);
-      const float x0 = lane < KT ? srow[lane] : -CUDART_INF_F;
-      const float x1 = lane + 32 < KT ? srow[lane + 32] : -CUDART_INF_F;
-      float tmax = fmaxf(x0, x1);
+    // running softmax per head: warp w takes heads w, w + 8, ... (two at a time, so that their
+    // shuffle chains overlap); lanes over the tile's keys
+    for (int hh0 = warp; hh0 < h; hh0 += 2 * (DEC_THREADS / 32)) {
+      float x0[2], x1[2], tmax[2], psum[2], p0[2], p1[2], corr[2], m_new[2];
+      bool on[2];
 #pragma unroll
-      for (int s = 16; s > 0; s >>= 1) tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, s));
-      const float m_old = mS[hh], m_new = fmaxf(m_old, tmax);
-      float p0 = 0.f, p1 = 0.f, corr = 1.f;
-      if (m_new != -CUDART_INF_F) {
-        corr = (m_old == -CUDART_INF_F) ? 0.f : expf(m_old - m_new);
-        p0 = expf(x0 - m_new);  // exp(-inf) = 0 for masked entries
-        p1 = expf(x1 - m_new);
+      for (int u = 0; u < 2; ++u) {
+        const int hh = hh0 + u * (DEC_THREADS / 32);
+        on[u] = hh < h;
+        const float* srow = sS + (on[u] ? hh : hh0) * (DEC_JR + 1);
+        x0[u] = lane < KT ? srow[lane] : -CUDART_INF_F;
+        x1[u] = lane + 32 < KT ? srow[lane + 32] : -CUDART_INF_F;
+        tmax[u] = fmaxf(x0[u], x1[u]);
       }
-      float psum = p0 + p1;
 #pragma unroll
-      for (int s = 16; s > 0; s >>= 1) psum += __shfl_xor_sync(0xffffffffu, psum, s);
-      if (lane < KT) srow[lane] = p0;
-      if (lane + 32 < KT) srow[lane + 32] = p1;
-      if (lane == 0) {
-        mS[hh] = m_new;
-        lS[hh] = lS[hh] * corr + psum;
-        cS[hh] = corr;
+      for (int s = 16; s > 0; s >>= 1)
+#pragma unroll
+        for (int u = 0; u < 2; ++u) tmax[u] = fmaxf(tmax[u], __shfl_xor_sync(0xffffffffu, tmax[u], s));
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const float m_old = mS[on[u] ? hh0 + u * (DEC_THREADS / 32) : hh0];
+        m_new[u] = fmaxf(m_old, tmax[u]);
+        p0[u] = p1[u] = 0.f;
+        corr[u] = 1.f;
+        if (m_new[u] != -CUDART_INF_F) {
+          corr[u] = (m_old == -CUDART_INF_F) ? 0.f : expf(m_old - m_new[u]);
+          p0[u] = expf(x0[u] - m_new[u]);  // exp(-inf) = 0 for masked entries
+          p1[u] = expf(x1[u] - m_new[u]);
+        }
+        psum[u] = p0[u] + p1[u];
+      }
+#pragma unroll
+      for (int s = 16; s > 0; s >>= 1)
+#pragma unroll
+        for (int u = 0; u < 2; ++u) psum[u] += __shfl_xor_sync(0xffffffffu, psum[u], s);
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        if (!on[u]) continue;
+        const int hh = hh0 + u * (DEC_THREADS / 32);
+        float* srow = sS + hh * (DEC_JR + 1);
+        if (lane < KT) srow[lane] = p0[u];
+        if (lane + 32 < KT) srow[lane + 32] = p1[u];
+        if (lane == 0) {
+          mS[hh] = m_new[u];
+          lS[hh] = lS[hh] * corr[u] + psum[u];
+          cS[hh] = corr[u];
+        }
       }
     }
     __syncthreads();
 
     // w[jr][hh] = p[hh][key] * va[jr][hh]
-    for (int idx = tid; idx < h * DEC_JR; idx += DEC_THREADS) {
-      const int jr = idx / h, hh = idx - jr * h;
-      const int key = jr / rk;
-      wS[idx] = key < KT ? sS[hh * (DEC_JR + 1) + key] * vaS[idx] : 0.f;
-    }
+    for (int key = warp; key < KT; key += DEC_THREADS / 32)
+      for (int q = 0; q < rk; ++q) {
+        const int jr = key * rk + q;
+        for (int hh = lane; hh < h; hh += 32) wS[jr * h + hh] = sS[hh * (DEC_JR + 1) + key] * vaS[jr * h + hh];
+      }
     __syncthreads();
 
     // acc[heads of hg][4 columns] = acc * corr + sum_jr w[jr][head] vb[jr][columns]
