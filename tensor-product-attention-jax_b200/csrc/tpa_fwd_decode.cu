@@ -9,7 +9,7 @@
 // so every factor byte is read from HBM exactly once per query row and nothing else is: the
 // staged tensor-core path rebuilds and writes all heads' dense K/V tiles first (h d / (R_k (h+d))
 // = 12.8x the factor bytes at h = 32, d = 128, R_k = 2), which is what a single decode row cannot
-// amortise.  fp32 math on CUDA cores: measured 650-750 GB/s of factor stream (3.8x the staged
+// amortise.  fp32 math on CUDA cores: measured 740-820 GB/s of factor stream (4.4x the staged
 // path for one row), i.e. still bound by its own instruction stream and block-wide syncs, not by HBM.
 //
 // grid = (key splits, query rows, batch); 256 threads.  A CTA walks its share of the keys in tiles
@@ -360,8 +360,8 @@ bool decode_supported(const Params& p) {
   return decode_smem_bytes(p) <= 200 * 1024;
 }
 
-// Measured (h = 32, d = 128, batch 16 x 32768 keys): one row, R_k = 2: 0.93 ms against 3.57 ms for the
-// staged tensor-core path; R_k = 4: 1.80 against 3.75; four rows: 3.93 against 3.57 (the rows are
+// Measured (h = 32, d = 128, batch 16 x 32768 keys): one row, R_k = 2: 0.82 ms against 3.57 ms for the
+// staged tensor-core path; R_k = 4: 1.69 against 3.75; four rows: 3.44 against 3.57 (the rows are
 // walked one after the other here, the staged path shares its tiles among them).
 bool decode_preferred(const Params& p) { return decode_supported(p) && p.lq <= 2; }
 
