@@ -54,9 +54,9 @@ enum {
   TPA_KERNEL_SM100_FUSED = 3,
   TPA_KERNEL_SM100_STAGED = 4,
   TPA_KERNEL_DECODE = 5 /* at most 8 query rows against >= 256 keys, bf16, heads <= 64 (a multiple
-                           of 8), head dims <= 128 (multiples of 8), 16-byte aligned factors:
+                           of 8), head dims <= 128 (multiples of 16), 16-byte aligned factors:
                            K and V are never materialised (rank-space logits, tpa/tpa.py:333-359);
-                           AUTO picks it for one or two query rows, where it is measured
+                           AUTO picks it for up to six query rows, where it is measured
                            faster than the staged path                                       */
 };
 

@@ -1,20 +1,21 @@
 // TPA forward for a handful of query rows against a long key/value factor cache (decode and
 // cross shapes, tpa/tpa_test.py:67-70; bf16 factors).  K and V are never materialised:
 //
-//   logits  s[h, j] = c * sum_{rq, rk} qa[rq, h] ka[j, rk, h] (qb[rq, :] . kb[j, rk, :])
+//   logits  s[h, j] = c * sum_{rq, rk} qa[rq, h] ka[j, rk, h] (qb[rq, :] . kb[j, rk, :])       (mma.sync)
 //           the rank-space form of the reference's `nomat` branch (tpa/tpa.py:333-359):
 //           R_q R_k (d + h) multiply-adds per key instead of R_k h d
-//   output  o[h, :] = (1 / R_k) sum_{j, rk} (p[h, j] va[j, rk, h]) vb[j, rk, :]
+//   output  o[h, :] = (1 / R_k) sum_{j, rk} (p[h, j] va[j, rk, h]) vb[j, rk, :]                 (mma.sync)
 //
 // so every factor byte is read from HBM exactly once per query row and nothing else is: the
 // staged tensor-core path rebuilds and writes all heads' dense K/V tiles first (h d / (R_k (h+d))
 // = 12.8x the factor bytes at h = 32, d = 128, R_k = 2), which is what a single decode row cannot
-// amortise.  fp32 math on CUDA cores: measured 740-820 GB/s of factor stream (4.4x the staged
-// path for one row), i.e. still bound by its own instruction stream and block-wide syncs, not by HBM.
+// amortise.  The two contractions (qb kb^T and w vb) run on the tensor cores, the rest in fp32 on CUDA
+// cores: measured 1.4-1.6 TB/s of factor stream (8.4x the staged path for one row, 24 % of the
+// HBM roof); what remains is the logits / softmax / p * va arithmetic between block-wide syncs.
 //
 // grid = (key splits, query rows, batch); 256 threads.  A CTA walks its share of the keys in tiles
 // of 64 (key, rank) rows, keeps a running (max, sum) per head and the h x dv accumulator in
-// registers (warp w owns value columns 16 w ...; lane l heads (h / 8)(l / 4) ... and 4 of those columns), and leaves
+// mma.sync fragments (warp w owns value columns 16 w ... 16 w + 15 of every head), and leaves
 // a normalised partial (o, lse) per split that tpa_combine_splits_kernel merges (with the caller's
 // carried state, if any) exactly as a ring step's partials are merged (tpa/ring_tpa.py:82-91).
 #include <math_constants.h>
@@ -32,6 +33,26 @@ __device__ __forceinline__ void bf16x8_to_float4(const uint4 v, float4& lo, floa
                    __uint_as_float(v.y << 16), __uint_as_float(v.y & 0xffff0000u));
   hi = make_float4(__uint_as_float(v.z << 16), __uint_as_float(v.z & 0xffff0000u),
                    __uint_as_float(v.w << 16), __uint_as_float(v.w & 0xffff0000u));
+}
+
+// D (16 x 8, fp32) += A (16 x 16, bf16, row-major fragments) * B (16 x 8, bf16, "col" fragments)
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t smem_addr(const void* ptr) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(ptr));
+}
+// two / four 8 x 8 b16 matrices; lane l supplies the address of row l % 8 of matrix l / 8
+__device__ __forceinline__ void ldmatrix_x2(uint32_t& r0, uint32_t& r1, const void* row) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(smem_addr(row)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* row) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_addr(row)));
 }
 
 // One factor array of a tile: 16-byte chunks (8 bf16) of the rows jr -> (key0 + jr / rank, jr % rank),
@@ -62,6 +83,16 @@ struct TileLoad {
       if (goff[i] >= 0 && key0 + keyrel[i] < key_end) v[i] = __ldg(reinterpret_cast<const uint4*>(base + goff[i]));
     }
   }
+  // the 16-byte chunks as they are (bf16 tile, row pitch `pitch` elements, a multiple of 8)
+  __device__ __forceinline__ void store_raw(__nv_bfloat16* dst, int pitch, int cols, int tid) const {
+    const int c = tid % CPR;
+    if (c * 8 >= cols) return;
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+      const int jr = tid / CPR + i * (DEC_THREADS / CPR);
+      *reinterpret_cast<uint4*>(dst + jr * pitch + c * 8) = v[i];
+    }
+  }
   __device__ __forceinline__ void store(float* dst, int ld, int cols, int tid) const {
     const int c = tid % CPR;
     if (c * 8 >= cols) return;
@@ -79,33 +110,60 @@ struct TileLoad {
   }
 };
 
-// NH = heads / 8: lane (hg = lane / 4, c = lane % 4) of warp w accumulates heads NH hg .. NH hg + NH - 1,
-// value columns 16 w + 4 c .. + 3 (a warp reads 64 bytes of a vb row and 32 NH bytes of w per step).
-template <int NH>
+// Shared-memory layout, shared by the kernel and the host-side size computation.
+struct DecodeSmem {
+  int qb16, kb16, vb16, w16;           // bf16 tiles (byte offsets), rows padded by 16 bytes
+  int qa, ka, va, dots, s, m, l, c, kseg, total;  // fp32 / int32 arrays (byte offsets)
+  int pk, pv, pw;                      // row pitches of the bf16 tiles, elements
+  __host__ __device__ DecodeSmem(int h, int dk, int dv, int rq, int mt) {
+    pk = dk + 8; pv = dv + 8; pw = DEC_JR + 8;
+    int off = 0;
+    qb16 = off; off += 16 * pk * 2;
+    kb16 = off; off += DEC_JR * pk * 2;
+    vb16 = off; off += DEC_JR * pv * 2;
+    w16 = off; off += mt * 16 * pw * 2;
+    qa = off; off += rq * h * 4;
+    ka = off; off += DEC_JR * h * 4;
+    va = off; off += DEC_JR * h * 4;
+    dots = off; off += DEC_JR * rq * 4;
+    s = off; off += h * (DEC_JR + 1) * 4;
+    m = off; off += h * 4;
+    l = off; off += h * 4;
+    c = off; off += h * 4;
+    kseg = off; off += DEC_JR * 4;
+    total = off;
+  }
+};
+
+// MT = ceil(heads / 16) row tiles of the p * vb product.  Both contractions run on the tensor
+// cores (mma.sync m16n8k16, bf16 in, fp32 out: with 32 heads a tcgen05 M128 tile would be three
+// quarters padding):  dots[rq, jr] = qb (16 x dk) kb^T,  warp w -> the 8 (key, rank) rows 8 w ...;
+//                     o[h, dv]   += w (h x 64) vb (64 x dv), warp w -> value columns 16 w ...
+template <int MT>
 __global__ void __launch_bounds__(DEC_THREADS)
 tpa_fwd_decode_kernel(const Params p, float* part_o, float* part_lse, const int keys_per_split) {
-  extern __shared__ float4 smem4[];
-  float* smem = reinterpret_cast<float*>(smem4);
+  extern __shared__ uint4 smem_u4[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(smem_u4);
   const int h = p.heads, dk = p.dk, dv = p.dv, rq = p.rank_q, rk = p.rank_k;
   const int KT = DEC_JR / rk;  // keys per tile
-  const int ldk = dk + 2;      // row pitch = 2 (mod 32) floats: the 64-bit reads of 32 rows hit every bank once
-  float* qbS = smem;                       // [rq][dk]
-  float* qaS = qbS + rq * dk;              // [rq][h], times sm_scale / (R_q R_k)
-  float* kbS = qaS + rq * h;               // [JR][dk + 2]
-  float* vbS = kbS + DEC_JR * ldk;         // [JR][dv]
-  float* kaS = vbS + DEC_JR * dv;          // [JR][h]
-  float* vaS = kaS + DEC_JR * h;           // [JR][h]
-  float* wS = vaS + DEC_JR * h;            // [JR][h] p * va
-  float* dotsP = wS + DEC_JR * h;          // [4][JR][rq] partial dots over a quarter of dk
-  float* dots = dotsP + 4 * DEC_JR * rq;   // [JR][rq]
-  float* sS = dots + DEC_JR * rq;          // [h][JR + 1] logits, then p
-  float* mS = sS + h * (DEC_JR + 1);       // [h] running maximum
-  float* lS = mS + h;                      // [h] running sum
-  float* cS = lS + h;                      // [h] correction of this tile
-  int* ksegS = reinterpret_cast<int*>(cS + h);  // [KT]
+  const DecodeSmem L(h, dk, dv, rq, MT);
+  __nv_bfloat16* qb16 = reinterpret_cast<__nv_bfloat16*>(smem + L.qb16);  // [16][dk + 8], rows >= rq zero
+  __nv_bfloat16* kb16 = reinterpret_cast<__nv_bfloat16*>(smem + L.kb16);  // [JR][dk + 8]
+  __nv_bfloat16* vb16 = reinterpret_cast<__nv_bfloat16*>(smem + L.vb16);  // [JR][dv + 8]
+  __nv_bfloat16* w16 = reinterpret_cast<__nv_bfloat16*>(smem + L.w16);    // [16 MT][JR + 8] p * va
+  float* qaS = reinterpret_cast<float*>(smem + L.qa);    // [rq][h], times sm_scale / (R_q R_k)
+  float* kaS = reinterpret_cast<float*>(smem + L.ka);    // [JR][h]
+  float* vaS = reinterpret_cast<float*>(smem + L.va);    // [JR][h]
+  float* dots = reinterpret_cast<float*>(smem + L.dots); // [JR][rq]
+  float* sS = reinterpret_cast<float*>(smem + L.s);      // [h][JR + 1] logits, then p
+  float* mS = reinterpret_cast<float*>(smem + L.m);      // [h] running maximum
+  float* lS = reinterpret_cast<float*>(smem + L.l);      // [h] running sum
+  float* cS = reinterpret_cast<float*>(smem + L.c);      // [h] correction of this tile
+  int* ksegS = reinterpret_cast<int*>(smem + L.kseg);    // [KT]
 
   const int split = blockIdx.x, qi = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t4 = lane & 3;  // fragment coordinates of mma.sync
   const bool causal = (p.flags & TPA_FLAG_CAUSAL) != 0;
   const bool has_seg = p.q_seg != nullptr;
   const __nv_bfloat16* qa = static_cast<const __nv_bfloat16*>(p.qa.ptr) + (int64_t)b * p.qa.stride[0] + (int64_t)qi * p.qa.stride[1];
@@ -126,20 +184,24 @@ tpa_fwd_decode_kernel(const Params p, float* part_o, float* part_lse, const int 
   }
 
   const float c = p.sm_scale / ((float)rq * (float)rk);
-  for (int idx = tid; idx < rq * dk; idx += DEC_THREADS)
-    qbS[idx] = to_float(qb[(idx / dk) * p.qb.stride[2] + idx % dk]);
+  for (int idx = tid; idx < 16 * L.pk; idx += DEC_THREADS) {
+    const int r = idx / L.pk, t = idx - r * L.pk;
+    qb16[idx] = (r < rq && t < dk) ? qb[r * p.qb.stride[2] + t] : __float2bfloat16_rn(0.f);
+  }
+  for (int idx = tid; idx < MT * 16 * L.pw; idx += DEC_THREADS) w16[idx] = __float2bfloat16_rn(0.f);
   for (int idx = tid; idx < rq * h; idx += DEC_THREADS)
     qaS[idx] = c * to_float(qa[(idx / h) * p.qa.stride[2] + idx % h]);
   for (int idx = tid; idx < h; idx += DEC_THREADS) {
     mS[idx] = -CUDART_INF_F;
     lS[idx] = 0.f;
   }
-  const int hg = lane >> 2, col0 = warp * 16 + (lane & 3) * 4;
-  float acc[NH][4];
+  float acc[MT][2][4];  // [row tile][column tile of 8][fragment]
 #pragma unroll
-  for (int i = 0; i < NH; ++i)
+  for (int i = 0; i < MT; ++i)
 #pragma unroll
-    for (int e = 0; e < 4; ++e) acc[i][e] = 0.f;
+    for (int n = 0; n < 2; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[i][n][e] = 0.f;
 
   // 64 rows x (dk | dv <= 128: 16 chunks per row) = 4 chunks per thread, x (h <= 64: 8 chunks) = 2
   TileLoad<4, 16> t_kb, t_vb;
@@ -158,41 +220,36 @@ tpa_fwd_decode_kernel(const Params p, float* part_o, float* part_lse, const int 
 
   for (int k0 = k_begin; k0 < k_end; k0 += KT) {
     __syncthreads();  // the previous tile's readers are done (and the query factors are written)
-    t_kb.store(kbS, ldk, dk, tid);
-    t_vb.store(vbS, dv, dv, tid);
+    t_kb.store_raw(kb16, L.pk, dk, tid);
+    t_vb.store_raw(vb16, L.pv, dv, tid);
     t_ka.store(kaS, h, h, tid);
     t_va.store(vaS, h, h, tid);
     if (has_seg && tid < KT) ksegS[tid] = (k0 + tid < k_end) ? kseg_g[k0 + tid] : 0;
     if (k0 + KT < k_end) fetch(k0 + KT);  // in flight while this tile is computed
     __syncthreads();
 
-    // partial dots over a quarter of dk: thread (jr = tid % 64, g = tid / 64), all ranks of q
+    // dots[jr][r] = qb[r, :] . kb[jr, :] for the rows jr = 8 warp ... 8 warp + 7
     {
-      const int jr = tid & (DEC_JR - 1), g = tid >> 6;
-      const int t0 = g * (dk >> 2), t1 = t0 + (dk >> 2);  // dk % 8 == 0: whole float2 steps
-      const float* kr = kbS + jr * ldk;
-      for (int r0 = 0; r0 < rq; r0 += 4) {  // four ranks at a time: one k load feeds eight independent FMA chains
-        float d[4][2];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) d[i][0] = d[i][1] = 0.f;
-#pragma unroll 2
-        for (int t = t0; t < t1; t += 2) {
-          const float2 kv = *reinterpret_cast<const float2*>(kr + t);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float2 qv = *reinterpret_cast<const float2*>(qbS + min(r0 + i, rq - 1) * dk + t);
-            d[i][0] = fmaf(kv.x, qv.x, d[i][0]);
-            d[i][1] = fmaf(kv.y, qv.y, d[i][1]);
-          }
-        }
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-          if (r0 + i < rq) dotsP[(g * DEC_JR + jr) * rq + r0 + i] = d[i][0] + d[i][1];
+      float d[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int ks = 0; ks < dk; ks += 16) {
+        uint32_t a[4], b0, b1;
+        a[0] = *reinterpret_cast<const uint32_t*>(qb16 + g * L.pk + ks + 2 * t4);
+        a[1] = *reinterpret_cast<const uint32_t*>(qb16 + (g + 8) * L.pk + ks + 2 * t4);
+        a[2] = *reinterpret_cast<const uint32_t*>(qb16 + g * L.pk + ks + 8 + 2 * t4);
+        a[3] = *reinterpret_cast<const uint32_t*>(qb16 + (g + 8) * L.pk + ks + 8 + 2 * t4);
+        ldmatrix_x2(b0, b1, kb16 + (warp * 8 + (lane & 7)) * L.pk + ks + ((lane >> 3) & 1) * 8);
+        mma_bf16(d, a, b0, b1);
+      }
+      const int jr = warp * 8 + 2 * t4;  // d[0] = (rank g, row jr), d[1] = (g, jr + 1), d[2] / d[3]: rank g + 8
+      if (g < rq) {
+        dots[jr * rq + g] = d[0];
+        dots[(jr + 1) * rq + g] = d[1];
+      }
+      if (g + 8 < rq) {
+        dots[jr * rq + g + 8] = d[2];
+        dots[(jr + 1) * rq + g + 8] = d[3];
       }
     }
-    __syncthreads();
-    for (int idx = tid; idx < DEC_JR * rq; idx += DEC_THREADS)
-      dots[idx] = (dotsP[idx] + dotsP[DEC_JR * rq + idx]) + (dotsP[2 * DEC_JR * rq + idx] + dotsP[3 * DEC_JR * rq + idx]);
     __syncthreads();
 
     // logits s[hh][key] = sum_rk ka[jr][hh] * sum_r qa[r][hh] dots[jr][r]; masked entries -inf
@@ -274,45 +331,42 @@ tpa_fwd_decode_kernel(const Params p, float* part_o, float* part_lse, const int 
     }
     __syncthreads();
 
-    // w[jr][hh] = p[hh][key] * va[jr][hh]
+    // w[hh][jr] = p[hh][key] * va[jr][hh], bf16 (the A operand of the next product)
     for (int key = warp; key < KT; key += DEC_THREADS / 32)
       for (int q = 0; q < rk; ++q) {
         const int jr = key * rk + q;
-        for (int hh = lane; hh < h; hh += 32) wS[jr * h + hh] = sS[hh * (DEC_JR + 1) + key] * vaS[jr * h + hh];
+        for (int hh = lane; hh < h; hh += 32)
+          w16[hh * L.pw + jr] = __float2bfloat16_rn(sS[hh * (DEC_JR + 1) + key] * vaS[jr * h + hh]);
       }
     __syncthreads();
 
-    // acc[heads of hg][4 columns] = acc * corr + sum_jr w[jr][head] vb[jr][columns]
-    if (col0 < dv) {
+    // acc[heads][16 columns of this warp] = acc * corr + w (h x 64) vb (64 x dv)
+    if (warp * 16 < dv) {
 #pragma unroll
-      for (int i = 0; i < NH; ++i) {
-        const float corr = cS[hg * NH + i];
+      for (int i = 0; i < MT; ++i) {
+        const float c0 = (i * 16 + g < h) ? cS[i * 16 + g] : 1.f;
+        const float c1 = (i * 16 + g + 8 < h) ? cS[i * 16 + g + 8] : 1.f;
 #pragma unroll
-        for (int e = 0; e < 4; ++e) acc[i][e] *= corr;
-      }
-      const int n_jr = KT * rk;
-      const float* wp = wS + hg * NH;
-      const float* vp = vbS + col0;
-#pragma unroll 4
-      for (int jr = 0; jr < n_jr; ++jr) {
-        const float4 v = *reinterpret_cast<const float4*>(vp + jr * dv);
-        float w[NH];
-        if constexpr (NH % 4 == 0) {
-#pragma unroll
-          for (int i = 0; i < NH; i += 4) {
-            const float4 w4 = *reinterpret_cast<const float4*>(wp + jr * h + i);
-            w[i] = w4.x; w[i + 1] = w4.y; w[i + 2] = w4.z; w[i + 3] = w4.w;
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < NH; ++i) w[i] = wp[jr * h + i];
+        for (int n = 0; n < 2; ++n) {
+          acc[i][n][0] *= c0; acc[i][n][1] *= c0;
+          acc[i][n][2] *= c1; acc[i][n][3] *= c1;
         }
+      }
 #pragma unroll
-        for (int i = 0; i < NH; ++i) {
-          acc[i][0] = fmaf(w[i], v.x, acc[i][0]);
-          acc[i][1] = fmaf(w[i], v.y, acc[i][1]);
-          acc[i][2] = fmaf(w[i], v.z, acc[i][2]);
-          acc[i][3] = fmaf(w[i], v.w, acc[i][3]);
+      for (int ks = 0; ks < DEC_JR; ks += 16) {
+        // vb rows ks ... ks + 15, columns 16 warp ... + 15: matrices (k 0-7 | 8-15) x (columns 0-7 | 8-15), transposed
+        uint32_t bfrag[4];
+        ldmatrix_x4_trans(bfrag, vb16 + (ks + ((lane >> 3) & 1) * 8 + (lane & 7)) * L.pv + warp * 16 + (lane >> 4) * 8);
+#pragma unroll
+        for (int i = 0; i < MT; ++i) {
+          uint32_t a[4];
+          const __nv_bfloat16* wr = w16 + (i * 16 + g) * L.pw + ks + 2 * t4;
+          a[0] = *reinterpret_cast<const uint32_t*>(wr);
+          a[1] = *reinterpret_cast<const uint32_t*>(wr + 8 * L.pw);
+          a[2] = *reinterpret_cast<const uint32_t*>(wr + 8);
+          a[3] = *reinterpret_cast<const uint32_t*>(wr + 8 * L.pw + 8);
+          mma_bf16(acc[i][0], a, bfrag[0], bfrag[1]);
+          mma_bf16(acc[i][1], a, bfrag[2], bfrag[3]);
         }
       }
     }
@@ -323,16 +377,23 @@ tpa_fwd_decode_kernel(const Params p, float* part_o, float* part_lse, const int 
   const int64_t rows = (int64_t)p.batch * p.lq * h;
   const int64_t rh0 = ((int64_t)b * p.lq + qi) * h;
 #pragma unroll
-  for (int i = 0; i < NH; ++i) {
-    const int hh = hg * NH + i;
-    const float l = lS[hh];
-    const bool empty = !(l > 0.f);
-    const float inv = empty ? 0.f : 1.f / (l * (float)rk);
-    if (col0 < dv)
-      *reinterpret_cast<float4*>(part_o + ((int64_t)split * rows + rh0 + hh) * dv + col0) =
-          make_float4(acc[i][0] * inv, acc[i][1] * inv, acc[i][2] * inv, acc[i][3] * inv);
-    if (warp == 0 && (lane & 3) == 0) part_lse[(int64_t)split * rows + rh0 + hh] = empty ? -CUDART_INF_F : mS[hh] + logf(l);
-  }
+  for (int i = 0; i < MT; ++i)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int hh = i * 16 + g + half * 8;
+      if (hh >= h) continue;
+      const float l = lS[hh];
+      const bool empty = !(l > 0.f);
+      const float inv = empty ? 0.f : 1.f / (l * (float)rk);
+#pragma unroll
+      for (int n = 0; n < 2; ++n) {
+        const int col = warp * 16 + n * 8 + 2 * t4;
+        if (col < dv)
+          *reinterpret_cast<float2*>(part_o + ((int64_t)split * rows + rh0 + hh) * dv + col) =
+              make_float2(acc[i][n][half * 2] * inv, acc[i][n][half * 2 + 1] * inv);
+      }
+      if (warp == 0 && t4 == 0) part_lse[(int64_t)split * rows + rh0 + hh] = empty ? -CUDART_INF_F : mS[hh] + logf(l);
+    }
 }
 
 inline bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; }
@@ -342,9 +403,7 @@ inline bool vec_ok(const TpaFactor& f) {
 inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
 
 size_t decode_smem_bytes(const Params& p) {
-  const size_t floats = (size_t)p.rank_q * (p.dk + p.heads) + (size_t)DEC_JR * (p.dk + 2 + p.dv + 3 * p.heads + 5 * p.rank_q) +
-                        (size_t)p.heads * (DEC_JR + 1 + 3) + DEC_JR;
-  return floats * sizeof(float);
+  return (size_t)DecodeSmem(p.heads, p.dk, p.dv, p.rank_q, (p.heads + 15) / 16).total;
 }
 
 }  // namespace
@@ -352,7 +411,7 @@ size_t decode_smem_bytes(const Params& p) {
 // A few query rows against many keys: bf16, vector-loadable factors, h <= 64 and d <= 128.
 bool decode_supported(const Params& p) {
   if (p.dtype != TPA_DTYPE_BF16 || p.lq > 8 || p.lk < 256) return false;
-  if (p.heads > 64 || p.heads % 8 != 0 || p.dk > 128 || p.dv > 128 || p.dk % 8 != 0 || p.dv % 8 != 0) return false;
+  if (p.heads > 64 || p.heads % 8 != 0 || p.dk > 128 || p.dv > 128 || p.dk % 16 != 0 || p.dv % 16 != 0) return false;
   if (p.rank_q > 16 || p.rank_k > 8) return false;
   if (!vec_ok(p.ka) || !vec_ok(p.kb) || !vec_ok(p.va) || !vec_ok(p.vb)) return false;
   if (!(p.flags & TPA_FLAG_STATE_STORE) && !aligned16(p.o)) return false;
@@ -360,10 +419,10 @@ bool decode_supported(const Params& p) {
   return decode_smem_bytes(p) <= 200 * 1024;
 }
 
-// Measured (h = 32, d = 128, batch 16 x 32768 keys): one row, R_k = 2: 0.82 ms against 3.57 ms for the
-// staged tensor-core path; R_k = 4: 1.69 against 3.75; four rows: 3.44 against 3.57 (the rows are
+// Measured (h = 32, d = 128, batch 16 x 32768 keys): one row, R_k = 2: 0.43 ms against 3.57 ms for the
+// staged tensor-core path; R_k = 4: 0.93 against 3.75; four rows: 1.91 against 3.57 (the rows are
 // walked one after the other here, the staged path shares its tiles among them).
-bool decode_preferred(const Params& p) { return decode_supported(p) && p.lq <= 2; }
+bool decode_preferred(const Params& p) { return decode_supported(p) && p.lq <= 6; }
 
 int decode_pick_splits(const Params& p) {
   const int KT = DEC_JR / p.rank_k;
@@ -405,15 +464,11 @@ cudaError_t launch_decode(const Params& p, void* workspace, TpaKernelInfo* info,
     return cudaGetLastError();
   };
   cudaError_t e;
-  switch (p.heads / 8) {
+  switch ((p.heads + 15) / 16) {
     case 1: e = launch(tpa_fwd_decode_kernel<1>); break;
     case 2: e = launch(tpa_fwd_decode_kernel<2>); break;
     case 3: e = launch(tpa_fwd_decode_kernel<3>); break;
-    case 4: e = launch(tpa_fwd_decode_kernel<4>); break;
-    case 5: e = launch(tpa_fwd_decode_kernel<5>); break;
-    case 6: e = launch(tpa_fwd_decode_kernel<6>); break;
-    case 7: e = launch(tpa_fwd_decode_kernel<7>); break;
-    default: e = launch(tpa_fwd_decode_kernel<8>); break;
+    default: e = launch(tpa_fwd_decode_kernel<4>); break;
   }
   if (e != cudaSuccess) return e;
   count_launch(1);
