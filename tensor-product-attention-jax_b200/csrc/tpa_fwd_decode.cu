@@ -11,7 +11,7 @@
 // = 12.8x the factor bytes at h = 32, d = 128, R_k = 2), which is what a single decode row cannot
 // amortise.  The two contractions (qb kb^T and w vb) run on the tensor cores, the rest in fp32 on CUDA
 // cores: measured 1.4-1.6 TB/s of factor stream (8.4x the staged path for one row, 24 % of the
-// HBM roof); what remains is the logits / softmax / p * va arithmetic between block-wide syncs.
+// HBM roof); what remains is the fp32 logits / softmax / p * va pass and five block-wide syncs per tile.
 //
 // grid = (key splits, query rows, batch); 256 threads.  A CTA walks its share of the keys in tiles
 // of 64 (key, rank) rows, keeps a running (max, sum) per head and the h x dv accumulator in
@@ -140,7 +140,7 @@ struct DecodeSmem {
 // quarters padding):  dots[rq, jr] = qb (16 x dk) kb^T,  warp w -> the 8 (key, rank) rows 8 w ...;
 //                     o[h, dv]   += w (h x 64) vb (64 x dv), warp w -> value columns 16 w ...
 template <int MT>
-__global__ void __launch_bounds__(DEC_THREADS)
+__global__ void __launch_bounds__(DEC_THREADS, MT <= 2 ? 2 : 1)
 tpa_fwd_decode_kernel(const Params p, float* part_o, float* part_lse, const int keys_per_split) {
   extern __shared__ uint4 smem_u4[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(smem_u4);
@@ -155,7 +155,7 @@ tpa_fwd_decode_kernel(const Params p, float* part_o, float* part_lse, const int 
   float* kaS = reinterpret_cast<float*>(smem + L.ka);    // [JR][h]
   float* vaS = reinterpret_cast<float*>(smem + L.va);    // [JR][h]
   float* dots = reinterpret_cast<float*>(smem + L.dots); // [JR][rq]
-  float* sS = reinterpret_cast<float*>(smem + L.s);      // [h][JR + 1] logits, then p
+  float* sS = reinterpret_cast<float*>(smem + L.s);      // scratch of the softmax pass (>= 16 h floats)
   float* mS = reinterpret_cast<float*>(smem + L.m);      // [h] running maximum
   float* lS = reinterpret_cast<float*>(smem + L.l);      // [h] running sum
   float* cS = reinterpret_cast<float*>(smem + L.c);      // [h] correction of this tile
@@ -195,6 +195,11 @@ tpa_fwd_decode_kernel(const Params p, float* part_o, float* part_lse, const int 
     mS[idx] = -CUDART_INF_F;
     lS[idx] = 0.f;
   }
+  constexpr int HI = (MT + 1) / 2;  // heads per lane in the softmax pass (lanes over heads)
+  float* red = sS;                  // [2][8 warps][h] per-warp maxima, then per-warp sums
+  float m_keep[HI], c_keep[HI];     // warp 0: the new maximum and correction of its heads
+#pragma unroll
+  for (int hi = 0; hi < HI; ++hi) m_keep[hi] = c_keep[hi] = 0.f;
   float acc[MT][2][4];  // [row tile][column tile of 8][fragment]
 #pragma unroll
   for (int i = 0; i < MT; ++i)
@@ -252,93 +257,81 @@ tpa_fwd_decode_kernel(const Params p, float* part_o, float* part_lse, const int 
     }
     __syncthreads();
 
-    // logits s[hh][key] = sum_rk ka[jr][hh] * sum_r qa[r][hh] dots[jr][r]; masked entries -inf
-    // (warp w takes keys w, w + 8, ..., four of them in flight; lanes over heads)
-    for (int kbase = warp; kbase < KT; kbase += 32) {
-      for (int hh = lane; hh < h; hh += 32) {
-        float sv[4] = {0.f, 0.f, 0.f, 0.f};
-        for (int q = 0; q < rk; ++q) {
-          float e[4] = {0.f, 0.f, 0.f, 0.f};
-          for (int r = 0; r < rq; ++r) {
-            const float a = qaS[r * h + hh];
+    // Logits, running softmax and w = p * va in one pass, the logits never leaving registers:
+    // warp w takes keys w, w + 8, ... (at most 8), lanes over heads.
+    //   s[hh][key] = sum_rk ka[jr][hh] * sum_r qa[r][hh] dots[jr][r]; masked entries -inf
+    float sv[HI][8];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) e[i] = fmaf(a, dots[(min(kbase + 8 * i, KT - 1) * rk + q) * rq + r], e[i]);
-          }
+    for (int hi = 0; hi < HI; ++hi) {
+      const int hh = min(lane + 32 * hi, h - 1);
 #pragma unroll
-          for (int i = 0; i < 4; ++i) sv[i] = fmaf(kaS[(min(kbase + 8 * i, KT - 1) * rk + q) * h + hh], e[i], sv[i]);
-        }
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int key = kbase + 8 * i;
-          if (key < KT) {
-            bool keep = k0 + key < k_end;
-            if (has_seg && keep) keep = ksegS[key] == qseg;
-            sS[hh * (DEC_JR + 1) + key] = keep ? sv[i] : -CUDART_INF_F;
-          }
-        }
-      }
-    }
-    __syncthreads();
-
-    // running softmax per head: warp w takes heads w, w + 8, ... (two at a time, so that their
-    // shuffle chains overlap); lanes over the tile's keys
-    for (int hh0 = warp; hh0 < h; hh0 += 2 * (DEC_THREADS / 32)) {
-      float x0[2], x1[2], tmax[2], psum[2], p0[2], p1[2], corr[2], m_new[2];
-      bool on[2];
-#pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        const int hh = hh0 + u * (DEC_THREADS / 32);
-        on[u] = hh < h;
-        const float* srow = sS + (on[u] ? hh : hh0) * (DEC_JR + 1);
-        x0[u] = lane < KT ? srow[lane] : -CUDART_INF_F;
-        x1[u] = lane + 32 < KT ? srow[lane + 32] : -CUDART_INF_F;
-        tmax[u] = fmaxf(x0[u], x1[u]);
-      }
-#pragma unroll
-      for (int s = 16; s > 0; s >>= 1)
-#pragma unroll
-        for (int u = 0; u < 2; ++u) tmax[u] = fmaxf(tmax[u], __shfl_xor_sync(0xffffffffu, tmax[u], s));
-#pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        const float m_old = mS[on[u] ? hh0 + u * (DEC_THREADS / 32) : hh0];
-        m_new[u] = fmaxf(m_old, tmax[u]);
-        p0[u] = p1[u] = 0.f;
-        corr[u] = 1.f;
-        if (m_new[u] != -CUDART_INF_F) {
-          corr[u] = (m_old == -CUDART_INF_F) ? 0.f : expf(m_old - m_new[u]);
-          p0[u] = expf(x0[u] - m_new[u]);  // exp(-inf) = 0 for masked entries
-          p1[u] = expf(x1[u] - m_new[u]);
-        }
-        psum[u] = p0[u] + p1[u];
-      }
-#pragma unroll
-      for (int s = 16; s > 0; s >>= 1)
-#pragma unroll
-        for (int u = 0; u < 2; ++u) psum[u] += __shfl_xor_sync(0xffffffffu, psum[u], s);
-#pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        if (!on[u]) continue;
-        const int hh = hh0 + u * (DEC_THREADS / 32);
-        float* srow = sS + hh * (DEC_JR + 1);
-        if (lane < KT) srow[lane] = p0[u];
-        if (lane + 32 < KT) srow[lane + 32] = p1[u];
-        if (lane == 0) {
-          mS[hh] = m_new[u];
-          lS[hh] = lS[hh] * corr[u] + psum[u];
-          cS[hh] = corr[u];
-        }
-      }
-    }
-    __syncthreads();
-
-    // w[hh][jr] = p[hh][key] * va[jr][hh], bf16 (the A operand of the next product)
-    for (int key = warp; key < KT; key += DEC_THREADS / 32)
+      for (int i = 0; i < 8; ++i) sv[hi][i] = 0.f;
       for (int q = 0; q < rk; ++q) {
-        const int jr = key * rk + q;
-        for (int hh = lane; hh < h; hh += 32)
-          w16[hh * L.pw + jr] = __float2bfloat16_rn(sS[hh * (DEC_JR + 1) + key] * vaS[jr * h + hh]);
+        float e[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) e[i] = 0.f;
+        for (int r = 0; r < rq; ++r) {
+          const float a = qaS[r * h + hh];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) e[i] = fmaf(a, dots[(min(warp + 8 * i, KT - 1) * rk + q) * rq + r], e[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sv[hi][i] = fmaf(kaS[(min(warp + 8 * i, KT - 1) * rk + q) * h + hh], e[i], sv[hi][i]);
       }
+      float pmax = -CUDART_INF_F;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int key = warp + 8 * i;
+        bool keep = key < KT && k0 + key < k_end;
+        if (has_seg && keep) keep = ksegS[key] == qseg;
+        if (!keep) sv[hi][i] = -CUDART_INF_F;
+        pmax = fmaxf(pmax, sv[hi][i]);
+      }
+      if (lane + 32 * hi < h) red[warp * h + hh] = pmax;  // this warp's maximum per head
+    }
     __syncthreads();
+#pragma unroll
+    for (int hi = 0; hi < HI; ++hi) {
+      const int hh = lane + 32 * hi;
+      if (hh >= h) continue;
+      float tmax = red[hh];
+#pragma unroll
+      for (int w = 1; w < DEC_THREADS / 32; ++w) tmax = fmaxf(tmax, red[w * h + hh]);
+      const float m_old = mS[hh], m_new = fmaxf(m_old, tmax);
+      const float corr = (m_new == -CUDART_INF_F) ? 1.f : ((m_old == -CUDART_INF_F) ? 0.f : expf(m_old - m_new));
+      float psum = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int key = warp + 8 * i;
+        if (key < KT) {
+          const float pr = (m_new == -CUDART_INF_F) ? 0.f : expf(sv[hi][i] - m_new);  // exp(-inf) = 0 for masked entries
+          psum += pr;
+          for (int q = 0; q < rk; ++q) {
+            const int jr = key * rk + q;
+            w16[hh * L.pw + jr] = __float2bfloat16_rn(pr * vaS[jr * h + hh]);
+          }
+        }
+      }
+      red[(DEC_THREADS / 32 + warp) * h + hh] = psum;  // this warp's share of the row sum
+      if (warp == 0) {
+        cS[hh] = corr;
+        m_keep[hi] = m_new;
+        c_keep[hi] = corr;
+      }
+    }
+    __syncthreads();
+    if (warp == 0) {  // nobody reads mS / lS before the next block-wide sync
+#pragma unroll
+      for (int hi = 0; hi < HI; ++hi) {
+        const int hh = lane + 32 * hi;
+        if (hh >= h) continue;
+        float psum = 0.f;
+#pragma unroll
+        for (int w = 0; w < DEC_THREADS / 32; ++w) psum += red[(DEC_THREADS / 32 + w) * h + hh];
+        mS[hh] = m_keep[hi];
+        lS[hh] = lS[hh] * c_keep[hi] + psum;
+      }
+    }
 
     // acc[heads][16 columns of this warp] = acc * corr + w (h x 64) vb (64 x dv)
     if (warp * 16 < dv) {
@@ -419,8 +412,8 @@ bool decode_supported(const Params& p) {
   return decode_smem_bytes(p) <= 200 * 1024;
 }
 
-// Measured (h = 32, d = 128, batch 16 x 32768 keys): one row, R_k = 2: 0.43 ms against 3.57 ms for the
-// staged tensor-core path; R_k = 4: 0.93 against 3.75; four rows: 1.91 against 3.57 (the rows are
+// Measured (h = 32, d = 128, batch 16 x 32768 keys): one row, R_k = 2: 0.41 ms against 3.57 ms for the
+// staged tensor-core path; R_k = 4: 0.97 against 3.75; four rows: 1.79 against 3.57 (the rows are
 // walked one after the other here, the staged path shares its tiles among them).
 bool decode_preferred(const Params& p) { return decode_supported(p) && p.lq <= 6; }
 
