@@ -203,6 +203,10 @@ def main():
     ap.add_argument("--pass", dest="which", default="fwd", choices=["fwd", "bwd"],
                     help="bwd: time tpa_bwd on the forward's results instead (single GPU; 2.5x the forward's "
                          "algorithmic FLOPs: five tile GEMMs instead of two); not the headline metric")
+    ap.add_argument("--lq", type=int, default=None,
+                    help="keep only the last LQ query rows of the workload (decode shapes against the whole "
+                         "key/value factor cache; single GPU, forward; reports the factor stream against the "
+                         "HBM roof; not the headline metric)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
@@ -235,6 +239,11 @@ def main():
     q, k, v = make_inputs(name, device, shard=(rank, world) if ring else None)
     ids = torch.zeros((b, q.shape[1]), dtype=torch.int32, device=device) if ring else None
     bwd = args.which == "bwd"
+    q_off = 0
+    if args.lq is not None:
+        assert not ring and not bwd and 0 < args.lq <= t, "--lq is a single-GPU forward measurement"
+        q_off = t - args.lq
+        q = q[:, q_off:].contiguous()
     if bwd:
         assert not ring, "--pass bwd is a single-GPU measurement"
         o_fwd, lse_fwd = tpa_b200.tpa.fwd_device(q, k, v, h, None, None, sm_scale, causal)
@@ -249,7 +258,7 @@ def main():
         if ring:
             return tpa_b200.ring_tpa.ring_tpa(q, k, v, ids, ids, None, h, sm_scale=sm_scale, causal=causal,
                                               mask_mode=args.mask_mode)
-        return tpa_b200.tpa.fwd_device(q, k, v, h, None, None, sm_scale, causal, kernel=args.kernel)[0]
+        return tpa_b200.tpa.fwd_device(q, k, v, h, None, None, sm_scale, causal, q_offset=q_off, kernel=args.kernel)[0]
 
     def sync():
         torch.cuda.synchronize(device)
@@ -293,12 +302,15 @@ def main():
         total_ms = float(tt.item())
     ms = total_ms / args.steps
     fl = flops(b, t, h, d, causal) * (2.5 if bwd else 1.0)
+    if args.lq is not None:  # the last lq rows: each sees its own prefix (causal) or every key
+        lq = args.lq
+        fl = 4.0 * b * h * d * (lq * (t - lq) + lq * (lq + 1) // 2 if causal else lq * t)
     value = fl / (ms * 1e-3) / 1e12
     toks = b * t / (ms * 1e-3)
 
     # ------------------------------------------------------------- end to end on pinned host arrays
     e2e = None
-    if not args.no_e2e and not bwd:
+    if not args.no_e2e and not bwd and args.lq is None:
         hq, hk, hv = (x.cpu().pin_memory() for x in (q, k, v))
         hid = ids.cpu().pin_memory() if ring else None
         out_host = torch.empty((b, q.shape[1], h, d), dtype=q.dtype).pin_memory()
@@ -351,8 +363,14 @@ def main():
                 "hbm_algorithmic_bytes": sum(x.numel() * x.element_size() for x in (q, k, v))
                 + b * q.shape[1] * h * d * q.element_size() + b * q.shape[1] * h * 4,
                 "hbm_peak_gbs": hbm}
+    if args.lq is not None:
+        # few rows against a long cache: the roof is the K/V factor stream, not the tensor pipe
+        stream = sum(x.numel() * x.element_size() for x in (q, k, v)) + b * args.lq * h * d * q.element_size()
+        gbs = stream / (kernel_ms * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "achieved": gbs, "peak": hbm, "unit": "GB/s", "frac": gbs / hbm, "peak_source": src,
+                    "traffic": None, "kernel": info["kernel"], "hbm_algorithmic_bytes": stream}
     cpu = None
-    if not args.no_cpu_baseline and world == 1 and not bwd:
+    if not args.no_cpu_baseline and world == 1 and not bwd and args.lq is None:
         tf, ctoks, cdt, sample = time_cpu(name, 1, 0)
         cpu = {"value": tf, "unit": "TFLOP/s", "tokens_per_s": ctoks, "cores": torch.get_num_threads(), "kind": "port",
                "sample": sample}
@@ -360,7 +378,9 @@ def main():
         "metric": METRIC if not bwd else "TPA bwd algorithmic TFLOP/s per B200 (2.5x the forward's FLOPs)", "value": value, "unit": "TFLOP/s", "tokens_per_s": toks, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": dtn, "data": "synthetic",
-        "config": {"workload": name, "shape": f"B{b} T{t} h{h} d{d} R{rq}/{rk}/{rk} causal={causal}",
+        "config": {"workload": name + (f"@lq{args.lq}" if args.lq is not None else ""),
+                   "shape": f"B{b} T{t} h{h} d{d} R{rq}/{rk}/{rk} causal={causal}"
+                            + (f", last {args.lq} query rows" if args.lq is not None else ""),
                    "parallelism": f"ring sp{world} ({args.mask_mode} causal mask)" if ring else "single GPU",
                    "l2": "inputs + outputs larger than L2 (no flush needed)" if name in ("c1", "c2", "c3") else "smaller than L2, not flushed",
                    "kernel": info},

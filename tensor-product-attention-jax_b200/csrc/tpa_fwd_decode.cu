@@ -423,7 +423,7 @@ int decode_pick_splits(const Params& p) {
   int splits = (int)(2 * 148 / ctas);                          // two CTAs fit an SM: fill them once, no second wave
   const int max_splits = (p.lk + 4 * KT - 1) / (4 * KT);      // at least four tiles each
   if (splits > max_splits) splits = max_splits;
-  if (splits > 64) splits = 64;
+  if (splits > 2 * 148) splits = 2 * 148;
   return splits < 1 ? 1 : splits;
 }
 
