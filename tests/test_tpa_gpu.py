@@ -350,6 +350,7 @@ DECODE_CASES = [
     (2, 8, 777, 3, 3, 8, 64, 128, 100, True, 700),      # rank 3 (tiles of 21 keys), packed ids, dk != dv
     (1, 2, 3000, 12, 8, 64, 128, 128, 0, True, 10),     # 64 heads, rank 8; most keys above the diagonal
     (1, 3, 512, 1, 1, 8, 16, 16, 0, False, 0),
+    (2, 1, 1500, 2, 2, 48, 64, 32, 0, True, 1499),      # 48 heads: three 16-row tiles of the p * vb product
 ]
 
 
