@@ -207,6 +207,9 @@ def main():
                     help="keep only the last LQ query rows of the workload (decode shapes against the whole "
                          "key/value factor cache; single GPU, forward; reports the factor stream against the "
                          "HBM roof; not the headline metric)")
+    ap.add_argument("--graph", action="store_true",
+                    help="capture one step in a CUDA graph and time its replays (single GPU): what a serving "
+                         "loop does for launch-bound shapes such as --lq 1")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
@@ -260,6 +263,24 @@ def main():
                                               mask_mode=args.mask_mode)
         return tpa_b200.tpa.fwd_device(q, k, v, h, None, None, sm_scale, causal, q_offset=q_off, kernel=args.kernel)[0]
 
+    if args.graph:
+        assert not ring, "--graph is a single-GPU measurement"
+        eager_step = step
+        side = torch.cuda.Stream(device)
+        with torch.cuda.stream(side):  # warm up on the capture stream: scratch buffers get allocated here
+            for _ in range(3):
+                eager_step()
+        torch.cuda.synchronize(device)
+        graph = torch.cuda.CUDAGraph()
+        n_cap = _capi.lib.tpa_launch_count()
+        with torch.cuda.graph(graph, stream=side):
+            graph_out = eager_step()
+        launches_per_replay = _capi.lib.tpa_launch_count() - n_cap  # kernels recorded in the graph
+
+        def step():
+            graph.replay()
+            return graph_out
+
     def sync():
         torch.cuda.synchronize(device)
         if ring:
@@ -292,6 +313,8 @@ def main():
             ev[i + 1].record()
         sync()
         launches = _capi.lib.tpa_launch_count() - n0
+        if args.graph:
+            launches = launches_per_replay * args.steps
         time.sleep(0.12)  # let the sample that covers the end of the timed region arrive
         clock_summary = clocks.summary(c_start)
     total_ms = ev[0].elapsed_time(ev[-1])
@@ -383,6 +406,7 @@ def main():
                             + (f", last {args.lq} query rows" if args.lq is not None else ""),
                    "parallelism": f"ring sp{world} ({args.mask_mode} causal mask)" if ring else "single GPU",
                    "l2": "inputs + outputs larger than L2 (no flush needed)" if name in ("c1", "c2", "c3") else "smaller than L2, not flushed",
+                   "cuda_graph": bool(args.graph),
                    "kernel": info},
         "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clock_summary,
     }

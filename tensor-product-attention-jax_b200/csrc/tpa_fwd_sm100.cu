@@ -1113,10 +1113,67 @@ cudaError_t launch_attn(const Params& p, const uint8_t* wq, const uint8_t* wk, c
 
 }  // namespace
 
+// The same merge with one WARP per (row, head, 4 columns), lanes over the splits: for the many
+// splits of a decode call (hundreds of partials of a handful of rows) the serial walk above is a
+// chain of dependent loads; here it is splits / 32 steps and two shuffle reductions.
+__global__ void __launch_bounds__(256) tpa_combine_splits_warp_kernel(const Params p, const float* part_o,
+                                                                      const float* part_lse, int splits) {
+  const int d = p.dv, lane = threadIdx.x & 31;
+  const int64_t rows = (int64_t)p.batch * p.lq * p.heads;
+  const int64_t idx = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (idx >= rows * (d / 4)) return;
+  const int64_t rh = idx / (d / 4);
+  const int c = (int)(idx % (d / 4)) * 4;
+  const bool load = (p.flags & TPA_FLAG_STATE_LOAD) != 0, store = (p.flags & TPA_FLAG_STATE_STORE) != 0;
+  float m = (load && lane == 0) ? p.state_lse[rh] : -CUDART_INF_F;
+  for (int s = lane; s < splits; s += 32) m = fmaxf(m, part_lse[s * rows + rh]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  float wsum = 0.f;
+  auto add = [&](const float* o, float lse) {
+    if (lse == -CUDART_INF_F) return;
+    const float w = expf(lse - m);
+    const float4 v = *reinterpret_cast<const float4*>(o);
+    acc.x += w * v.x; acc.y += w * v.y; acc.z += w * v.z; acc.w += w * v.w;
+    wsum += w;
+  };
+  if (m != -CUDART_INF_F) {
+    if (load && lane == 0) add(p.state_o + rh * d + c, p.state_lse[rh]);
+    for (int s = lane; s < splits; s += 32) add(part_o + (s * rows + rh) * d + c, part_lse[s * rows + rh]);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    acc.x += __shfl_xor_sync(0xffffffffu, acc.x, o);
+    acc.y += __shfl_xor_sync(0xffffffffu, acc.y, o);
+    acc.z += __shfl_xor_sync(0xffffffffu, acc.z, o);
+    acc.w += __shfl_xor_sync(0xffffffffu, acc.w, o);
+    wsum += __shfl_xor_sync(0xffffffffu, wsum, o);
+  }
+  if (lane != 0) return;
+  const bool none = !(wsum > 0.f);
+  const float inv = none ? 0.f : 1.f / wsum;
+  const float lse = none ? -CUDART_INF_F : m + logf(wsum);
+  if (store) {
+    *reinterpret_cast<float4*>(p.state_o + rh * d + c) = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+    if (c == 0) p.state_lse[rh] = lse;
+  } else {
+    const float q = none ? CUDART_NAN_F : 1.f;  // rows that saw no key are NaN (tpa/tpa.py:439)
+    uint2 o;
+    o.x = pack_bf16(acc.x * inv * q, acc.y * inv * q);
+    o.y = pack_bf16(acc.z * inv * q, acc.w * inv * q);
+    *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(p.o) + rh * d + c) = o;
+    if (c == 0 && p.lse != nullptr) p.lse[rh] = lse;
+  }
+}
+
 cudaError_t launch_combine_splits(const Params& p, const float* part_o, const float* part_lse, int splits,
                                   cudaStream_t stream) {
-  const int64_t threads = (int64_t)p.batch * p.lq * p.heads * (p.dv / 4);
-  tpa_combine_splits_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(p, part_o, part_lse, splits);
+  const int64_t items = (int64_t)p.batch * p.lq * p.heads * (p.dv / 4);
+  if (splits > 32)
+    tpa_combine_splits_warp_kernel<<<(unsigned)((items + 7) / 8), 256, 0, stream>>>(p, part_o, part_lse, splits);
+  else
+    tpa_combine_splits_kernel<<<(unsigned)((items + 255) / 256), 256, 0, stream>>>(p, part_o, part_lse, splits);
   count_launch(1);
   return cudaGetLastError();
 }
