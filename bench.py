@@ -138,15 +138,38 @@ def make_inputs(name, device, shard=None, seed=0):
     return q, k, v
 
 
-def cpu_sample(name, max_rows=256):
-    """Bounded CPU sample of a workload: `max_rows` evenly spaced query rows against all keys,
-    which for a causal workload has the whole job's mean cost per token."""
+def host_threads():
+    """Use every host core this process may run on (torchrun exports OMP_NUM_THREADS=1)."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    torch.set_num_threads(max(1, n))
+    return torch.get_num_threads()
+
+
+def config_for(name, world, mask_mode, lq=None):
+    """The workload description; identical for the b200 and the reference arm."""
+    dtn, b, t, h, d, rq, rk, causal = WORKLOADS[name]
+    ring = world > 1
+    return {"workload": name + (f"@lq{lq}" if lq is not None else ""),
+            "shape": f"B{b} T{t} h{h} d{d} R{rq}/{rk}/{rk} causal={causal}"
+                     + (f", last {lq} query rows" if lq is not None else ""),
+            "parallelism": f"ring sp{world} ({mask_mode} causal mask)" if ring else "single GPU",
+            "l2": "inputs + outputs larger than L2 (no flush needed)" if name.split("@")[0] in ("c1", "c2", "c3")
+                  else "smaller than L2, not flushed"}
+
+
+def cpu_sample(name, n_rows):
+    """Bounded CPU sample of a workload: `n_rows` evenly spaced query rows against all keys,
+    which for a causal workload has the whole job's mean cost per token.  Blocks of >= 1024 rows
+    keep the per-head matrix products large enough for the host BLAS to thread."""
     import numpy as np
     from oracle import tpa_oracle as orc
 
     dt, b, t, h, d, rq, rk, causal = WORKLOADS[name]
     q, k, v = orc.make_factors(2, b, t, t, rq, rk, h, d, d)
-    n = min(max_rows, t)
+    n = min(n_rows, t)
     rows = torch.from_numpy(np.linspace(0, t - 1, n).round().astype(np.int64))
     tq, tk, tv = (torch.from_numpy(x) for x in (q, k, v))
     if dt == "bf16":
@@ -156,8 +179,19 @@ def cpu_sample(name, max_rows=256):
     return run, fl, b * n, f"{n} evenly spaced query rows of {name} against all {t} keys, torch fp32, {torch.get_num_threads()} threads"
 
 
-def time_cpu(name, steps, warmup):
-    run, fl, toks, sample = cpu_sample(name)
+def calibrate_rows(name, seconds_per_step):
+    """Number of sample rows whose oracle run takes about `seconds_per_step` on this host
+    (one untimed probe of 256 rows; at least 256, at most 4096 rows)."""
+    run, _, _, _ = cpu_sample(name, 256)
+    t0 = time.perf_counter()
+    run()
+    probe = time.perf_counter() - t0
+    n = int(256 * seconds_per_step / max(probe, 1e-3))
+    return max(256, min(4096, n // 256 * 256))
+
+
+def time_cpu(name, steps, warmup, n_rows):
+    run, fl, toks, sample = cpu_sample(name, n_rows)
     for _ in range(warmup):
         run()
     t0 = time.perf_counter()
@@ -167,26 +201,88 @@ def time_cpu(name, steps, warmup):
     return fl / dt / 1e12, toks / dt, dt, sample
 
 
-def reference_arm(args, name):
+def reference_arm(args, name, world):
+    """The CPU arm: the oracle port on all host threads, exactly --steps timed and --warmup untimed
+    steps, each step a sample of the workload sized so that the whole run takes about two minutes."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps, warmup = min(args.steps, 3), min(args.warmup, 1)
-    tf, toks, dt, sample = time_cpu(name, steps, warmup)
-    dtn, b, t, h, d, rq, rk, causal = WORKLOADS[name]
-    cores = torch.get_num_threads()
+    cores = host_threads()
+    steps, warmup = args.steps, args.warmup
+    n_rows = calibrate_rows(name, 120.0 / max(1, steps + warmup))
+    tf, toks, dt, sample = time_cpu(name, steps, warmup, n_rows)
+    dtn = WORKLOADS[name][0]
     line = {
         "impl": "reference", "metric": METRIC, "value": tf, "unit": "TFLOP/s", "tokens_per_s": toks,
         "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": dt * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": {"workload": name, "shape": f"B{b} T{t} h{h} d{d} R{rq}/{rk}/{rk} causal={causal}",
-                   "note": "CPU oracle (restatement of the reference math); the reference itself needs jax, which is not installed"},
+        "config": config_for(name, world, args.mask_mode),
+        "note": "CPU oracle (restatement of the reference math); the reference itself needs jax, which is not "
+                f"installed: reference on the JAX CPU backend unavailable on this box.  Workload dtype {dtn}, oracle in fp32.",
         "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------- parity of the timed output
+
+
+def _sample_rows(t, n_random, seed):
+    fixed = [0, 1, 2, 3, t - 4, t - 3, t - 2, t - 1]
+    rnd = torch.randperm(t, generator=torch.Generator().manual_seed(seed))[:n_random].tolist()
+    return torch.tensor(sorted(set(r for r in fixed + rnd if 0 <= r < t)))
+
+
+def _bounds(dtn):
+    # the tolerances of the benchmark: fp32 max-abs 1e-5; bf16 max-abs 2e-2 and mean-abs 5e-3
+    return (1e-5, 1e-5) if dtn == "f32" else (2e-2, 5e-3)
+
+
+def parity_single(o, q, k, v, h, d, causal, q_off, dtn, n_rows=64):
+    """Sampled rows of the output the timed loop just produced against the CPU oracle."""
+    from oracle import tpa_oracle as orc
+
+    lq = q.shape[1]
+    rows = _sample_rows(lq, n_rows, 7)
+    f = lambda x: x.float().cpu()  # noqa: E731
+    ref = orc.tpa_reference_torch(f(q), f(k), f(v), h, sm_scale=d**-0.5, causal=causal, rows=rows, q_offset=q_off)
+    diff = (f(o)[:, rows] - ref).abs()
+    mx, mean = float(diff.max()), float(diff.mean())
+    bmax, bmean = _bounds(dtn)
+    return {"max_abs": mx, "mean_abs": mean, "rows": int(len(rows)), "bound_max_abs": bmax, "bound_mean_abs": bmean,
+            "against": "CPU oracle, sampled query rows of the last timed step, all heads",
+            "ok": bool(mx <= bmax and mean <= bmean and not torch.isnan(f(o)[:, rows]).any())}
+
+
+def parity_ring(o, q, k_full, v_full, h, d, causal, mask_mode, rank, world, dtn, n_rows=32):
+    """This rank's sampled output rows against the ring definition computed directly on the CPU:
+    every key shard contributes a block result under its own mask (shard-local triangle for
+    "reference_local", tpa/ring_tpa.py:73-79; global positions for "global"), merged with the
+    LSE weights of tpa/ring_tpa.py:82-91."""
+    from oracle import tpa_oracle as orc
+
+    lq = q.shape[1]
+    rows = _sample_rows(lq, n_rows, 11 + rank)
+    f = lambda x: x.float().cpu()  # noqa: E731
+    fq, fk, fv = f(q), f(k_full), f(v_full)
+    per = fk.shape[1] // world
+    parts = []
+    for s in range(world):
+        sl = slice(s * per, (s + 1) * per)
+        offs = (rank * lq, s * per) if mask_mode == "global" else (0, 0)
+        if causal and mask_mode == "global" and s > rank:
+            continue
+        parts.append(orc.tpa_reference_torch(fq, fk[:, sl], fv[:, sl], h, sm_scale=d**-0.5, causal=causal, rows=rows,
+                                             q_offset=offs[0], k_offset=offs[1], return_lse=True))
+    lse = torch.stack([p[1] for p in parts])            # [steps, b, rows, h]
+    tot = torch.logsumexp(lse, dim=0)
+    w = torch.exp(lse - tot).unsqueeze(-1)
+    ref = (torch.nan_to_num(torch.stack([p[0] for p in parts])) * w).sum(0)
+    diff = (f(o)[:, rows] - ref).abs()
+    return float(diff.max()), float(diff.mean()), int(len(rows))
 
 
 def main():
@@ -212,6 +308,9 @@ def main():
                          "loop does for launch-bound shapes such as --lq 1")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-parity", action="store_true", help="skip the oracle check of the timed output")
+    ap.add_argument("--no-n1", action="store_true",
+                    help="N > 1: skip timing the unsharded workload on rank 0's GPU (ring_efficiency)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
 
@@ -225,7 +324,7 @@ def main():
         name = f"{name}@T{args.seq_len}"
         WORKLOADS[name] = tuple(w)
     if args.impl == "reference":
-        return reference_arm(args, name)
+        return reference_arm(args, name, world)
 
     import torch.distributed as dist
     import tpa_b200
@@ -308,8 +407,9 @@ def main():
         sync()
         n0 = _capi.lib.tpa_launch_count()
         ev[0].record()
+        last = None
         for i in range(args.steps):
-            step()
+            last = step()
             ev[i + 1].record()
         sync()
         launches = _capi.lib.tpa_launch_count() - n0
@@ -367,6 +467,50 @@ def main():
                "ms_per_step": e_ms, "h2d_bytes_per_step": h2d * world,
                "d2h_bytes_per_step": out_host.numel() * out_host.element_size() * world}
 
+    # ------------------------------------------------------------- parity of what was just timed
+    parity = None
+    if not args.no_parity and not bwd:
+        host_threads()
+        if ring:
+            kf = [torch.empty_like(k) for _ in range(world)]
+            vf = [torch.empty_like(v) for _ in range(world)]
+            dist.all_gather(kf, k)
+            dist.all_gather(vf, v)
+            mx, mean, nrows = parity_ring(last, q, torch.cat(kf, 1), torch.cat(vf, 1), h, d, causal, args.mask_mode,
+                                          rank, world, dtn)
+            del kf, vf
+            agg = torch.tensor([mx, mean], device=device)
+            dist.all_reduce(agg, op=dist.ReduceOp.MAX)
+            bmax, bmean = _bounds(dtn)
+            mx, mean = float(agg[0]), float(agg[1])
+            parity = {"max_abs": mx, "mean_abs": mean, "rows": nrows * world, "bound_max_abs": bmax,
+                      "bound_mean_abs": bmean,
+                      "against": f"CPU ring oracle ({args.mask_mode} mask over all {world} key shards), {nrows} sampled rows "
+                                 "of every rank's last timed output, all heads; max over ranks",
+                      "ok": bool(mx <= bmax and mean <= bmean)}
+        else:
+            parity = parity_single(last if not isinstance(last, tuple) else last[0], q, k, v, h, d, causal, q_off, dtn)
+
+    # ------------------------------------------------------------- same-box single-GPU time of the ring workload
+    n1_ms = None
+    if ring and not args.no_n1:
+        if rank == 0:
+            fq, fk, fv = make_inputs(name, device)
+            fid = torch.zeros((b, t), dtype=torch.int32, device=device)
+            # one shard = the whole sequence: the ring's only step is the plain causal forward
+            run1 = lambda: tpa_b200.tpa.fwd_device(fq, fk, fv, h, fid, fid, sm_scale, causal, want_lse=False)  # noqa: E731
+            run1()
+            torch.cuda.synchronize(device)
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a0.record()
+            for _ in range(3):
+                run1()
+            a1.record()
+            torch.cuda.synchronize(device)
+            n1_ms = a0.elapsed_time(a1) / 3
+            del fq, fk, fv
+        dist.barrier()
+
     if rank != 0:
         if ring:
             dist.destroy_process_group()
@@ -394,25 +538,26 @@ def main():
                     "traffic": None, "kernel": info["kernel"], "hbm_algorithmic_bytes": stream}
     cpu = None
     if not args.no_cpu_baseline and world == 1 and not bwd and args.lq is None:
-        tf, ctoks, cdt, sample = time_cpu(name, 1, 0)
-        cpu = {"value": tf, "unit": "TFLOP/s", "tokens_per_s": ctoks, "cores": torch.get_num_threads(), "kind": "port",
+        cores = host_threads()
+        tf, ctoks, cdt, sample = time_cpu(name, 1, 0, 2048)
+        cpu = {"value": tf, "unit": "TFLOP/s", "tokens_per_s": ctoks, "cores": cores, "kind": "port",
                "sample": sample}
     line = {
         "metric": METRIC if not bwd else "TPA bwd algorithmic TFLOP/s per B200 (2.5x the forward's FLOPs)", "value": value, "unit": "TFLOP/s", "tokens_per_s": toks, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": dtn, "data": "synthetic",
-        "config": {"workload": name + (f"@lq{args.lq}" if args.lq is not None else ""),
-                   "shape": f"B{b} T{t} h{h} d{d} R{rq}/{rk}/{rk} causal={causal}"
-                            + (f", last {args.lq} query rows" if args.lq is not None else ""),
-                   "parallelism": f"ring sp{world} ({args.mask_mode} causal mask)" if ring else "single GPU",
-                   "l2": "inputs + outputs larger than L2 (no flush needed)" if name in ("c1", "c2", "c3") else "smaller than L2, not flushed",
-                   "cuda_graph": bool(args.graph),
-                   "kernel": info},
+        "config": config_for(name, world, args.mask_mode, args.lq), "kernel": info, "cuda_graph": bool(args.graph),
         "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clock_summary,
+        "parity": parity,
     }
+    if n1_ms is not None:
+        # strong scaling on one box: the unsharded workload on one GPU against N GPUs
+        line["ring"] = {"n1_ms": n1_ms, "ring_efficiency": n1_ms / (world * ms), "mask_mode": args.mask_mode}
     print(json.dumps(line), flush=True)
     if ring:
         dist.destroy_process_group()
+    if parity is not None and not parity["ok"]:
+        sys.exit(3)
 
 
 if __name__ == "__main__":

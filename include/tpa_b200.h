@@ -122,8 +122,8 @@ typedef struct TpaKernelInfo {
 
 /* Forward pass.  Replaces pl.pallas_call(_fwd_kernel ...) at tpa/tpa.py:492-543 for the
  * whole batch.  `workspace` must hold tpa_fwd_workspace_bytes(args) bytes (may be NULL
- * when that is 0) and be 256-byte aligned; its first 16 bytes are a device status block
- * (see tpa_read_status). */
+ * when that is 0) and be 256-byte aligned; its first 256 bytes are reserved for a device status
+ * block, of which the first 16 are used (see tpa_read_status). */
 int tpa_fwd(const TpaFwdArgs* args, void* workspace, size_t workspace_bytes, void* stream);
 
 /* Same forward pass for callers that cannot allocate the workspace: an XLA custom-call
@@ -139,6 +139,12 @@ int tpa_fwd(const TpaFwdArgs* args, void* workspace, size_t workspace_bytes, voi
  * them overlap.  Every GPU that loads the library holds TPA_STATIC_SCRATCH_BYTES until exit. */
 #define TPA_STATIC_SCRATCH_BYTES (64u << 20)
 int tpa_fwd_static_scratch(const TpaFwdArgs* args, void* stream);
+
+/* tpa_read_status for tpa_fwd_static_scratch (no counterpart in the reference): the status block
+ * of that entry point is the head of the library's static array, whose address no caller holds.
+ * Synchronises `stream`, reads the block of the current device and returns TPA_OK or
+ * TPA_ERR_DEVICE_TIMEOUT; `detail` as for tpa_read_status.  Allocates nothing. */
+int tpa_read_status_static_scratch(void* stream, uint32_t detail[4]);
 
 /* Backward pass: gradients of the forward result with respect to the three concatenated
  * factor arrays.  Replaces _tpa_bwd / _bwd (tpa/tpa.py:168-217, 823-962): _precompute_delta
@@ -173,8 +179,8 @@ typedef struct TpaBwdArgs {
 
 /* `workspace`: tpa_bwd_workspace_bytes(args) bytes, 256-byte aligned (dense fp32 dQ, dK, dV
  * of the whole batch, delta and, for the tensor-core passes, the staged bf16 Q, K, V, dO tiles).
- * Six launches (SIMT) or eight (tensor cores); enqueue-only.  The first 16 bytes are the device
- * status block that tpa_read_status reads. */
+ * Six launches (SIMT) or eight (tensor cores); enqueue-only.  The first 256 bytes are reserved for
+ * the device status block that tpa_read_status reads (16 bytes used). */
 int tpa_bwd(const TpaBwdArgs* args, void* workspace, size_t workspace_bytes, void* stream);
 size_t tpa_bwd_workspace_bytes(const TpaBwdArgs* args);
 
@@ -188,6 +194,14 @@ int tpa_query_kernel(const TpaFwdArgs* args, TpaKernelInfo* info);
  * TPA_OK or TPA_ERR_DEVICE_TIMEOUT.  `detail` (host, may be NULL) receives the raw
  * device words {flag, where, block, spins}. */
 int tpa_read_status(const void* workspace, void* stream, uint32_t detail[4]);
+
+/* Self-test of the bounded device-side waits (no counterpart in the reference): launches one warp
+ * that waits on a barrier nothing ever signals, with a budget of `budget_cycles` SM cycles (at most
+ * 2^28) instead of the kernels' 2^28.  The wait runs out, the kernel ends normally and the status
+ * block at the head of `workspace` (>= 256 bytes, 256-byte aligned) then reads
+ * {1, 0x7e57, block, spins}: tpa_read_status returns TPA_ERR_DEVICE_TIMEOUT.  Nothing faults or
+ * stays waiting; the context remains usable. */
+int tpa_selftest_wait_timeout(void* workspace, size_t workspace_bytes, int64_t budget_cycles, void* stream);
 
 /* Human-readable text for a status code (static storage). */
 const char* tpa_status_string(int status);

@@ -509,9 +509,11 @@ def tpa_reference_torch(
     o = torch.empty((b, nq, h, dv), dtype=dtype)
     l = torch.empty((b, nq, h), dtype=dtype)
     for hi in range(h):
-        qh = torch.einsum("blr,blrd->bld", q[..., hi], q[..., h:]) / rq
-        kh = torch.einsum("blr,blrd->bld", k[..., hi], k[..., h:]) / rk
-        vh = torch.einsum("blr,blrd->bld", v[..., hi], v[..., h:]) / rk
+        # rank mean as a broadcast multiply + sum: torch threads it, an einsum with these shapes
+        # becomes l tiny matrix products on one core
+        qh = (q[..., hi, None] * q[..., h:]).sum(2) / rq
+        kh = (k[..., hi, None] * k[..., h:]).sum(2) / rk
+        vh = (v[..., hi, None] * v[..., h:]).sum(2) / rk
         x = torch.einsum("bqd,bkd->bqk", qh, kh) * sm_scale
         if keep is not None:
             x = x.masked_fill(~keep, -math.inf)

@@ -13,7 +13,7 @@ static thread_local char g_cuda_error[256] = "";
 
 void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
 
-static int fail_cuda(cudaError_t e) {
+int fail_cuda(cudaError_t e) {
   std::snprintf(g_cuda_error, sizeof(g_cuda_error), "%s: %s", cudaGetErrorName(e),
                 cudaGetErrorString(e));
   return TPA_ERR_CUDA;
@@ -232,6 +232,16 @@ int tpa_bwd(const TpaBwdArgs* args, void* workspace, size_t workspace_bytes, voi
     if (e == cudaSuccess) e = launch_bwd_pairs_simt(bp, s);
   }
   if (e == cudaSuccess) e = launch_bwd_contract(bp, s);
+  return e == cudaSuccess ? TPA_OK : fail_cuda(e);
+}
+
+int tpa_selftest_wait_timeout(void* workspace, size_t workspace_bytes, int64_t budget_cycles, void* stream) {
+  if (workspace == nullptr || workspace_bytes < kStatusBytes || (reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
+    return TPA_ERR_WORKSPACE;
+  if (budget_cycles <= 0 || budget_cycles > (int64_t)1 << 28) return TPA_ERR_BAD_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemsetAsync(workspace, 0, kStatusBytes, s);
+  if (e == cudaSuccess) e = launch_wait_selftest(static_cast<uint32_t*>(workspace), budget_cycles, s);
   return e == cudaSuccess ? TPA_OK : fail_cuda(e);
 }
 

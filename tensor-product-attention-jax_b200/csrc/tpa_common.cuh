@@ -69,7 +69,11 @@ cudaError_t launch_decode(const Params& p, void* workspace, TpaKernelInfo* info,
 cudaError_t launch_combine_splits(const Params& p, const float* part_o, const float* part_lse, int splits,
                                   cudaStream_t stream);
 
+cudaError_t launch_wait_selftest(uint32_t* status, long long budget_cycles, cudaStream_t stream);
+
 void count_launch(int n);
+// Records the text of `e` for tpa_last_cuda_error() on this thread and returns TPA_ERR_CUDA.
+int fail_cuda(cudaError_t e);
 
 __device__ __forceinline__ float to_float(float x) { return x; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }

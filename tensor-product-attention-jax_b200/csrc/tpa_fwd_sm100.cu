@@ -86,6 +86,7 @@ struct Barriers {
 struct Waiter {
   Barriers* bars;
   uint32_t* status;
+  long long budget = kWaitCycles;
   // Returns when the phase with this parity has completed, or after the cycle budget.
   __device__ __forceinline__ void operator()(uint64_t* bar, uint32_t parity, uint32_t where) const {
     if (mbar_try_wait(bar, parity)) return;
@@ -93,7 +94,7 @@ struct Waiter {
     uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
       if (bars->abort) return;
-      if ((++spins & 63u) == 0 && clock64() - t0 > kWaitCycles) {
+      if ((++spins & 63u) == 0 && clock64() - t0 > budget) {
         bars->abort = 1;
         if (status != nullptr && atomicCAS(status, 0u, 1u) == 0u) {
           status[1] = where;
@@ -416,7 +417,7 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = bars->tmem_base;
-  const Waiter wait{bars, p.status};
+  const Waiter wait{bars, p.status, kWaitCycles};
   const __nv_bfloat16* qa = static_cast<const __nv_bfloat16*>(p.qa.ptr) + batch * p.qa.stride[0] + head;
   const __nv_bfloat16* qb = static_cast<const __nv_bfloat16*>(p.qb.ptr) + batch * p.qb.stride[0];
   const __nv_bfloat16* ka = static_cast<const __nv_bfloat16*>(p.ka.ptr) + batch * p.ka.stride[0] + head;
@@ -1042,48 +1043,23 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
   if (warp == 0) tmem_dealloc(tmem, 512);
 }
 
-// ---------------------------------------------------------------------------------------------
-// Merges the partial (o, lse) of the key splits (and the caller's carried state, if loaded) the
-// way the ring merges steps (tpa/ring_tpa.py:82-91): weights exp(lse_i - max), normalised.
-// One thread per (row, head, 4 columns).
-__global__ void __launch_bounds__(256) tpa_combine_splits_kernel(const Params p, const float* part_o,
-                                                                 const float* part_lse, int splits) {
-  const int d = p.dv;
-  const int64_t rows = (int64_t)p.batch * p.lq * p.heads;
-  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= rows * (d / 4)) return;
-  const int64_t rh = idx / (d / 4);
-  const int c = (int)(idx % (d / 4)) * 4;
-  const bool load = (p.flags & TPA_FLAG_STATE_LOAD) != 0, store = (p.flags & TPA_FLAG_STATE_STORE) != 0;
-  float m = load ? p.state_lse[rh] : -CUDART_INF_F;
-  for (int s = 0; s < splits; ++s) m = fmaxf(m, part_lse[s * rows + rh]);
-  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  float wsum = 0.f;
-  auto add = [&](const float* o, float lse) {
-    if (lse == -CUDART_INF_F) return;
-    const float w = expf(lse - m);
-    const float4 v = *reinterpret_cast<const float4*>(o);
-    acc.x += w * v.x; acc.y += w * v.y; acc.z += w * v.z; acc.w += w * v.w;
-    wsum += w;
-  };
-  if (m != -CUDART_INF_F) {
-    if (load) add(p.state_o + rh * d + c, p.state_lse[rh]);
-    for (int s = 0; s < splits; ++s) add(part_o + (s * rows + rh) * d + c, part_lse[s * rows + rh]);
+// Self-test of the bounded wait: one warp waits, with a short cycle budget, on an mbarrier that
+// nothing ever arrives at.  The wait runs out, the status block records {1, where, block, spins},
+// the abort flag makes the second wait fall through at once, and the kernel ends normally.
+__global__ void __launch_bounds__(32) tpa_wait_selftest_kernel(uint32_t* status, long long budget) {
+  __shared__ Barriers bars;
+  if (threadIdx.x == 0) {
+    mbar_init(&bars.q_full, 1);
+    bars.abort = 0;
+    fence_mbar_init();
   }
-  const bool none = !(wsum > 0.f);
-  const float inv = none ? 0.f : 1.f / wsum;
-  const float lse = none ? -CUDART_INF_F : m + logf(wsum);
-  if (store) {
-    *reinterpret_cast<float4*>(p.state_o + rh * d + c) = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
-    if (c == 0) p.state_lse[rh] = lse;
-  } else {
-    const float q = none ? CUDART_NAN_F : 1.f;  // rows that saw no key are NaN (tpa/tpa.py:439)
-    uint2 o;
-    o.x = pack_bf16(acc.x * inv * q, acc.y * inv * q);
-    o.y = pack_bf16(acc.z * inv * q, acc.w * inv * q);
-    *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(p.o) + rh * d + c) = o;
-    if (c == 0 && p.lse != nullptr) p.lse[rh] = lse;
+  __syncwarp();
+  const Waiter wait{&bars, status, budget};
+  if (threadIdx.x == 0) {
+    wait(&bars.q_full, 0, 0x7e57);
+    wait(&bars.q_full, 0, 0x7e58);  // falls through: the abort flag is up
   }
+  __syncwarp();
 }
 
 template <int D>
@@ -1113,67 +1089,110 @@ cudaError_t launch_attn(const Params& p, const uint8_t* wq, const uint8_t* wk, c
 
 }  // namespace
 
-// The same merge with one WARP per (row, head, 4 columns), lanes over the splits: for the many
-// splits of a decode call (hundreds of partials of a handful of rows) the serial walk above is a
-// chain of dependent loads; here it is splits / 32 steps and two shuffle reductions.
-__global__ void __launch_bounds__(256) tpa_combine_splits_warp_kernel(const Params p, const float* part_o,
-                                                                      const float* part_lse, int splits) {
-  const int d = p.dv, lane = threadIdx.x & 31;
+// Merges the partial (o, lse) of the key splits (and the caller's carried state, if loaded) the
+// way the ring merges steps (tpa/ring_tpa.py:82-91): weights exp(lse_i - max), normalised.
+//
+// One CTA of 8 warps serves whole (row, head) items, never a part of one: with STATE_LOAD and
+// STATE_STORE on the same buffers (every middle ring step) the old state_lse / state_o of an item
+// are read by the same CTA that overwrites them, after a barrier, so no other block can see a
+// half-updated item.  WPR = warps per item: 1 (eight items per CTA; a handful of splits) or 8 (one
+// item per CTA; the hundreds of partials of a decode call, warps striding over the splits and
+// meeting in shared memory).  Lanes own the columns (float4 each, two when dv > 128).
+template <int WPR>
+__global__ void __launch_bounds__(256) tpa_combine_splits_kernel(const Params p, const float* part_o,
+                                                                 const float* part_lse, int splits) {
+  constexpr int kItems = 8 / WPR;
+  __shared__ float4 red_acc[WPR > 1 ? 8 : 1][64];
+  __shared__ float red_w[8];
+  const int d = p.dv, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int sub = warp % WPR;
   const int64_t rows = (int64_t)p.batch * p.lq * p.heads;
-  const int64_t idx = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (idx >= rows * (d / 4)) return;
-  const int64_t rh = idx / (d / 4);
-  const int c = (int)(idx % (d / 4)) * 4;
+  const int64_t rh_raw = (int64_t)blockIdx.x * kItems + warp / WPR;
+  const bool item_ok = rh_raw < rows;
+  const int64_t rh = item_ok ? rh_raw : rows - 1;  // idle warps shadow the last item and write nothing
   const bool load = (p.flags & TPA_FLAG_STATE_LOAD) != 0, store = (p.flags & TPA_FLAG_STATE_STORE) != 0;
-  float m = (load && lane == 0) ? p.state_lse[rh] : -CUDART_INF_F;
+  const int nchunk = d / 4;  // float4 chunks per row (dv is a multiple of 4 here)
+  const float old_lse = load ? p.state_lse[rh] : -CUDART_INF_F;
+
+  // every warp finds the maximum over all splits itself (splits / 32 loads per lane)
+  float m = old_lse;
   for (int s = lane; s < splits; s += 32) m = fmaxf(m, part_lse[s * rows + rh]);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+
+  float4 acc[2] = {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)};
   float wsum = 0.f;
   auto add = [&](const float* o, float lse) {
-    if (lse == -CUDART_INF_F) return;
+    if (lse == -CUDART_INF_F) return;  // warp-uniform
     const float w = expf(lse - m);
-    const float4 v = *reinterpret_cast<const float4*>(o);
-    acc.x += w * v.x; acc.y += w * v.y; acc.z += w * v.z; acc.w += w * v.w;
     wsum += w;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int c = lane + 32 * i;
+      if (c < nchunk) {
+        const float4 v = *reinterpret_cast<const float4*>(o + c * 4);
+        acc[i].x += w * v.x; acc[i].y += w * v.y; acc[i].z += w * v.z; acc[i].w += w * v.w;
+      }
+    }
   };
   if (m != -CUDART_INF_F) {
-    if (load && lane == 0) add(p.state_o + rh * d + c, p.state_lse[rh]);
-    for (int s = lane; s < splits; s += 32) add(part_o + (s * rows + rh) * d + c, part_lse[s * rows + rh]);
+    if (load && sub == 0) add(p.state_o + rh * d, old_lse);
+#pragma unroll 4
+    for (int s = sub; s < splits; s += WPR) add(part_o + (s * rows + rh) * d, part_lse[s * rows + rh]);
   }
+  if constexpr (WPR > 1) {
+    // the eight warps of the item meet in shared memory, warp 0 finishes
+    if (lane == 0) red_w[warp] = wsum;
+    if (warp > 0) {
+      red_acc[warp][lane] = acc[0];
+      red_acc[warp][lane + 32] = acc[1];
+    }
+    __syncthreads();
+    if (warp > 0) return;
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    acc.x += __shfl_xor_sync(0xffffffffu, acc.x, o);
-    acc.y += __shfl_xor_sync(0xffffffffu, acc.y, o);
-    acc.z += __shfl_xor_sync(0xffffffffu, acc.z, o);
-    acc.w += __shfl_xor_sync(0xffffffffu, acc.w, o);
-    wsum += __shfl_xor_sync(0xffffffffu, wsum, o);
+    for (int w = 1; w < 8; ++w) {
+      wsum += red_w[w];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const float4 v = red_acc[w][lane + 32 * i];
+        acc[i].x += v.x; acc[i].y += v.y; acc[i].z += v.z; acc[i].w += v.w;
+      }
+    }
+  } else {
+    __syncthreads();  // all items of the CTA have read their old state before anyone overwrites it
   }
-  if (lane != 0) return;
+  if (!item_ok) return;
   const bool none = !(wsum > 0.f);
   const float inv = none ? 0.f : 1.f / wsum;
   const float lse = none ? -CUDART_INF_F : m + logf(wsum);
-  if (store) {
-    *reinterpret_cast<float4*>(p.state_o + rh * d + c) = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
-    if (c == 0) p.state_lse[rh] = lse;
-  } else {
-    const float q = none ? CUDART_NAN_F : 1.f;  // rows that saw no key are NaN (tpa/tpa.py:439)
-    uint2 o;
-    o.x = pack_bf16(acc.x * inv * q, acc.y * inv * q);
-    o.y = pack_bf16(acc.z * inv * q, acc.w * inv * q);
-    *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(p.o) + rh * d + c) = o;
-    if (c == 0 && p.lse != nullptr) p.lse[rh] = lse;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int c = lane + 32 * i;
+    if (c >= nchunk) continue;
+    if (store) {
+      *reinterpret_cast<float4*>(p.state_o + rh * d + c * 4) =
+          make_float4(acc[i].x * inv, acc[i].y * inv, acc[i].z * inv, acc[i].w * inv);
+    } else {
+      const float q = none ? CUDART_NAN_F : 1.f;  // rows that saw no key are NaN (tpa/tpa.py:439)
+      uint2 o;
+      o.x = pack_bf16(acc[i].x * inv * q, acc[i].y * inv * q);
+      o.y = pack_bf16(acc[i].z * inv * q, acc[i].w * inv * q);
+      *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(p.o) + rh * d + c * 4) = o;
+    }
+  }
+  if (lane == 0) {
+    if (store) p.state_lse[rh] = lse;
+    else if (p.lse != nullptr) p.lse[rh] = lse;
   }
 }
 
 cudaError_t launch_combine_splits(const Params& p, const float* part_o, const float* part_lse, int splits,
                                   cudaStream_t stream) {
-  const int64_t items = (int64_t)p.batch * p.lq * p.heads * (p.dv / 4);
+  const int64_t rows = (int64_t)p.batch * p.lq * p.heads;
   if (splits > 32)
-    tpa_combine_splits_warp_kernel<<<(unsigned)((items + 7) / 8), 256, 0, stream>>>(p, part_o, part_lse, splits);
+    tpa_combine_splits_kernel<8><<<(unsigned)rows, 256, 0, stream>>>(p, part_o, part_lse, splits);
   else
-    tpa_combine_splits_kernel<<<(unsigned)((items + 255) / 256), 256, 0, stream>>>(p, part_o, part_lse, splits);
+    tpa_combine_splits_kernel<1><<<(unsigned)((rows + 7) / 8), 256, 0, stream>>>(p, part_o, part_lse, splits);
   count_launch(1);
   return cudaGetLastError();
 }
@@ -1319,13 +1338,14 @@ cudaError_t launch_sm100(const Params& p, int variant, void* workspace, TpaKerne
   }
   if (e != cudaSuccess) return e;
   count_launch(1);
-  if (splits > 1) {
-    const int64_t threads = (int64_t)p.batch * p.lq * p.heads * (p.dv / 4);
-    tpa_combine_splits_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(p, part_o, part_lse, splits);
-    e = cudaGetLastError();
-    if (e == cudaSuccess) count_launch(1);
-  }
+  if (splits > 1) e = launch_combine_splits(p, part_o, part_lse, splits, stream);
   return e;
+}
+
+cudaError_t launch_wait_selftest(uint32_t* status, long long budget_cycles, cudaStream_t stream) {
+  tpa_wait_selftest_kernel<<<1, 32, 0, stream>>>(status, budget_cycles);
+  count_launch(1);
+  return cudaGetLastError();
 }
 
 }  // namespace tpa

@@ -68,6 +68,17 @@ extern "C" int tpa_fwd_static_scratch(const TpaFwdArgs* args, void* stream) {
   if (tpa_fwd_workspace_bytes(&a) > (size_t)TPA_STATIC_SCRATCH_BYTES) return TPA_ERR_STATIC_SCRATCH;
   cudaError_t err = cudaSuccess;
   void* scratch = scratch_for_current_device(&err);
-  if (scratch == nullptr) return TPA_ERR_CUDA;
+  // the first look-up on a device is where the array is instantiated, the step most likely to
+  // fail in a process whose memory is already reserved: its error text must not be lost
+  if (scratch == nullptr) return tpa::fail_cuda(err);
   return tpa_fwd(&a, scratch, (size_t)TPA_STATIC_SCRATCH_BYTES, stream);
+}
+
+// The status block of tpa_fwd_static_scratch sits at the head of the static array, whose address
+// no caller has; this reads it for the current device (same contract as tpa_read_status).
+extern "C" int tpa_read_status_static_scratch(void* stream, uint32_t detail[4]) {
+  cudaError_t err = cudaSuccess;
+  void* scratch = scratch_for_current_device(&err);
+  if (scratch == nullptr) return tpa::fail_cuda(err);
+  return tpa_read_status(scratch, stream, detail);
 }

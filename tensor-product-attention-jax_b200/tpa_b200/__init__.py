@@ -9,6 +9,6 @@ is no CPU or PyTorch fallback.
 """
 
 from . import _capi  # noqa: F401  (loads the shared library or raises)
-from . import tpa, ring_tpa  # noqa: F401
+from . import tpa, ring_tpa, mha  # noqa: F401
 
-__all__ = ["tpa", "ring_tpa"]
+__all__ = ["tpa", "ring_tpa", "mha"]

@@ -36,11 +36,13 @@ BWD_ACCUMULATE_DQ, BWD_ACCUMULATE_DKV = 1, 2
 EXPORTS = (
     "tpa_fwd",
     "tpa_fwd_static_scratch",
+    "tpa_read_status_static_scratch",
     "tpa_fwd_workspace_bytes",
     "tpa_bwd",
     "tpa_bwd_workspace_bytes",
     "tpa_query_kernel",
     "tpa_read_status",
+    "tpa_selftest_wait_timeout",
     "tpa_status_string",
     "tpa_last_cuda_error",
     "tpa_launch_count",
@@ -126,6 +128,8 @@ def _load():
     lib.tpa_fwd.restype = C.c_int
     lib.tpa_fwd_static_scratch.argtypes = [C.POINTER(TpaFwdArgs), C.c_void_p]
     lib.tpa_fwd_static_scratch.restype = C.c_int
+    lib.tpa_read_status_static_scratch.argtypes = [C.c_void_p, C.POINTER(C.c_uint32 * 4)]
+    lib.tpa_read_status_static_scratch.restype = C.c_int
     lib.tpa_fwd_workspace_bytes.argtypes = [C.POINTER(TpaFwdArgs)]
     lib.tpa_fwd_workspace_bytes.restype = C.c_size_t
     lib.tpa_bwd.argtypes = [C.POINTER(TpaBwdArgs), C.c_void_p, C.c_size_t, C.c_void_p]
@@ -136,6 +140,8 @@ def _load():
     lib.tpa_query_kernel.restype = C.c_int
     lib.tpa_read_status.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_uint32 * 4)]
     lib.tpa_read_status.restype = C.c_int
+    lib.tpa_selftest_wait_timeout.argtypes = [C.c_void_p, C.c_size_t, C.c_int64, C.c_void_p]
+    lib.tpa_selftest_wait_timeout.restype = C.c_int
     lib.tpa_status_string.argtypes = [C.c_int]
     lib.tpa_status_string.restype = C.c_char_p
     lib.tpa_last_cuda_error.argtypes = []

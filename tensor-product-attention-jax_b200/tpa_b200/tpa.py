@@ -43,6 +43,8 @@ class BlockSizes:
 
 _DTYPES = {torch.float32: _capi.DTYPE_F32, torch.bfloat16: _capi.DTYPE_BF16}
 _workspaces: dict = {}
+# what the Q tiles staged in a workspace were made from: key as _workspaces, value = signature
+_staged_q: dict = {}
 
 
 def _workspace(device, nbytes, kind=None):
@@ -211,6 +213,15 @@ def fwd_device(
         nbytes = _capi.lib.tpa_fwd_workspace_bytes(C.byref(a))
         ws = _workspace(q.device, nbytes)
         stream = torch.cuda.current_stream(q.device).cuda_stream
+        # TPA_FLAG_REUSE_STAGED_Q is a promise about the workspace's contents; keep it only when the
+        # last call that staged into this very buffer had the same q operand, shapes and scale
+        # (another call on the stream, or a regrown buffer, silently voids the caller's promise)
+        sig = (q.data_ptr(), q._version, tuple(q.shape), tuple(q.stride()), q.dtype, tuple(k.shape), num_heads,
+               float(sm_scale), ws.data_ptr() if ws is not None else 0, nbytes, a.kernel)
+        key = (q.device, stream)
+        if reuse_staged_q and _staged_q.get(key) != sig:
+            a.flags &= ~_capi.FLAG_REUSE_STAGED_Q
+        _staged_q[key] = sig
         st = _capi.lib.tpa_fwd(
             C.byref(a), ws.data_ptr() if ws is not None else None, nbytes, C.c_void_p(stream)
         )

@@ -394,3 +394,56 @@ def test_decode_kernel(case):
     assert torch.nan_to_num(f(o2) - ref).abs().max() <= 2e-2
     with pytest.raises(ValueError):  # forced on a shape it does not take
         tpa_b200.tpa.fwd_device(tq.float(), tk.float(), tv.float(), h, kernel="decode")
+
+
+@pytest.mark.parametrize("kernel,b,lq,h,d,dv,chunk", [
+    ("decode", 2, 4, 48, 64, 48, 6144),       # > 32 splits: one merge CTA per (row, head), 384 of them
+    ("decode", 1, 8, 32, 128, 96, 4864),      # dv = 96: 24 float4 chunks per row
+    ("decode", 3, 1, 64, 128, 128, 2048),     # few splits: eight (row, head) items per merge CTA
+    ("sm100_staged", 1, 200, 8, 128, 128, 4096),   # key splits of the tensor-core kernel
+])
+def test_middle_ring_step_loads_and_stores_the_same_state(kernel, b, lq, h, d, dv, chunk):
+    """A middle ring step reads and writes ONE carried state (TPA_FLAG_STATE_LOAD and _STORE on the
+    same buffers) while its key splits are merged: three key chunks chained store / load+store /
+    load must equal one call over all keys.  The merge of an item's splits must see the old
+    state of that item only, whichever block or wave serves it."""
+    lk = 3 * chunk
+    q, k, v = orc.make_factors(123, b, max(lq, lk), max(lq, lk), 3, 2, h, d, dv)
+    tq, tk, tv = dev(q[:, :lq], torch.bfloat16), dev(k[:, :lk], torch.bfloat16), dev(v[:, :lk], torch.bfloat16)
+    q_off = lk - lq
+    args = (h, None, None, d**-0.5, True)
+    info = tpa_b200.tpa.query_kernel(tq, tk[:, :chunk], tv[:, :chunk], h, kernel=kernel, causal=True)
+    assert info["launches"] >= 2 and info["grid"][0 if kernel == "decode" else 1] > 1, info
+    state = (torch.empty(b, lq, h, dv, device="cuda"), torch.empty(b, lq, h, device="cuda"))
+    for _ in range(3):  # a race need not show on the first attempt
+        for i in range(3):
+            ks = slice(i * chunk, (i + 1) * chunk)
+            o, lse = tpa_b200.tpa.fwd_device(tq, tk[:, ks], tv[:, ks], *args, q_offset=q_off, k_offset=i * chunk,
+                                             state=state, load_state=i > 0, store_state=i < 2, kernel=kernel)
+        f = lambda t: t.float().cpu()  # noqa: E731
+        ref, lref = orc.tpa_reference_torch(f(tq), f(tk), f(tv), h, sm_scale=d**-0.5, causal=True, q_offset=q_off,
+                                            return_lse=True)
+        diff = (f(o) - ref).abs()
+        assert diff.max() <= 2e-2 and diff.mean() <= 5e-3, (float(diff.max()), float(diff.mean()))
+        assert (lse.cpu() - lref).abs().max() <= 1e-2
+
+
+def test_bounded_wait_runs_out_and_reports():
+    """A device-side wait that nothing satisfies gives up after its cycle budget: the kernel ends
+    normally, the status block says where, tpa_read_status returns TPA_ERR_DEVICE_TIMEOUT, and the
+    next launch on the same context works.  (One warp, a budget of about a millisecond.)"""
+    import ctypes as C
+    ws = torch.zeros(4096, dtype=torch.uint8, device="cuda")
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    st = _capi.lib.tpa_selftest_wait_timeout(ws.data_ptr(), ws.numel(), 1 << 21, stream)
+    assert st == _capi.TPA_OK, _capi.status_string(st)
+    detail = (C.c_uint32 * 4)()
+    st = _capi.lib.tpa_read_status(ws.data_ptr(), stream, C.byref(detail))
+    assert st == _capi.TPA_ERR_DEVICE_TIMEOUT
+    flag, where, block, spins = list(detail)
+    assert flag == 1 and where == 0x7e57 and block == 0 and spins >= 64
+    assert "wait ran out" in _capi.status_string(st)
+    # the context is intact
+    q, k, v = orc.make_factors(1, 1, 8, 8, 1, 1, 1, 4, 6)
+    o = tpa_b200.tpa.tpa(dev(q), dev(k), dev(v), num_heads=1)
+    assert np.max(np.abs(o.cpu().numpy() - orc.tpa_reference(q, k, v, 1))) <= 1e-5

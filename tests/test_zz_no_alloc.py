@@ -52,6 +52,7 @@ def _case(seed, b, t, h, d, rq, rk):
 
 def test_static_scratch_matches_workspace_entry_point_twice():
     stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    first = True
     for seed, (b, t, h, d, rq, rk), causal in [(901, (2, 1024, 8, 128, 3, 2), True),
                                                (902, (1, 512, 16, 64, 2, 4), False)]:
         q, k, v = _case(seed, b, t, h, d, rq, rk)
@@ -62,11 +63,23 @@ def test_static_scratch_matches_workspace_entry_point_twice():
         got = torch.full_like(want, float("nan"))
         got_lse = torch.full_like(want_lse, float("nan"))
         a = _args(q, k, v, h, got, got_lse, d**-0.5, causal)
+        if first:
+            # the first call on a device looks the array up (and lets the driver instantiate it):
+            # make it before measuring free memory, as a caller would at start-up
+            assert _capi.lib.tpa_fwd_static_scratch(C.byref(a), stream) == _capi.TPA_OK
+            first = False
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
         n0 = _capi.lib.tpa_launch_count()
         st = _capi.lib.tpa_fwd_static_scratch(C.byref(a), stream)
         assert st == _capi.TPA_OK, _capi.status_string(st)
         torch.cuda.synchronize()
         assert _capi.lib.tpa_launch_count() == n0 + launches  # the same kernels, nothing else
+        # nothing was allocated on the device: free memory is what it was before the call
+        assert torch.cuda.mem_get_info()[0] == free_before
+        # the status block inside the static array is readable, and no bounded wait ran out
+        detail = (C.c_uint32 * 4)()
+        assert _capi.lib.tpa_read_status_static_scratch(stream, C.byref(detail)) == _capi.TPA_OK, list(detail)
         # tolerance of the bf16 tests; in fact bit-identical (same kernels, same inputs)
         diff = (got.float() - want.float()).abs()
         assert diff.max() <= 2e-2 and diff.mean() <= 5e-3
