@@ -23,7 +23,7 @@
 extern "C" {
 #endif
 
-#define TPA_B200_ABI_VERSION 1
+#define TPA_B200_ABI_VERSION 2
 
 /* Status codes.  0 = success; negative = the call did nothing. */
 enum {
@@ -68,10 +68,20 @@ enum {
                                (the carry of tpa/ring_tpa.py:69-71) instead of (0, -inf)       */
   TPA_FLAG_STATE_STORE = 4, /* write the merged partial back to state_o / state_lse
                                (tpa/ring_tpa.py:82-91) instead of the final o / lse            */
-  TPA_FLAG_REUSE_STAGED_Q = 8 /* the workspace is the one the previous call used, with the same
+  TPA_FLAG_REUSE_STAGED_Q = 8,/* the workspace is the one the previous call used, with the same
                                q operand, sm_scale, ranks and shapes (the ring scan keeps q
                                fixed, tpa/ring_tpa.py:73-79): the STAGED variant then skips
                                re-staging Q.  Ignored by the other kernels.                    */
+  TPA_FLAG_REUSE_STAGED_KV = 32,/* likewise for the K and V tiles: same k, v operands, ranks, lk and
+                               lq as the previous call on this workspace (two query chunks of
+                               one rank against the same gathered keys); STAGED only          */
+  TPA_FLAG_CAUSAL_PER_PART = 16 /* with kv_parts > 1: the causal (and window) comparison uses the
+                               key's index inside its own part, not in the whole key array.
+                               This is what the reference's ring computes with causal=True: no
+                               shard offset reaches its block kernel, so every visiting shard
+                               is masked on shard-local indices (tpa/ring_tpa.py:73-79,
+                               tpa/tpa.py:376-379).  One call with the N shards as N parts then
+                               equals the N steps of the scan plus their merges.               */
 };
 
 /* One factor operand: `ptr[b*stride[0] + l*stride[1] + r*stride[2] + c]`, c contiguous.
@@ -108,6 +118,34 @@ typedef struct TpaFwdArgs {
   int64_t q_offset, k_offset; /* global positions of local row 0 (causal comparison only)  */
   int32_t kernel;       /* TPA_KERNEL_*                                                    */
   int32_t reserved;
+  /* ---- everything below may stay zero: the call is then exactly the reference's ---------- */
+  int32_t kv_parts;     /* 0 or 1: k and v are one array.  P > 1: the lk keys are P parts of
+                           lk / P rows each (the visiting shards of a ring, gathered in one
+                           buffer, tpa/ring_tpa.py:96): part p of a factor starts
+                           p * {k,v}_part_stride elements after part 0, key index = p * lk/P +
+                           row.  Staged tensor-core variant and the generic kernel only; lk / P
+                           must be a multiple of 128.                                        */
+  int32_t window;       /* > 0: sliding-window attention, planned in the reference
+                           (tpa/ring_tpa.py:5-7, tpa/tpa.py:31-32) but not written there.  With
+                           diff = (i + q_offset) - (j + k_offset): key j is kept for query i iff
+                           diff < window * dilation, diff % dilation == 0 and (causal: diff >= 0;
+                           not causal: -diff < window * dilation), i.e. `window` keys at stride
+                           `dilation` behind the query (and as many ahead when not causal).   */
+  int32_t dilation;     /* 0 or 1: none; D > 1: only every D-th position (see window); may be
+                           used without a window                                             */
+  int32_t rope_len;     /* rows of rope_cos / rope_sin                                       */
+  int64_t k_part_stride, v_part_stride;   /* elements, kv_parts > 1                          */
+  int64_t kv_segment_part_stride;         /* elements of kv_segment_ids between parts        */
+  /* Rotary position embedding of the dim factors of q and k (the step before this path in a
+   * TPA model; the reference has none, its README links the paper only).  rope_cos / rope_sin:
+   * fp32 [rope_len, dk / 2].  Pairs of adjacent columns (2c, 2c + 1) of every rank row of B_Q
+   * at query row i are rotated by the angle whose cos / sin are in row i + rope_q_offset,
+   * column c; B_K at key index j likewise with j + rope_k_offset:
+   * (x, y) -> (x cos - y sin, x sin + y cos).  Rotation commutes with the rank sum, so it is
+   * applied once to each rebuilt Q and K row.  NULL: no rotation.  Forward only.            */
+  const float* rope_cos;
+  const float* rope_sin;
+  int64_t rope_q_offset, rope_k_offset;
 } TpaFwdArgs;
 
 typedef struct TpaKernelInfo {

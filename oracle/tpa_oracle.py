@@ -38,6 +38,10 @@ __all__ = [
     "ring_tpa_reference",
     "make_factors",
     "segment_ids",
+    "position_mask",
+    "key_positions",
+    "rope_tables",
+    "apply_rope",
     "attn_flops",
 ]
 
@@ -126,17 +130,77 @@ def lse_accum(a, b):
     return np.where(np.isneginf(hi), -np.inf, out)
 
 
-def _mask(b, lq, lk, q_seg, kv_seg, causal, q_offset=0, k_offset=0):
+def position_mask(q_pos, k_pos, causal, window=0, dilation=1):
+    """Keep-mask [lq, lk] from positions: the causal rule of tpa/tpa_test.py:52-54 /
+    tpa/tpa.py:376-379 (query position >= key position), and the sliding-window / dilated
+    variants the reference only plans (tpa/ring_tpa.py:5-7, tpa/tpa.py:31-32), defined here as:
+    with diff = q_pos - k_pos a pair is kept iff |diff| < window * dilation and
+    diff % dilation == 0 (and diff >= 0 when causal), i.e. `window` keys at stride `dilation`
+    behind the query, and as many ahead when not causal.  window = 0: no window."""
+    diff = np.asarray(q_pos)[:, None] - np.asarray(k_pos)[None, :]
+    keep = np.ones(diff.shape, dtype=bool)
+    if causal:
+        keep &= diff >= 0
+    dilation = max(1, int(dilation))
+    if window and window > 0:
+        span = int(window) * dilation
+        keep &= (diff < span) & (-diff < span)
+    if dilation > 1:
+        keep &= diff % dilation == 0
+    return keep
+
+
+def key_positions(lk, k_offset=0, kv_parts=1, per_part=False):
+    """Position of every key in the mask comparisons.  With `per_part` the keys are `kv_parts`
+    equal parts (the visiting shards of a ring) and each is compared on its index inside its own
+    part, which is what the reference's ring does at every step (tpa/ring_tpa.py:73-79)."""
+    idx = np.arange(lk)
+    if per_part and kv_parts > 1:
+        idx = idx % (lk // kv_parts)
+    return idx + k_offset
+
+
+def _mask(b, lq, lk, q_seg, kv_seg, causal, q_offset=0, k_offset=0, window=0, dilation=1, kv_parts=1,
+          per_part=False):
     """Boolean keep-mask [b, lq, lk] (tpa/tpa_test.py:46-55; tpa/tpa.py:369-383)."""
     keep = np.ones((b, lq, lk), dtype=bool)
     if q_seg is not None:
         assert kv_seg is not None
         keep &= np.asarray(q_seg)[:, :, None] == np.asarray(kv_seg)[:, None, :]
-    if causal:
-        qi = np.arange(lq)[:, None] + q_offset
-        ki = np.arange(lk)[None, :] + k_offset
-        keep &= (qi >= ki)[None]
+    if causal or window or dilation > 1:
+        keep &= position_mask(np.arange(lq) + q_offset, key_positions(lk, k_offset, kv_parts, per_part),
+                              causal, window, dilation)[None]
     return keep
+
+
+# --------------------------------------------------------------------------- rotary embedding
+
+
+def rope_tables(length, d, base=10000.0, dtype=np.float32):
+    """cos / sin tables [length, d / 2] of the rotary position embedding (Su et al., RoFormer):
+    angle of position t, pair c = t * base ** (-2 c / d)."""
+    inv = base ** (-np.arange(0, d, 2, dtype=np.float64) / d)
+    ang = np.arange(length, dtype=np.float64)[:, None] * inv[None, :]
+    return np.cos(ang).astype(dtype), np.sin(ang).astype(dtype)
+
+
+def apply_rope(x, num_heads, cos, sin, offset=0):
+    """Rotate the dim factor B = x[..., h:] of a concatenated factor array [b, l, r, h + d].
+
+    The reference has no rotary embedding (its README links the paper only); Tensor Product
+    Attention applies it to the B factors of q and k before the rank sum, which equals rotating
+    the rebuilt Q and K rows because the rotation is linear and the same for every rank:
+    columns (2c, 2c + 1) of row t turn by the angle of table row t + offset,
+    (x, y) -> (x cos - y sin, x sin + y cos).  Returns a new array; A is untouched."""
+    x = np.array(x, dtype=np.float64 if np.asarray(x).dtype == np.float64 else np.float32, copy=True)
+    l = x.shape[1]
+    c = np.asarray(cos)[offset:offset + l][None, :, None, :].astype(x.dtype)
+    s_ = np.asarray(sin)[offset:offset + l][None, :, None, :].astype(x.dtype)
+    b = x[..., num_heads:]
+    ev, od = b[..., 0::2].copy(), b[..., 1::2].copy()
+    b[..., 0::2] = ev * c - od * s_
+    b[..., 1::2] = ev * s_ + od * c
+    return x
 
 
 # --------------------------------------------------------------------------- (i) materialised definition
@@ -155,19 +219,25 @@ def tpa_reference(
     q_offset=0,
     k_offset=0,
     return_lse=False,
+    window=0,
+    dilation=1,
+    kv_parts=1,
+    per_part=False,
 ):
     """Definition of the result: tpa/tpa_test.py:22-57 + tpa/mha.py:23-37.
 
     Rows whose every key is masked come out NaN (softmax of all -inf), which is
     also what the kernel writes (tpa/tpa.py:439).  `q_offset/k_offset` shift the
     causal comparison to global positions; the reference has no such argument
-    (both are 0 there).
+    (both are 0 there).  `window`, `dilation`, `kv_parts`, `per_part`: see position_mask and
+    key_positions.
     """
     q_, k_, v_ = materialize(q, k, v, num_heads, dtype)
     b, lq = q_.shape[:2]
     lk = k_.shape[1]
     x = np.einsum("bqhd,bkhd->bhqk", q_, k_) * dtype(sm_scale)
-    keep = _mask(b, lq, lk, q_segment_ids, kv_segment_ids, causal, q_offset, k_offset)
+    keep = _mask(b, lq, lk, q_segment_ids, kv_segment_ids, causal, q_offset, k_offset, window, dilation, kv_parts,
+                 per_part)
     x = np.where(keep[:, None], x, -np.inf)
     with np.errstate(invalid="ignore", divide="ignore"):
         m = np.max(x, axis=-1, keepdims=True)
@@ -473,6 +543,10 @@ def tpa_reference_torch(
     k_offset=0,
     dtype=None,
     return_lse=False,
+    window=0,
+    dilation=1,
+    kv_parts=1,
+    per_part=False,
 ):
     """Same definition as tpa_reference, in torch on the host cores (all threads).
 
@@ -503,8 +577,9 @@ def tpa_reference_torch(
         if rows is not None:
             qs = qs[:, rows]
         keep = qs[:, :, None] == torch.as_tensor(kv_segment_ids)[:, None, :]
-    if causal:
-        c = (q_pos[:, None] + q_offset) >= (torch.arange(lk)[None, :] + k_offset)
+    if causal or window or dilation > 1:
+        c = torch.from_numpy(position_mask(q_pos.numpy() + q_offset, key_positions(lk, k_offset, kv_parts, per_part),
+                                           causal, window, dilation))
         keep = c[None] if keep is None else keep & c[None]
     o = torch.empty((b, nq, h, dv), dtype=dtype)
     l = torch.empty((b, nq, h), dtype=dtype)

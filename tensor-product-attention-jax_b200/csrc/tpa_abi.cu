@@ -40,8 +40,22 @@ static int validate(const TpaFwdArgs* a, Params* p) {
   if ((store || load) && (a->state_o == nullptr || a->state_lse == nullptr)) return TPA_ERR_BAD_ARG;
   if (!store && a->o == nullptr) return TPA_ERR_BAD_ARG;
   if (a->flags & ~(uint32_t)(TPA_FLAG_CAUSAL | TPA_FLAG_STATE_LOAD | TPA_FLAG_STATE_STORE |
-                             TPA_FLAG_REUSE_STAGED_Q))
+                             TPA_FLAG_REUSE_STAGED_Q | TPA_FLAG_CAUSAL_PER_PART | TPA_FLAG_REUSE_STAGED_KV))
     return TPA_ERR_BAD_ARG;
+  const int parts = a->kv_parts > 1 ? a->kv_parts : 1;
+  if (a->kv_parts < 0 || a->window < 0 || a->dilation < 0) return TPA_ERR_BAD_ARG;
+  if (parts > 1 && (a->lk % parts != 0 || a->k_part_stride <= 0 || a->v_part_stride <= 0)) return TPA_ERR_BAD_ARG;
+  if ((a->flags & TPA_FLAG_CAUSAL_PER_PART) && parts == 1) return TPA_ERR_BAD_ARG;
+  // the kernels compare clamped 32-bit differences against window * dilation
+  if ((int64_t)a->window * (a->dilation > 1 ? a->dilation : 1) > ((int64_t)1 << 29) || a->dilation > (1 << 29))
+    return TPA_ERR_UNSUPPORTED;
+  if ((a->rope_cos == nullptr) != (a->rope_sin == nullptr)) return TPA_ERR_BAD_ARG;
+  if (a->rope_cos != nullptr) {
+    // every row the call touches must exist in the tables; pairs of columns need an even dk
+    if (a->dk % 2 != 0 || a->rope_q_offset < 0 || a->rope_k_offset < 0 ||
+        a->rope_q_offset + a->lq > a->rope_len || a->rope_k_offset + a->lk > a->rope_len)
+      return TPA_ERR_BAD_ARG;
+  }
   if (a->kernel < TPA_KERNEL_AUTO || a->kernel > TPA_KERNEL_DECODE) return TPA_ERR_BAD_ARG;
   if (a->heads > 65535 || a->batch > 65535) return TPA_ERR_UNSUPPORTED;
   if (a->dk > 256 || a->dv > 256) return TPA_ERR_UNSUPPORTED;
@@ -56,11 +70,29 @@ static int validate(const TpaFwdArgs* a, Params* p) {
   p->sm_scale = a->sm_scale; p->flags = a->flags;
   p->q_offset = a->q_offset; p->k_offset = a->k_offset;
   p->status = nullptr;
+  p->kv_parts = parts;
+  p->part_len = a->lk / parts;
+  p->k_part_stride = a->k_part_stride; p->v_part_stride = a->v_part_stride;
+  p->kseg_part_stride = a->kv_segment_part_stride;
+  p->per_part = (a->flags & TPA_FLAG_CAUSAL_PER_PART) != 0;
+  p->window = a->window;
+  p->dilation = a->dilation > 1 ? a->dilation : 1;
+  p->rope_cos = a->rope_cos; p->rope_sin = a->rope_sin; p->rope_len = a->rope_len;
+  p->rope_q_offset = a->rope_q_offset; p->rope_k_offset = a->rope_k_offset;
   return TPA_OK;
 }
 
+// Extensions only some kernels implement (parts, window / dilation, rotary embedding).
+static bool has_extensions(const Params& p) {
+  return p.kv_parts > 1 || p.has_window() || p.rope_cos != nullptr;
+}
+
 static int choose(const TpaFwdArgs* a, const Params& p, int* kernel) {
-  const bool dec = decode_supported(p);
+  const bool ext = has_extensions(p);
+  if (ext && (a->kernel == TPA_KERNEL_DECODE || a->kernel == TPA_KERNEL_SM100_FUSED)) return TPA_ERR_KERNEL_FORCED;
+  // the generic kernel walks keys 64 at a time, the tensor-core kernel 128: parts must be whole tiles
+  if (p.kv_parts > 1 && p.part_len % 64 != 0) return TPA_ERR_UNSUPPORTED;
+  const bool dec = !ext && decode_supported(p);
   if (a->kernel == TPA_KERNEL_DECODE && !dec) return TPA_ERR_KERNEL_FORCED;
   if (a->kernel == TPA_KERNEL_DECODE || (a->kernel == TPA_KERNEL_AUTO && decode_preferred(p))) {
     *kernel = TPA_KERNEL_DECODE;
@@ -99,6 +131,7 @@ static int validate_bwd(const TpaBwdArgs* a, BwdParams* bp) {
   int st = validate(&a->fwd, &bp->f);
   if (st != TPA_OK) return st;
   if (a->fwd.flags & ~(uint32_t)TPA_FLAG_CAUSAL) return TPA_ERR_BAD_ARG;
+  if (has_extensions(bp->f)) return TPA_ERR_UNSUPPORTED;  // parts, windows and rotary embedding are forward only
   if (a->fwd.o == nullptr || a->fwd.lse == nullptr || a->d_o == nullptr || a->dq == nullptr ||
       a->dk == nullptr || a->dv == nullptr)
     return TPA_ERR_BAD_ARG;

@@ -25,7 +25,63 @@ struct Params {
   uint32_t flags;
   int64_t q_offset, k_offset;
   uint32_t* status;  // device status block {flag, where, block, spins} or nullptr
+  // keys in parts (kv_parts >= 1, part_len = lk / kv_parts); strides in elements
+  int kv_parts, part_len;
+  int64_t k_part_stride, v_part_stride, kseg_part_stride;
+  bool per_part;      // causal / window comparison on the key's index inside its part
+  int window, dilation;  // window 0 = none; dilation >= 1
+  const float* rope_cos;
+  const float* rope_sin;
+  int rope_len;
+  int64_t rope_q_offset, rope_k_offset;
+
+  __host__ __device__ __forceinline__ bool has_window() const { return window > 0 || dilation > 1; }
 };
+
+// Masking rule shared by the kernels.  With diff = (query row + q_offset) - (key position + k_offset):
+// causal keeps diff >= 0; a window keeps |diff| < window * dilation; dilation D keeps diff % D == 0.
+// The kernels take the 64-bit difference once per thread and tile (first column of the thread),
+// clamp it to +-2^30 -- beyond that every rule has the same answer as at the bound, since
+// window * dilation <= 2^29 is enforced on entry -- and work in 32 bits per element.  The
+// remainder for dilation is taken from the exact 64-bit value, once, as `phase`.
+struct MaskRule {
+  bool causal, windowed, dilated;
+  int span;      // window * dilation
+  int dilation;
+};
+__host__ __device__ __forceinline__ MaskRule mask_rule(const Params& p) {
+  return MaskRule{(p.flags & TPA_FLAG_CAUSAL) != 0, p.window > 0, p.dilation > 1,
+                  (int)((int64_t)p.window * p.dilation), p.dilation};
+}
+__host__ __device__ __forceinline__ int clamp_diff(int64_t d) {
+  const int64_t lim = (int64_t)1 << 30;
+  return (int)(d > lim ? lim : (d < -lim ? -lim : d));
+}
+__host__ __device__ __forceinline__ int diff_phase(int64_t d, int dilation) {
+  const int r = (int)(d % dilation);
+  return r < 0 ? r + dilation : r;
+}
+// causal and window part of the rule for one element, diff = clamped first-column diff - column
+__host__ __device__ __forceinline__ bool keep_diff32(const MaskRule& m, int diff) {
+  bool keep = !m.causal || diff >= 0;
+  if (m.windowed) keep = keep && diff < m.span && -diff < m.span;
+  return keep;
+}
+// dilation part: column `idx` of a thread whose first column has remainder `phase`
+__host__ __device__ __forceinline__ bool keep_dilated(const MaskRule& m, int phase, int idx) {
+  return (phase - idx) % m.dilation == 0;
+}
+
+// Element offset of key row `kc` of a K or V factor (parts, then rows inside the part).
+__host__ __device__ __forceinline__ int64_t key_row_offset(const Params& p, const TpaFactor& f, int64_t part_stride,
+                                                           int kc) {
+  const int part = kc / p.part_len;
+  return (int64_t)part * part_stride + (int64_t)(kc - part * p.part_len) * f.stride[1];
+}
+__host__ __device__ __forceinline__ int64_t kseg_offset(const Params& p, int kc) {
+  const int part = kc / p.part_len;
+  return (int64_t)part * p.kseg_part_stride + (kc - part * p.part_len);
+}
 
 // Device-side view of one backward call.
 struct BwdParams {

@@ -51,6 +51,20 @@ __device__ __forceinline__ void rebuild_tile(float* dst, int ld, int rows, int r
   }
 }
 
+// Rotary embedding of a rebuilt tile in shared memory: columns (2c, 2c + 1) of row r turn by the
+// angle in table row pos0 + r.  Rows at or past row_end hold zeros and stay zero.
+__device__ __forceinline__ void rope_tile(float* dst, int ld, int rows, int cols, const float* cosr,
+                                          const float* sinr, int64_t pos0, int tid) {
+  const int half = cols / 2;
+  for (int idx = tid; idx < rows * half; idx += SIMT_THREADS) {
+    const int r = idx / half, c = idx - r * half;
+    const float cs = cosr[(pos0 + r) * half + c], sn = sinr[(pos0 + r) * half + c];
+    const float x = dst[r * ld + 2 * c], y = dst[r * ld + 2 * c + 1];
+    dst[r * ld + 2 * c] = x * cs - y * sn;
+    dst[r * ld + 2 * c + 1] = x * sn + y * cs;
+  }
+}
+
 template <typename T, int JJ>
 __global__ void __launch_bounds__(SIMT_THREADS)
 tpa_fwd_simt_kernel(const Params p) {
@@ -82,6 +96,11 @@ tpa_fwd_simt_kernel(const Params p) {
 
   rebuild_tile<T>(Qs, ldk, SIMT_BQ, q0, p.lq, dk, qa, p.qa.stride, qb, p.qb.stride, p.rank_q, h,
                   1.f / (float)p.rank_q, tid);
+  const bool rope = p.rope_cos != nullptr;
+  if (rope) {
+    __syncthreads();
+    rope_tile(Qs, ldk, min(SIMT_BQ, p.lq - q0), dk, p.rope_cos, p.rope_sin, q0 + p.rope_q_offset, tid);
+  }
 
   float m[SIMT_RPW], l[SIMT_RPW], acc[SIMT_RPW][JJ];
   int qseg[SIMT_RPW];
@@ -119,16 +138,43 @@ tpa_fwd_simt_kernel(const Params p) {
     else if (kmax / SIMT_BK + 1 < n_tiles) n_tiles = (int)(kmax / SIMT_BK) + 1;
   }
 
+  // (with the comparison on part-local key indices the bound above does not apply: every part
+  // has visible tiles, and the per-tile test below skips the others)
+  if (p.per_part) n_tiles = (p.lk + SIMT_BK - 1) / SIMT_BK;
+  const MaskRule rule = mask_rule(p);
+  const bool positional = causal || rule.windowed;
+  const int64_t q_lo = (int64_t)q0 + p.q_offset, q_hi = q_lo + SIMT_BQ - 1;
+  const int64_t span = rule.span;
+
   const float inv_rk = 1.f / (float)p.rank_k;
   for (int tile = 0; tile < n_tiles; ++tile) {
     const int k0 = tile * SIMT_BK;
+    // a tile (it lies in one part: parts are multiples of the tile) no row of the block can see
+    const int64_t kp_lo = (int64_t)(p.per_part ? k0 % p.part_len : k0) + p.k_offset, kp_hi = kp_lo + SIMT_BK - 1;
+    if (causal && kp_lo > q_hi) continue;
+    if (p.window > 0 && (q_lo - kp_hi >= span || (!causal && kp_lo - q_hi >= span))) continue;
+    const int part = k0 / p.part_len;
+    const int64_t koff = (int64_t)part * p.k_part_stride - (int64_t)part * p.part_len * p.ka.stride[1];
+    const int64_t voff = (int64_t)part * p.v_part_stride - (int64_t)part * p.part_len * p.va.stride[1];
     __syncthreads();  // everyone is done with the previous K/V/P tiles (and Q is written)
-    rebuild_tile<T>(Ks, ldk, SIMT_BK, k0, p.lk, dk, ka, p.ka.stride, kb, p.kb.stride, p.rank_k, h,
+    rebuild_tile<T>(Ks, ldk, SIMT_BK, k0, p.lk, dk, ka + koff, p.ka.stride, kb + koff, p.kb.stride, p.rank_k, h,
                     inv_rk, tid);
-    rebuild_tile<T>(Vs, ldv, SIMT_BK, k0, p.lk, dv, va, p.va.stride, vb, p.vb.stride, p.rank_k, h,
+    rebuild_tile<T>(Vs, ldv, SIMT_BK, k0, p.lk, dv, va + voff, p.va.stride, vb + voff, p.vb.stride, p.rank_k, h,
                     inv_rk, tid);
-    if (has_seg && tid < SIMT_BK) ksegs[tid] = (k0 + tid < p.lk) ? kseg_g[k0 + tid] : 0;
+    if (has_seg && tid < SIMT_BK) ksegs[tid] = (k0 + tid < p.lk) ? kseg_g[kseg_offset(p, k0 + tid)] : 0;
+    if (rope) {
+      __syncthreads();
+      rope_tile(Ks, ldk, min(SIMT_BK, p.lk - k0), dk, p.rope_cos, p.rope_sin, k0 + p.rope_k_offset, tid);
+    }
     __syncthreads();
+
+    // row position minus the position of the tile's first key, per row of this warp (see MaskRule)
+    int rel[SIMT_RPW], phase[SIMT_RPW];
+#pragma unroll
+    for (int i = 0; i < SIMT_RPW; ++i) {
+      rel[i] = clamp_diff(qpos[i] - kp_lo);
+      phase[i] = rule.dilated ? diff_phase(qpos[i] - kp_lo, rule.dilation) : 0;
+    }
 
     // logits: this lane owns key columns `lane` and `lane + 32` of the 4 rows of its warp
     float s[SIMT_RPW][2];
@@ -155,7 +201,8 @@ tpa_fwd_simt_kernel(const Params p) {
       for (int c = 0; c < 2; ++c) {
         const int kc = k0 + lane + 32 * c;
         keep[c] = kc < p.lk;
-        if (causal) keep[c] = keep[c] && (qpos[i] >= (int64_t)kc + p.k_offset);
+        if (positional) keep[c] = keep[c] && keep_diff32(rule, rel[i] - (lane + 32 * c));
+        if (rule.dilated) keep[c] = keep[c] && keep_dilated(rule, phase[i], lane + 32 * c);
         if (has_seg) keep[c] = keep[c] && (qseg[i] == ksegs[lane + 32 * c]);
         x[c] = keep[c] ? s[i][c] * p.sm_scale : -CUDART_INF_F;
       }

@@ -83,6 +83,13 @@ struct Barriers {
   float xch[2][2][2][kUnitRows];
 };
 
+#ifdef TPA_DEBUG_CYCLES
+// tuning builds only: thread-private slots of the status block (words 8..63) get clock values
+#define TPA_TICK(slot) do { if (dbg_on && (slot) < 56) p.status[8 + (slot)] = (uint32_t)clock64(); } while (0)
+#else
+#define TPA_TICK(slot) do { } while (0)
+#endif
+
 struct Waiter {
   Barriers* bars;
   uint32_t* status;
@@ -130,6 +137,24 @@ __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+// Key tiles are walked, and staged, in an order of their own.  With the causal comparison on
+// part-local indices (TPA_FLAG_CAUSAL_PER_PART) the tiles with the same index inside their parts
+// are adjacent: walk index = local tile * parts + part.  Every row block then sees a prefix of the
+// walk, as it does for one part, and nothing else in the tile loops changes.  Otherwise the walk
+// is the key array's own order.
+__device__ __forceinline__ int walk_group(const Params& p) { return p.per_part ? p.kv_parts : 1; }
+// walk index -> tile index in the key array
+__device__ __forceinline__ int walk_to_key_tile(const Params& p, int kt) {
+  if (!p.per_part) return kt;
+  return (kt % p.kv_parts) * (p.part_len / kTileKv) + kt / p.kv_parts;
+}
+// tile index in the key array -> walk index
+__device__ __forceinline__ int key_tile_to_walk(const Params& p, int tile) {
+  if (!p.per_part) return tile;
+  const int tps = p.part_len / kTileKv;
+  return (tile % tps) * p.kv_parts + tile / tps;
 }
 
 // dst tile rows [0,128): dst[row][:] = scale * sum_r a[row0+row, r] * b[row0+row, r, :], bf16,
@@ -193,21 +218,34 @@ __global__ void __launch_bounds__(256) tpa_stage_tiles_kernel(const Params p, ui
   uint8_t* ws;
   int rank, ntiles, length;
   float scale;
+  bool is_q = false, is_v = false;
   if (tile < nq) {
-    fa = &p.qa; fb = &p.qb; ws = ws_q; rank = p.rank_q; ntiles = nq; scale = qscale; length = p.lq;
+    fa = &p.qa; fb = &p.qb; ws = ws_q; rank = p.rank_q; ntiles = nq; scale = qscale; length = p.lq; is_q = true;
   } else if (tile < nq + nk) {
     tile -= nq;
     fa = &p.ka; fb = &p.kb; ws = ws_k; rank = p.rank_k; ntiles = nk; scale = 1.f; length = p.lk;
   } else {
     tile -= nq + nk;
-    fa = &p.va; fb = &p.vb; ws = ws_v; rank = p.rank_k; ntiles = nk; scale = 1.f; length = p.lk;
+    fa = &p.va; fb = &p.vb; ws = ws_v; rank = p.rank_k; ntiles = nk; scale = 1.f; length = p.lk; is_v = true;
   }
   const int hg = blockIdx.x, batch = blockIdx.z;
-  const __nv_bfloat16* a = static_cast<const __nv_bfloat16*>(fa->ptr) + batch * fa->stride[0] + hg * 8;
-  const __nv_bfloat16* b = static_cast<const __nv_bfloat16*>(fb->ptr) + batch * fb->stride[0];
+  // keys in parts: rows of this tile start part * part_stride into the factor (the tile lies in
+  // one part), and its image goes to its place in the walk order
+  int slot = tile;
+  int64_t part_off = 0;
+  if (!is_q && p.kv_parts > 1) {
+    const int part = tile / (p.part_len / kTileKv);
+    part_off = (int64_t)part * (is_v ? p.v_part_stride : p.k_part_stride) - (int64_t)part * p.part_len * fa->stride[1];
+    slot = key_tile_to_walk(p, tile);
+  }
+  const __nv_bfloat16* a = static_cast<const __nv_bfloat16*>(fa->ptr) + batch * fa->stride[0] + part_off + hg * 8;
+  const __nv_bfloat16* b = static_cast<const __nv_bfloat16*>(fb->ptr) + batch * fb->stride[0] + part_off;
   const int chunk = threadIdx.x % CH, r_in = threadIdx.x / CH;
-  uint8_t* out0 = ws + (((int64_t)batch * p.heads + hg * 8) * ntiles + tile) * kTileBytes +
+  uint8_t* out0 = ws + (((int64_t)batch * p.heads + hg * 8) * ntiles + slot) * kTileBytes +
                   (chunk >> 3) * (kUnitRows * 128);
+  // rotary embedding of Q and K rows: table row = row index + offset
+  const bool rope = p.rope_cos != nullptr && !is_v;
+  const int64_t rope_off = is_q ? p.rope_q_offset : p.rope_k_offset;
   for (int row = r_in; row < kUnitRows; row += 256 / CH) {
     const int64_t g = (int64_t)tile * kUnitRows + row;
     const __nv_bfloat16* ap = a + g * fa->stride[1];
@@ -246,6 +284,20 @@ __global__ void __launch_bounds__(256) tpa_stage_tiles_kernel(const Params p, ui
           }
         }
       }
+    }
+    if (rope && g < length) {
+      // this thread's 8 columns are 4 whole pairs; the rotation is the same for every head
+      const float4 cs = __ldg(reinterpret_cast<const float4*>(p.rope_cos + (g + rope_off) * (D / 2) + chunk * 4));
+      const float4 sn = __ldg(reinterpret_cast<const float4*>(p.rope_sin + (g + rope_off) * (D / 2) + chunk * 4));
+      const float c4[4] = {cs.x, cs.y, cs.z, cs.w}, s4[4] = {sn.x, sn.y, sn.z, sn.w};
+#pragma unroll
+      for (int h = 0; h < 8; ++h)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float x = acc[h][2 * e], y = acc[h][2 * e + 1];
+          acc[h][2 * e] = x * c4[e] - y * s4[e];
+          acc[h][2 * e + 1] = x * s4[e] + y * c4[e];
+        }
     }
     const uint32_t off = sw128_offset(row, chunk & 7);
 #pragma unroll
@@ -293,10 +345,11 @@ __global__ void __launch_bounds__(128) tpa_seg_ranges_kernel(const Params p, int
     lo[u] = min(min(red[0][2 * u], red[1][2 * u]), min(red[2][2 * u], red[3][2 * u]));
     hi[u] = max(max(red[0][2 * u + 1], red[1][2 * u + 1]), max(red[2][2 * u + 1], red[3][2 * u + 1]));
   }
-  for (int tile = t; tile < n_kv; tile += 128) {
-    const int4* src = reinterpret_cast<const int4*>(ks + (int64_t)tile * kTileKv);
+  for (int tile = t; tile < n_kv; tile += 128) {  // `tile` counts in walk order
+    const int key_tile = walk_to_key_tile(p, tile);
+    const int4* src = reinterpret_cast<const int4*>(ks + kseg_offset(p, key_tile * kTileKv));
     int kmin = INT_MAX, kmax = INT_MIN;
-    const int n4 = min(kTileKv, p.lk - tile * kTileKv) / 4;  // lk % 4 == 0
+    const int n4 = min(kTileKv, p.lk - key_tile * kTileKv) / 4;  // lk % 4 == 0
     for (int i = 0; i < n4; ++i) {
       const int4 v = __ldg(src + i);
       kmin = min(kmin, min(min(v.x, v.y), min(v.z, v.w)));
@@ -317,7 +370,10 @@ __global__ void __launch_bounds__(128) tpa_seg_ranges_kernel(const Params p, int
   }
 }
 
-template <int D, bool STAGED>
+// MODE 0: the reference's call.  1: key parts (a ring in one call).  2: windows / dilation as well.
+// The plain instantiation keeps none of the others' arithmetic (one position per key, the walk is
+// the key array's order), and parts alone cost one counter per tile.
+template <int D, bool STAGED, int MODE>
 __global__ void __launch_bounds__(Roles<STAGED>::kThreads, 1)
 tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, const uint8_t* ws_v,
                      const int pairs, const int group, const int4* seg_ranges) {
@@ -352,27 +408,37 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
   const bool store_state = (p.flags & TPA_FLAG_STATE_STORE) != 0;
 
   // number of key tiles each unit can see (tpa/tpa.py:427-431, with global offsets)
+  // Tiles are counted in walk order (see walk_group): G tiles share one position range.
   const int n_kv = (p.lk + kTileKv - 1) / kTileKv;
+  constexpr bool kParts = MODE >= 1;
+  const int G = kParts ? walk_group(p) : 1;
+  const int n_loc = n_kv / G;
+  const bool windowed = MODE == 2 && p.window > 0;
+  const bool dilated = MODE == 2 && p.dilation > 1;
+  const int span = windowed ? p.window * p.dilation : 0;
   int n_vis[2];
 #pragma unroll
   for (int u = 0; u < 2; ++u) {
     const int q0u = q0 + u * kUnitRows;
-    if (q0u >= p.lq) {
-      n_vis[u] = 0;
-    } else if (causal) {
-      const int64_t last = (int64_t)q0u + kUnitRows - 1 + p.q_offset - p.k_offset;
-      n_vis[u] = last < 0 ? 0 : (int)min((int64_t)n_kv, last / kTileKv + 1);
-    } else {
-      n_vis[u] = n_kv;
-    }
+    int hi = q0u >= p.lq ? 0 : n_loc;
+    const int64_t last = (int64_t)q0u + kUnitRows - 1 + p.q_offset - p.k_offset;  // position of the last row, key-relative
+    if (hi > 0 && causal) hi = last < 0 ? 0 : (int)min((int64_t)n_loc, last / kTileKv + 1);
+    if (hi > 0 && windowed && !causal)  // keys at most span - 1 ahead of the last row
+      hi = last + span - 1 < 0 ? 0 : (int)min((int64_t)hi, (last + span - 1) / kTileKv + 1);
+    n_vis[u] = hi * G;
   }
+  // A window starts the walk at the tile of the first key the block's first row can see.
   // With segment ids the walk starts at the first tile any row of the block can match and ends
   // where the unit's last match is (tpa_seg_ranges_kernel).  From here on tiles are counted
-  // from j0: tile j of the loops below is key tile j0 + j.
+  // from j0: tile j of the loops below is walk tile j0 + j.
   int j0 = 0;
+  if (windowed) {
+    const int64_t first = (int64_t)q0 + p.q_offset - p.k_offset - (span - 1);
+    if (first > 0) j0 = (int)min((int64_t)n_loc, first / kTileKv) * G;
+  }
   if (seg_ranges != nullptr) {
     const int4 r = seg_ranges[(int64_t)batch * pairs + pair];
-    j0 = r.x;
+    j0 = max(j0, r.x);
     n_vis[0] = min(n_vis[0], r.y);
     n_vis[1] = min(n_vis[1], r.z);
   }
@@ -496,12 +562,31 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
       loaded = true;
     }
 
+#ifdef TPA_DEBUG_CYCLES
+    const bool dbg_on = blockIdx.x == TPA_DEBUG_CYCLES && warp == 8 && lane == 0 && p.status != nullptr;  // unit 1, half 0
+    TPA_TICK(0);
+#endif
+    // position of walk tile j0 + j: tile (j0 + j) / G of its part, kept by counting
+    int pos_tile = kParts ? j0 / G : j0, pos_cnt = kParts ? j0 % G : 0;
     for (int j = 0; j < n_u; ++j) {
+      TPA_TICK(1 + 3 * j);
       wait(&bars->s_full[u], j & 1, 0x100 + u);
       tc_fence_after();
-      const int k0 = (j0 + j) * kTileKv + half * 64;  // first key of this thread's columns
-      const bool diag = causal && ((int64_t)k0 + 63 + p.k_offset > (int64_t)q0u + p.q_offset);
-      const bool tail = k0 + 63 >= p.lk;  // columns past the last key (zero rows in the staged tile)
+      TPA_TICK(2 + 3 * j);
+      // this thread's 64 columns: index of the first in the walk (= in the key array unless the
+      // walk is interleaved, and then no tile is ragged) and its position in the comparisons
+      const int k0 = (j0 + j) * kTileKv + half * 64;
+      const int64_t kp0 = (int64_t)pos_tile * kTileKv + half * 64 + p.k_offset;
+      if (kParts) {
+        if (++pos_cnt == G) { pos_cnt = 0; ++pos_tile; }
+      } else {
+        ++pos_tile;
+      }
+      const int64_t q_lo = (int64_t)q0u + p.q_offset;
+      // does any (row of the unit, column of this half) pair fall to the causal or window rule?
+      const bool edge = (causal && kp0 + 63 > q_lo) ||
+                        (windowed && (q_lo + kUnitRows - 1 - kp0 >= span || (!causal && kp0 + 63 - q_lo >= span)));
+      const bool tail = G == 1 && k0 + 63 >= p.lk;  // columns past the last key (zero rows in the staged tile)
       // Segment ids: when every key of these 64 columns and every row of this warp carry the
       // same id, nothing is masked and the element-wise test is skipped (warp-uniform).
       const int32_t* ks = bars->kseg[j & 1] + half * 64;
@@ -513,16 +598,39 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
         const int kmax = __reduce_max_sync(0xffffffffu, max(k2.x, k2.y));
         seg_mask = !__all_sync(0xffffffffu, kmin == kmax && qseg == kmin);
       }
-      const bool masked = diag || seg_mask || tail;
+      const bool masked = edge || seg_mask || tail || dilated;
+      // The causal rule, the window and the end of the keys leave this thread a range [lo, hi) of
+      // its 64 columns.  rel = its row's position minus its first column's, clamped to 32 bits
+      // (see MaskRule); column c is kept by the causal rule iff c <= rel, by the window iff
+      // |rel - c| < span.
+      int lo = 0, hi = 64, phase = 0;
+      if (masked) {
+        const int rel = clamp_diff(qpos - kp0);
+        if (tail) hi = min(hi, p.lk - k0);
+        if (edge) {
+          if (causal) hi = min(hi, rel + 1);
+          else if (windowed) hi = min(hi, rel + span);
+          if (windowed) lo = max(lo, rel - span + 1);
+        }
+        if (dilated) phase = diff_phase(qpos - kp0, p.dilation);
+      }
+      const unsigned width = hi > lo ? (unsigned)(hi - lo) : 0u;
 
       auto mask_chunk = [&](uint32_t(&r)[32], int c) {
+        if (edge || tail) {
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const int kc = k0 + c * 32 + e;
-          bool keep = kc < p.lk;
-          if (diag) keep = keep && qpos >= (int64_t)kc + p.k_offset;
-          if (seg_mask) keep = keep && (qseg == ks[c * 32 + e]);
-          if (!keep) r[e] = 0xff800000u;  // -inf
+          for (int e = 0; e < 32; ++e)
+            if ((unsigned)(c * 32 + e - lo) >= width) r[e] = 0xff800000u;  // -inf
+        }
+        if (seg_mask) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e)
+            if (qseg != ks[c * 32 + e]) r[e] = 0xff800000u;
+        }
+        if (dilated) {  // a loop of its own: the remainders are only computed when asked for
+#pragma unroll
+          for (int e = 0; e < 32; ++e)
+            if ((phase - (c * 32 + e)) % p.dilation != 0) r[e] = 0xff800000u;
         }
       };
       // p = 2^(s - reference maximum) for one 32-column chunk, packed to bf16, plus the row
@@ -632,6 +740,7 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->p_ready[u]);
+      TPA_TICK(3 + 3 * j);
     }
 
     // ---- epilogue: o = acc / (l * R_k), lse = ln2 * (m + log2 l); NaN / -inf for empty rows
@@ -640,6 +749,7 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
         wait(&bars->o_done[u], (n_u - 1) & 1, 0x300 + u);
         tc_fence_after();
       }
+      TPA_TICK(40);
       // row sum = this half's share + the partner's
       float* xch = bars->xch[n_u & 1][u][0];
       xch[half * kUnitRows + row] = l;
@@ -929,11 +1039,12 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
         bulk_g2s(sK + s * kTileBytes, gk + (int64_t)(j0 + j) * kTileBytes, kTileBytes, &bars->k_full[s]);
         if (j >= 2) wait(&bars->v_empty[s], ((j >> 1) - 1) & 1, 0x500);
         // ids of a ragged last tile: only the keys that exist (lk % 4 == 0, so 16-byte multiples)
-        const int n_ids = min(kTileKv, p.lk - (j0 + j) * kTileKv);
+        const int key_tile = walk_to_key_tile(p, j0 + j);
+        const int n_ids = min(kTileKv, p.lk - key_tile * kTileKv);
         mbar_arrive_expect_tx(&bars->v_full[s], kTileBytes + (has_seg ? n_ids * 4 : 0));
         bulk_g2s(sV + s * kTileBytes, gv + (int64_t)(j0 + j) * kTileBytes, kTileBytes, &bars->v_full[s]);
         if (has_seg)
-          bulk_g2s(bars->kseg[s], p.kv_seg + (int64_t)batch * p.kv_seg_bstride + (int64_t)(j0 + j) * kTileKv,
+          bulk_g2s(bars->kseg[s], p.kv_seg + (int64_t)batch * p.kv_seg_bstride + kseg_offset(p, key_tile * kTileKv),
                    n_ids * 4, &bars->v_full[s]);
       }
     }
@@ -1076,11 +1187,11 @@ inline size_t ceil128(size_t x) { return (x + 127) / 128 * 128; }  // whole tile
 inline size_t staged_q_bytes(const Params& p) { return align256((size_t)p.batch * p.heads * ceil128(p.lq) * p.dk * 2); }
 inline size_t staged_kv_bytes(const Params& p) { return align256((size_t)p.batch * p.heads * ceil128(p.lk) * p.dk * 2); }
 
-template <int D, bool STAGED>
+template <int D, bool STAGED, int MODE>
 cudaError_t launch_attn(const Params& p, const uint8_t* wq, const uint8_t* wk, const uint8_t* wv,
                         dim3 grid, int pairs, int group, const int4* seg_ranges, size_t smem,
                         cudaStream_t stream) {
-  auto kern = tpa_fwd_sm100_kernel<D, STAGED>;
+  auto kern = tpa_fwd_sm100_kernel<D, STAGED, MODE>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   kern<<<grid, Roles<STAGED>::kThreads, smem, stream>>>(p, wq, wk, wv, pairs, group, seg_ranges);
@@ -1216,6 +1327,10 @@ bool sm100_supported(const Params& p) {
   // masked.  Key ids travel as 16-byte multiples.
   if (p.kv_seg != nullptr && p.lk % 4 != 0) return false;
   if (p.heads % 8 != 0) return false;
+  if (p.kv_parts > 1 && p.part_len % kTileKv != 0) return false;  // a key tile lies in one part
+  if (p.kv_parts > 1 && (p.k_part_stride % 8 != 0 || p.v_part_stride % 8 != 0)) return false;
+  if (p.kv_parts > 1 && p.kv_seg != nullptr && p.kseg_part_stride % 4 != 0) return false;
+  if (p.rope_cos != nullptr && (!aligned16(p.rope_cos) || !aligned16(p.rope_sin))) return false;
   // factors are read with 16-byte loads; output rows are written with them
   if (!factor_vec_ok(p.qa) || !factor_vec_ok(p.ka) || !factor_vec_ok(p.va)) return false;
   if (!factor_vec_ok(p.qb) || !factor_vec_ok(p.kb) || !factor_vec_ok(p.vb)) return false;
@@ -1290,7 +1405,8 @@ cudaError_t launch_sm100(const Params& p, int variant, void* workspace, TpaKerne
     info->grid[1] = grid.y;
     info->grid[2] = grid.z;
     info->smem_bytes = (int)smem;
-    info->launches = (staged ? 2 : 1) + (p.q_seg != nullptr ? 1 : 0) + (splits > 1 ? 1 : 0);
+    const bool stage_nothing = (p.flags & TPA_FLAG_REUSE_STAGED_Q) && (p.flags & TPA_FLAG_REUSE_STAGED_KV);
+    info->launches = (staged && !stage_nothing ? 2 : 1) + (p.q_seg != nullptr ? 1 : 0) + (splits > 1 ? 1 : 0);
   }
   if (dry_run) return cudaSuccess;
   cudaError_t e;
@@ -1321,20 +1437,32 @@ cudaError_t launch_sm100(const Params& p, int variant, void* workspace, TpaKerne
     const float qscale = p.sm_scale * kLog2e / ((float)p.rank_q * (float)p.rank_k);
     // ring steps after the first keep the Q tiles the previous call staged in this workspace
     const int nq = (p.lq + kUnitRows - 1) / kUnitRows, nk = (p.lk + kTileKv - 1) / kTileKv;
+    // ... and two query chunks against the same gathered keys keep the K and V tiles
     const int first_tile = (p.flags & TPA_FLAG_REUSE_STAGED_Q) ? nq : 0;
-    dim3 sgrid(p.heads / 8, nq - first_tile + 2 * nk, p.batch);
-    if (p.dk == 128)
-      tpa_stage_tiles_kernel<128><<<sgrid, 256, 0, stream>>>(p, wq, wk, wv, qscale, first_tile);
-    else
-      tpa_stage_tiles_kernel<64><<<sgrid, 256, 0, stream>>>(p, wq, wk, wv, qscale, first_tile);
-    e = cudaGetLastError();
-    if (e != cudaSuccess) return e;
-    count_launch(1);
-    e = p.dk == 128 ? launch_attn<128, true>(pk, wq, wk, wv, grid, pairs, group, seg_ranges, smem, stream)
-                    : launch_attn<64, true>(pk, wq, wk, wv, grid, pairs, group, seg_ranges, smem, stream);
+    const int end_tile = (p.flags & TPA_FLAG_REUSE_STAGED_KV) ? nq : nq + 2 * nk;
+    if (end_tile > first_tile) {
+      dim3 sgrid(p.heads / 8, end_tile - first_tile, p.batch);
+      if (p.dk == 128)
+        tpa_stage_tiles_kernel<128><<<sgrid, 256, 0, stream>>>(p, wq, wk, wv, qscale, first_tile);
+      else
+        tpa_stage_tiles_kernel<64><<<sgrid, 256, 0, stream>>>(p, wq, wk, wv, qscale, first_tile);
+      e = cudaGetLastError();
+      if (e != cudaSuccess) return e;
+      count_launch(1);
+    }
+    const int mode = p.has_window() ? 2 : (p.kv_parts > 1 ? 1 : 0);
+    auto go = [&](auto kern_d) {
+      constexpr int DD = decltype(kern_d)::value;
+      switch (mode) {
+        case 0: return launch_attn<DD, true, 0>(pk, wq, wk, wv, grid, pairs, group, seg_ranges, smem, stream);
+        case 1: return launch_attn<DD, true, 1>(pk, wq, wk, wv, grid, pairs, group, seg_ranges, smem, stream);
+        default: return launch_attn<DD, true, 2>(pk, wq, wk, wv, grid, pairs, group, seg_ranges, smem, stream);
+      }
+    };
+    e = p.dk == 128 ? go(std::integral_constant<int, 128>{}) : go(std::integral_constant<int, 64>{});
   } else {
-    e = p.dk == 128 ? launch_attn<128, false>(pk, wq, wk, wv, grid, pairs, group, seg_ranges, smem, stream)
-                    : launch_attn<64, false>(pk, wq, wk, wv, grid, pairs, group, seg_ranges, smem, stream);
+    e = p.dk == 128 ? launch_attn<128, false, 0>(pk, wq, wk, wv, grid, pairs, group, seg_ranges, smem, stream)
+                    : launch_attn<64, false, 0>(pk, wq, wk, wv, grid, pairs, group, seg_ranges, smem, stream);
   }
   if (e != cudaSuccess) return e;
   count_launch(1);

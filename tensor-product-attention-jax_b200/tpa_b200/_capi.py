@@ -29,7 +29,8 @@ KERNELS = {"auto": KERNEL_AUTO, "simt": KERNEL_SIMT, "sm100": KERNEL_SM100,
            "sm100_fused": KERNEL_SM100_FUSED, "sm100_staged": KERNEL_SM100_STAGED, "decode": KERNEL_DECODE}
 KERNEL_NAMES = {KERNEL_SIMT: "simt", KERNEL_SM100_FUSED: "sm100_fused", KERNEL_SM100_STAGED: "sm100_staged",
                 KERNEL_DECODE: "decode"}
-FLAG_CAUSAL, FLAG_STATE_LOAD, FLAG_STATE_STORE, FLAG_REUSE_STAGED_Q = 1, 2, 4, 8
+FLAG_CAUSAL, FLAG_STATE_LOAD, FLAG_STATE_STORE, FLAG_REUSE_STAGED_Q, FLAG_CAUSAL_PER_PART = 1, 2, 4, 8, 16
+FLAG_REUSE_STAGED_KV = 32
 BWD_ACCUMULATE_DQ, BWD_ACCUMULATE_DKV = 1, 2
 
 # Every symbol include/tpa_b200.h declares.
@@ -86,6 +87,17 @@ class TpaFwdArgs(C.Structure):
         ("k_offset", C.c_int64),
         ("kernel", C.c_int32),
         ("reserved", C.c_int32),
+        ("kv_parts", C.c_int32),
+        ("window", C.c_int32),
+        ("dilation", C.c_int32),
+        ("rope_len", C.c_int32),
+        ("k_part_stride", C.c_int64),
+        ("v_part_stride", C.c_int64),
+        ("kv_segment_part_stride", C.c_int64),
+        ("rope_cos", C.c_void_p),
+        ("rope_sin", C.c_void_p),
+        ("rope_q_offset", C.c_int64),
+        ("rope_k_offset", C.c_int64),
     ]
 
 

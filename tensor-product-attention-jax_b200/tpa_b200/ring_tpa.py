@@ -196,6 +196,119 @@ def _ring_global_zigzag(q, k, v, qseg, kseg, group, size, rank, num_heads, sm_sc
     return out
 
 
+def _gather_ring(k, v, kseg, group, size, rank):
+    """All N K/V factor shards (and key ids) of the ring in one buffer per array, in sequence order:
+    [N, b, l, r, h + d] with slot s = the shard of rank s.
+
+    The same N - 1 neighbour hops as the scan of tpa/ring_tpa.py:69-106 -- at hop t every rank sends
+    on what it received at hop t - 1 and receives the shard that started t ranks behind it -- but
+    they do not wait for compute: all are queued at entry on the side stream, into their own
+    slots, and the attention then runs as one call over the N parts.  Only the compact factors
+    travel (tpa/ring_tpa.py:96).  Returns the buffers; on CUDA the current stream has been made
+    to wait for the last hop."""
+    kbuf = torch.empty((size,) + tuple(k.shape), dtype=k.dtype, device=k.device)
+    vbuf = torch.empty((size,) + tuple(v.shape), dtype=v.dtype, device=v.device)
+    sbuf = torch.empty((size,) + tuple(kseg.shape), dtype=kseg.dtype, device=kseg.device)
+    kbuf[rank].copy_(k)
+    vbuf[rank].copy_(v)
+    sbuf[rank].copy_(kseg)
+    if size == 1:
+        return kbuf, vbuf, sbuf
+    use_streams = k.is_cuda
+    if use_streams:
+        main = torch.cuda.current_stream(k.device)
+        side = _side_streams.get(k.device) or _side_streams.setdefault(k.device, torch.cuda.Stream(k.device))
+        side.wait_stream(main)  # the local shard is in its slot
+        ctx = torch.cuda.stream(side)
+    else:
+        import contextlib
+        ctx = contextlib.nullcontext()
+    with ctx:
+        for hop in range(1, size):
+            have, want = (rank - hop + 1) % size, (rank - hop) % size
+            reqs = _rotate_block([kbuf[have], vbuf[have], sbuf[have]], [kbuf[want], vbuf[want], sbuf[want]],
+                                 group, rank, size)
+            # the next hop forwards what this one receives
+            for r in reqs:
+                r.wait()
+    if use_streams:
+        main.wait_stream(side)
+    return kbuf, vbuf, sbuf
+
+
+def _device_parts(q, kbuf, vbuf, qs, sbuf, num_heads, sm_scale, causal, per_part, q_offset, out, lse, reuse_kv=False):
+    """One tpa_fwd call over gathered key parts (the whole ring for this rank's rows)."""
+    parts = kbuf.shape[0]
+    if parts == 1:  # one shard: the plain call
+        kbuf, vbuf, sbuf = kbuf[0], vbuf[0], sbuf[0]
+    return _tpa.fwd_device(q, kbuf, vbuf, num_heads, qs, sbuf, sm_scale, causal, q_offset=q_offset, out=out, lse=lse,
+                           want_lse=lse is not None, kv_parts=parts, per_part=per_part and parts > 1,
+                           reuse_staged_kv=reuse_kv)
+
+
+def _parts_supported(q, k):
+    """The one-call path needs key parts of whole 64-row tiles (128 on tensor cores, else the generic
+    kernel takes them) -- the same on every rank, because shapes are."""
+    return k.shape[1] % 64 == 0
+
+
+def _ring_one_call(q, k, v, qseg, kseg, group, size, rank, num_heads, sm_scale, causal, mask_mode, return_lse, parts_fn):
+    """Ring forward as gather + one attention call (two for the balanced global mask)."""
+    b, lq = q.shape[:2]
+    lk = k.shape[1]
+    dv = v.shape[-1] - num_heads
+    dev = q.device
+    want_lse = return_lse
+    if causal and mask_mode == "global" and size > 1 and lq == lk and lq % 2 == 0:
+        # balanced: this rank computes sequence chunks `rank` and 2N-1-rank (see _ring_global_zigzag);
+        # the keys are the gathered shards in sequence order, compared on global positions
+        c = lq // 2
+        mine, want = [2 * rank, 2 * rank + 1], [rank, 2 * size - 1 - rank]
+        holder = lambda ch: ch // 2  # noqa: E731
+        src = {ch: [q[:, i * c:(i + 1) * c], qseg[:, i * c:(i + 1) * c]] for i, ch in enumerate(mine)}
+        got = {ch: [torch.empty_like(t) for t in src[mine[0]]] for ch in want}
+        send = sorted(((_zigzag_owner(ch, size), ch) for ch in mine), key=lambda x: x[1])
+        recv = sorted(((holder(ch), ch) for ch in want), key=lambda x: x[1])
+        _exchange_chunks([(peer, src[ch]) for peer, ch in send], [(peer, got[ch]) for peer, ch in recv], group, rank)
+        kbuf, vbuf, sbuf = _gather_ring(k, v, kseg, group, size, rank)
+        outs, lses = [], []
+        n_parts = want[1] // 2 + 1  # shards the late chunk can see; the early one sees a prefix of them
+        for i, ch in enumerate((want[1], want[0])):  # late chunk first: it stages every tile both need
+            o_c = torch.empty((b, c, num_heads, dv), dtype=q.dtype, device=dev)
+            l_c = torch.empty((b, c, num_heads), dtype=torch.float32, device=dev) if want_lse else None
+            parts_fn(got[ch][0], kbuf[:n_parts], vbuf[:n_parts], got[ch][1], sbuf[:n_parts], num_heads, sm_scale, True,
+                     False, ch * c, o_c, l_c, i == 1)
+            outs.append(o_c)
+            lses.append(l_c)
+        out_l, out_e = outs
+        out = torch.empty((b, lq, num_heads, dv), dtype=q.dtype, device=dev)
+        lse = torch.empty((b, lq, num_heads), dtype=torch.float32, device=dev) if want_lse else None
+        pieces = [[out_e], [out_l]] if not want_lse else [[out_e, lses[1]], [out_l, lses[0]]]
+        dsts = [[out[:, :c]], [out[:, c:]]] if not want_lse else [[out[:, :c], lse[:, :c]], [out[:, c:], lse[:, c:]]]
+        back_send = sorted(((holder(ch), ch, ts) for ch, ts in zip(want, pieces)), key=lambda x: x[1])
+        back_recv = sorted(((_zigzag_owner(ch, size), ch, ts) for ch, ts in zip(mine, dsts)), key=lambda x: x[1])
+        tmp = [[torch.empty_like(t) for t in pieces[0]] for _ in back_recv]
+        _exchange_chunks([(peer, ts) for peer, _, ts in back_send], [(peer, t) for (peer, _, _), t in zip(back_recv, tmp)],
+                         group, rank)
+        for (_, _, ds), ts in zip(back_recv, tmp):
+            for d_, t in zip(ds, ts):
+                d_.copy_(t)
+        return (out, lse) if return_lse else out
+
+    kbuf, vbuf, sbuf = _gather_ring(k, v, kseg, group, size, rank)
+    out = torch.empty((b, lq, num_heads, dv), dtype=q.dtype, device=dev)
+    lse = torch.empty((b, lq, num_heads), dtype=torch.float32, device=dev) if want_lse else None
+    if causal and mask_mode == "global":
+        # contiguous shards, global positions: only the shards up to this rank's own are visible
+        n_parts = min(size, (rank * lq + lq - 1) // lk + 1)
+        parts_fn(q, kbuf[:n_parts], vbuf[:n_parts], qseg, sbuf[:n_parts], num_heads, sm_scale, True, False, rank * lq,
+                 out, lse, False)
+    else:
+        # the reference's ring: every visiting shard is masked on shard-local indices
+        parts_fn(q, kbuf, vbuf, qseg, sbuf, num_heads, sm_scale, causal, causal and size > 1, 0, out, lse, False)
+    return (out, lse) if return_lse else out
+
+
 def ring_tpa(
     q,
     k,
@@ -212,7 +325,9 @@ def ring_tpa(
     *,
     mask_mode: str = "reference_local",
     return_lse: bool = False,
+    one_call: bool | None = None,
     _block_fn=None,
+    _parts_fn=None,
 ):
     """Ring TPA forward on this rank's shard; arguments as tpa/ring_tpa.py:209-222.
 
@@ -224,6 +339,9 @@ def ring_tpa(
     shard; returns this rank's o[b, l/N, h, dv].  `impl="pallas"` is the reference's name
     for its kernel path and selects the CUDA kernels here; "xla" raises NotImplementedError
     and anything else ValueError, as in the reference (tpa/ring_tpa.py:237-273).
+
+    `one_call` (keyword only): None picks the one-call path whenever the shard length allows,
+    False forces the step-by-step scan with carried state.
 
     `mask_mode` (keyword only; not in the reference) chooses what `causal=True` means:
     "reference_local" masks on shard-local indices at every step, which is what the
@@ -238,12 +356,12 @@ def ring_tpa(
         raise ValueError(f"Unknown implementaiton: {impl}")
     if mask_mode not in MASK_MODES:
         raise ValueError(f"mask_mode must be one of {MASK_MODES}")
-    if (_block_fn is None and not return_lse and torch.is_grad_enabled()
+    if (_block_fn is None and _parts_fn is None and not return_lse and torch.is_grad_enabled()
             and (q.requires_grad or k.requires_grad or v.requires_grad)):
         return _RingTpaFunction.apply(q, k, v, q_segment_ids, kv_segment_ids, axis_name, num_heads,
                                       sm_scale, causal, mask_mode)
     block = _block_fn or _device_block
-    if _block_fn is None and not q.is_cuda:
+    if _block_fn is None and _parts_fn is None and not q.is_cuda:
         raise RuntimeError("tpa_b200 needs a CUDA device: there is no CPU implementation")
 
     group = _group_of(axis_name)
@@ -260,6 +378,17 @@ def ring_tpa(
         raise AssertionError(tuple(k.shape))
     kseg = kv_segment_ids.to(torch.int32).contiguous()
     qseg = q_segment_ids.to(torch.int32).contiguous()
+
+    # Default: all hops are queued at entry and the attention runs as ONE call over the gathered
+    # shards (no per-step launch, no carried state in HBM).  The step-by-step scan below remains
+    # for shard lengths the one-call kernels do not take and on request (`one_call=False`).
+    if one_call is None:
+        one_call = _parts_fn is not None or (_block_fn is None and _parts_supported(q, k))
+    if one_call:
+        if _parts_fn is None and not _parts_supported(q, k):
+            raise ValueError("one_call=True needs shard lengths that are multiples of 64")
+        return _ring_one_call(q, k.contiguous(), v.contiguous(), qseg, kseg, group, size, rank, num_heads, sm_scale,
+                              causal, mask_mode, return_lse, _parts_fn or _device_parts)
 
     # (the balanced exchange does not carry the LSE back; with return_lse the contiguous walk runs)
     if causal and mask_mode == "global" and size > 1 and lq == lk and lq % 2 == 0 and not return_lse:
@@ -470,7 +599,9 @@ def ring_tp_self_attention(
     *,
     mask_mode: str = "reference_local",
     gather_output: bool = False,
+    one_call: bool | None = None,
     _block_fn=None,
+    _parts_fn=None,
 ):
     """Ring self-attention over whole-sequence arrays; arguments as tpa/ring_tpa.py:290-304.
 
@@ -500,7 +631,8 @@ def ring_tp_self_attention(
     o = ring_tpa(
         q[:, sl], k[:, sl], v[:, sl], q_segment_ids[:, sl], kv_segment_ids[:, sl],
         axis_name=group, num_heads=num_heads, sm_scale=sm_scale, causal=causal, impl=impl,
-        debug=debug, interpret=interpret, mask_mode=mask_mode, _block_fn=_block_fn,
+        debug=debug, interpret=interpret, mask_mode=mask_mode, one_call=one_call, _block_fn=_block_fn,
+        _parts_fn=_parts_fn,
     )
     if not gather_output or size == 1:
         return o

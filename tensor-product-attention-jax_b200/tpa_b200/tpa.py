@@ -90,15 +90,24 @@ def _factor(x, col0):
     return f
 
 
-def _check_shapes(q, k, v, num_heads):
-    if q.ndim != 4 or k.ndim != 4 or v.ndim != 4:
+def _check_shapes(q, k, v, num_heads, kv_parts=1):
+    """(b, lq, lk, rank_q, rank_k, dk, dv).  With `kv_parts` > 1, k and v are
+    [parts, b, lk / parts, r, h + d] and lk counts the keys of all parts."""
+    if kv_parts > 1:
+        if k.ndim != 5 or v.ndim != 5 or k.shape[0] != kv_parts or v.shape[0] != kv_parts:
+            raise AssertionError(f"expected [{kv_parts}, b, l, r, h+d] key / value parts, got {k.shape}, {v.shape}")
+        kshape = (k.shape[1], kv_parts * k.shape[2]) + tuple(k.shape[3:])
+        vshape = (v.shape[1], kv_parts * v.shape[2]) + tuple(v.shape[3:])
+    else:
+        kshape, vshape = tuple(k.shape), tuple(v.shape)
+    if q.ndim != 4 or len(kshape) != 4 or len(vshape) != 4:
         raise AssertionError(f"expected [b, l, r, h+d] factors, got {q.shape}, {k.shape}, {v.shape}")
     b, lq, rank_q, h_dk = q.shape
-    _, lk, rank_k, h_dv = v.shape
+    _, lk, rank_k, h_dv = vshape
     # tpa/tpa.py:474-475: rank is read from v and k must match it
-    if tuple(k.shape) != (b, lk, rank_k, h_dk):
+    if kshape != (b, lk, rank_k, h_dk):
         raise AssertionError(tuple(k.shape))
-    if v.shape[0] != b:
+    if vshape[0] != b:
         raise AssertionError(tuple(v.shape))
     dk, dv = h_dk - num_heads, h_dv - num_heads
     if dk <= 0 or dv <= 0:
@@ -106,17 +115,26 @@ def _check_shapes(q, k, v, num_heads):
     return b, lq, lk, rank_q, rank_k, dk, dv
 
 
-def _fill_operands(a, q, k, v, num_heads, q_segment_ids, kv_segment_ids):
-    """Shapes, dtype, factor pointers and segment ids of a TpaFwdArgs; returns tensors to keep alive."""
-    b, lq, lk, rank_q, rank_k, dk, dv = _check_shapes(q, k, v, num_heads)
+def _fill_operands(a, q, k, v, num_heads, q_segment_ids, kv_segment_ids, kv_parts=1):
+    """Shapes, dtype, factor pointers and segment ids of a TpaFwdArgs; returns tensors to keep alive.
+
+    `kv_parts` > 1: k and v are [parts, b, lk / parts, r, h + d] (the shards of a ring gathered in
+    one buffer) and the key ids [parts, b, lk / parts]."""
+    b, lq, lk, rank_q, rank_k, dk, dv = _check_shapes(q, k, v, num_heads, kv_parts)
     a.struct_size = C.sizeof(_capi.TpaFwdArgs)
     a.dtype = _DTYPES[q.dtype]
     a.batch, a.lq, a.lk = b, lq, lk
     a.rank_q, a.rank_k = rank_q, rank_k
     a.heads, a.dk, a.dv = num_heads, dk, dv
     a.qa, a.qb = _factor(q, 0), _factor(q, num_heads)
-    a.ka, a.kb = _factor(k, 0), _factor(k, num_heads)
-    a.va, a.vb = _factor(v, 0), _factor(v, num_heads)
+    if kv_parts > 1:
+        a.ka, a.kb = _factor(k[0], 0), _factor(k[0], num_heads)
+        a.va, a.vb = _factor(v[0], 0), _factor(v[0], num_heads)
+        a.kv_parts = kv_parts
+        a.k_part_stride, a.v_part_stride = k.stride(0), v.stride(0)
+    else:
+        a.ka, a.kb = _factor(k, 0), _factor(k, num_heads)
+        a.va, a.vb = _factor(v, 0), _factor(v, num_heads)
     keep = []
     if q_segment_ids is not None:
         qs = q_segment_ids.to(device=q.device, dtype=torch.int32)
@@ -124,11 +142,17 @@ def _fill_operands(a, q, k, v, num_heads, q_segment_ids, kv_segment_ids):
         # a 1-D id row is shared by the whole batch (vmap in_axes None, tpa/tpa.py:155-161)
         qs = qs.contiguous()
         ks = ks.contiguous()
-        if qs.shape[-1] != lq or ks.shape[-1] != lk:
-            raise AssertionError((tuple(qs.shape), tuple(ks.shape)))
+        if kv_parts > 1:
+            if tuple(ks.shape) != (kv_parts, b, lk // kv_parts) or qs.shape[-1] != lq:
+                raise AssertionError((tuple(qs.shape), tuple(ks.shape)))
+            a.kv_segment_part_stride = ks.stride(0)
+            a.kv_segment_batch_stride = ks.stride(1)
+        else:
+            if qs.shape[-1] != lq or ks.shape[-1] != lk:
+                raise AssertionError((tuple(qs.shape), tuple(ks.shape)))
+            a.kv_segment_batch_stride = lk if ks.ndim == 2 else 0
         a.q_segment_ids, a.kv_segment_ids = qs.data_ptr(), ks.data_ptr()
         a.q_segment_batch_stride = lq if qs.ndim == 2 else 0
-        a.kv_segment_batch_stride = lk if ks.ndim == 2 else 0
         keep += [qs, ks]
     return keep
 
@@ -139,7 +163,7 @@ def _check_operands(q, k, v, q_segment_ids, kv_segment_ids):
     if q.dtype not in _DTYPES or k.dtype != q.dtype or v.dtype != q.dtype:
         raise NotImplementedError(f"dtype {q.dtype}/{k.dtype}/{v.dtype}: float32 or bfloat16 factors only")
     for x in (q, k, v):
-        if x.stride(3) != 1:
+        if x.stride(-1) != 1:
             raise ValueError("the last (h+d) axis of the factors must be contiguous")
     if (q_segment_ids is None) != (kv_segment_ids is None):
         raise AssertionError("segment ids must be given for both sides or neither")  # tpa/tpa.py:369-371
@@ -165,8 +189,24 @@ def fwd_device(
     want_lse=True,
     kernel="auto",
     reuse_staged_q=False,
+    reuse_staged_kv=False,
+    kv_parts=1,
+    per_part=False,
+    window=0,
+    dilation=1,
+    rope=None,
+    rope_q_offset=0,
+    rope_k_offset=0,
 ):
     """One tpa_fwd call on CUDA tensors; returns (o, lse_fp32).
+
+    Beyond the reference (all off by default): `kv_parts` > 1 takes k, v as
+    [parts, b, lk / parts, r, h + d] and key ids as [parts, b, lk / parts] -- the shards of a ring
+    gathered in one buffer -- and `per_part` compares positions on part-local key indices, which
+    makes one call equal the reference's whole ring scan (tpa/ring_tpa.py:60-112); `window` /
+    `dilation` are the sliding-window and dilated masks the reference plans
+    (tpa/ring_tpa.py:5-7); `rope=(cos, sin)` (fp32 [positions, dk / 2]) rotates the dim factors
+    of q and k, row i by table row i + rope_q_offset (keys: + rope_k_offset).
 
     `reuse_staged_q=True` promises that the previous call on this stream had the same q,
     shapes and scale (ring steps): the staged variant then keeps its Q tiles.
@@ -177,17 +217,32 @@ def fwd_device(
     Work is enqueued on the current stream of q's device.
     """
     _check_operands(q, k, v, q_segment_ids, kv_segment_ids)
-    b, lq, lk, rank_q, rank_k, dk, dv = _check_shapes(q, k, v, num_heads)
+    b, lq, lk, rank_q, rank_k, dk, dv = _check_shapes(q, k, v, num_heads, kv_parts)
 
     a = _capi.TpaFwdArgs()
-    keep = _fill_operands(a, q, k, v, num_heads, q_segment_ids, kv_segment_ids)
+    keep = _fill_operands(a, q, k, v, num_heads, q_segment_ids, kv_segment_ids, kv_parts)
     flags = _capi.FLAG_CAUSAL if causal else 0
+    if per_part:
+        flags |= _capi.FLAG_CAUSAL_PER_PART
+    a.window, a.dilation = int(window), int(dilation)
+    if rope is not None:
+        cos, sin = rope
+        for t in (cos, sin):
+            if t.dtype != torch.float32 or not t.is_contiguous() or t.device != q.device or t.shape != cos.shape:
+                raise ValueError("rope tables: two contiguous fp32 [positions, dk / 2] tensors on q's device")
+        if cos.ndim != 2 or cos.shape[1] * 2 != dk:
+            raise ValueError(f"rope tables must be [positions, {dk // 2}], got {tuple(cos.shape)}")
+        a.rope_cos, a.rope_sin, a.rope_len = cos.data_ptr(), sin.data_ptr(), cos.shape[0]
+        a.rope_q_offset, a.rope_k_offset = int(rope_q_offset), int(rope_k_offset)
+        keep += [cos, sin]
     if load_state:
         flags |= _capi.FLAG_STATE_LOAD
     if store_state:
         flags |= _capi.FLAG_STATE_STORE
     if reuse_staged_q:
         flags |= _capi.FLAG_REUSE_STAGED_Q
+    if reuse_staged_kv:
+        flags |= _capi.FLAG_REUSE_STAGED_KV
     if load_state or store_state:
         so, sl = state
         assert so.dtype == torch.float32 and sl.dtype == torch.float32
@@ -213,15 +268,20 @@ def fwd_device(
         nbytes = _capi.lib.tpa_fwd_workspace_bytes(C.byref(a))
         ws = _workspace(q.device, nbytes)
         stream = torch.cuda.current_stream(q.device).cuda_stream
-        # TPA_FLAG_REUSE_STAGED_Q is a promise about the workspace's contents; keep it only when the
-        # last call that staged into this very buffer had the same q operand, shapes and scale
-        # (another call on the stream, or a regrown buffer, silently voids the caller's promise)
-        sig = (q.data_ptr(), q._version, tuple(q.shape), tuple(q.stride()), q.dtype, tuple(k.shape), num_heads,
-               float(sm_scale), ws.data_ptr() if ws is not None else 0, nbytes, a.kernel)
+        # TPA_FLAG_REUSE_STAGED_Q / _KV are promises about the workspace's contents; keep them only
+        # when the last call that staged into this very buffer had the same operand, shapes and
+        # scale (another call on the stream, or a regrown buffer, silently voids the promise)
+        common = (tuple(q.shape), tuple(k.shape), q.dtype, num_heads, float(sm_scale), ws.data_ptr() if ws is not None else 0,
+                  nbytes, a.kernel, kv_parts, bool(per_part), None if rope is None else (rope[0].data_ptr(), rope_q_offset, rope_k_offset))
+        sig_q = common + (q.data_ptr(), q._version, tuple(q.stride()))
+        sig_kv = common + (k.data_ptr(), v.data_ptr(), tuple(k.stride()), tuple(v.stride()))
         key = (q.device, stream)
-        if reuse_staged_q and _staged_q.get(key) != sig:
+        last_q, last_kv = _staged_q.get(key, (None, None))
+        if reuse_staged_q and last_q != sig_q:
             a.flags &= ~_capi.FLAG_REUSE_STAGED_Q
-        _staged_q[key] = sig
+        if reuse_staged_kv and last_kv != sig_kv:
+            a.flags &= ~_capi.FLAG_REUSE_STAGED_KV
+        _staged_q[key] = (sig_q, sig_kv)
         st = _capi.lib.tpa_fwd(
             C.byref(a), ws.data_ptr() if ws is not None else None, nbytes, C.c_void_p(stream)
         )

@@ -26,7 +26,7 @@ def test_library_exports_every_declared_symbol():
     assert declared == set(_capi.EXPORTS), declared ^ set(_capi.EXPORTS)
     for name in declared:
         assert getattr(_capi.lib, name) is not None
-    assert _capi.lib.tpa_abi_version() == 1
+    assert _capi.lib.tpa_abi_version() == 2
 
 
 def _args(**over):

@@ -127,3 +127,60 @@ def test_backward_oracle_is_the_autograd_of_the_definition(causal, seg):
     want = torch.autograd.grad(loss, (tq, tk, tv))
     for got, w in zip(grads, want):
         np.testing.assert_allclose(got, w.numpy(), atol=2e-5, rtol=1e-4)
+
+
+# --------------------------------------------------------------------------- extensions of the definition
+
+
+def test_parts_with_part_local_mask_equal_the_ring_definition():
+    """One call whose keys are the N shards as N parts, compared on part-local indices, is the
+    reference's ring with causal=True (shard-local mask at every step, tpa/ring_tpa.py:73-91)."""
+    n, b, l, h, d = 4, 2, 64, 2, 8
+    q, k, v = orc.make_factors(7, b, l * n, l * n, 3, 2, h, d, d)
+    ids = orc.segment_ids(b, l * n, 24)
+    ring = orc.ring_tpa_reference(q, k, v, ids, ids, h, n, sm_scale=0.3, causal=True, mask_mode="reference_local")
+    for r in range(n):
+        sl = slice(r * l, (r + 1) * l)
+        o = orc.tpa_reference(q[:, sl], k, v, h, ids[:, sl], ids, sm_scale=0.3, causal=True, kv_parts=n, per_part=True)
+        np.testing.assert_allclose(o, ring[:, sl], rtol=1e-12, atol=1e-12, equal_nan=True)
+
+
+def test_window_and_dilation_masks_by_brute_force():
+    for causal in (False, True):
+        for window, dilation in ((0, 3), (5, 1), (4, 2)):
+            keep = orc.position_mask(np.arange(40) + 7, np.arange(50) + 2, causal, window, dilation)
+            for i in range(40):
+                for j in range(50):
+                    diff = (i + 7) - (j + 2)
+                    want = (not causal or diff >= 0) and diff % dilation == 0
+                    if window:
+                        want = want and abs(diff) < window * dilation
+                    assert keep[i, j] == want, (causal, window, dilation, i, j)
+    # a causal window of w keeps exactly min(w, i + 1) keys for row i
+    keep = orc.position_mask(np.arange(30), np.arange(30), True, 6, 1)
+    assert [int(r.sum()) for r in keep] == [min(6, i + 1) for i in range(30)]
+
+
+def test_rope_on_the_dim_factors_is_rope_on_the_rebuilt_rows():
+    """Rotating B before the rank sum equals rotating Q and K rows after it, and the logits then
+    depend on relative position only (the defining property of the rotary embedding)."""
+    b, l, h, d = 1, 12, 3, 16
+    q, k, v = orc.make_factors(11, b, l, l, 4, 2, h, d, d, dtype=np.float64)
+    cos, sin = orc.rope_tables(64, d, dtype=np.float64)
+    q_, k_, _ = orc.materialize(q, k, v, h)
+    qr, kr, _ = orc.materialize(orc.apply_rope(q, h, cos, sin, 5), orc.apply_rope(k, h, cos, sin, 5), v, h)
+
+    def rot(x, off):
+        out = x.copy()
+        c, s_ = cos[off:off + l][None, :, None, :], sin[off:off + l][None, :, None, :]
+        out[..., 0::2] = x[..., 0::2] * c - x[..., 1::2] * s_
+        out[..., 1::2] = x[..., 0::2] * s_ + x[..., 1::2] * c
+        return out
+
+    np.testing.assert_allclose(qr, rot(q_, 5), atol=1e-12)
+    np.testing.assert_allclose(kr, rot(k_, 5), atol=1e-12)
+    # shift both offsets: q.k of the same (row, key) pair is unchanged
+    q2, k2, _ = orc.materialize(orc.apply_rope(q, h, cos, sin, 20), orc.apply_rope(k, h, cos, sin, 20), v, h)
+    np.testing.assert_allclose(np.einsum("bqhd,bkhd->bhqk", qr, kr), np.einsum("bqhd,bkhd->bhqk", q2, k2), atol=1e-10)
+    # the head factor is untouched
+    assert np.array_equal(orc.apply_rope(q, h, cos, sin, 3)[..., :h], q[..., :h])

@@ -1,5 +1,6 @@
 """Host logic of the ring path on CPU: 2 and 4 gloo ranks, the device kernel replaced by an
-oracle-backed block with the same state contract (test-only hook `_block_fn`)."""
+oracle-backed block with the same state contract (test-only hook `_block_fn`, the step-by-step
+scan) or by an oracle-backed call over gathered key parts (`_parts_fn`, the one-call path)."""
 
 import os
 import socket
@@ -36,6 +37,17 @@ def oracle_block(q, k, v, qs, ks, num_heads, sm_scale, causal, q_off, k_off, sta
             lse.copy_(torch.from_numpy(l_).float())
 
 
+def oracle_parts(q, kbuf, vbuf, qs, sbuf, num_heads, sm_scale, causal, per_part, q_off, out, lse, reuse_kv):
+    """CPU stand-in for one tpa_fwd call over gathered key parts [parts, b, l, ...]."""
+    n, b, l = kbuf.shape[:3]
+    cat = lambda x: x.transpose(0, 1).reshape(b, n * l, *x.shape[3:]).numpy()  # noqa: E731  parts side by side
+    o_, l_ = orc.tpa_reference(q.numpy(), cat(kbuf), cat(vbuf), num_heads, qs.numpy(), cat(sbuf), sm_scale=sm_scale,
+                               causal=causal, q_offset=q_off, kv_parts=n, per_part=per_part, return_lse=True)
+    out.copy_(torch.from_numpy(o_).to(out.dtype))
+    if lse is not None:
+        lse.copy_(torch.from_numpy(l_).float())
+
+
 def oracle_bwd_block(q, k, v, qs, ks, num_heads, sm_scale, causal, q_off, k_off, o, lse, do, grads, accumulate_dq):
     """CPU stand-in for one tpa_bwd call (fp32 gradients, dk / dv always accumulate)."""
     g = orc.tpa_bwd_block(q.numpy(), k.numpy(), v.numpy(), do.numpy(), o.numpy(), lse.numpy(), num_heads,
@@ -62,13 +74,14 @@ def _worker(rank, world, port, case, ret):
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        seed, b, l, rq, rk, h, dk, dv, seg, sm, causal, mode = case
+        seed, b, l, rq, rk, h, dk, dv, seg, sm, causal, mode, path = case
         q, k, v = orc.make_factors(seed, b, l, l, rq, rk, h, dk, dv)
         ids = orc.segment_ids(b, l, seg) if seg else np.zeros((b, l), np.int32)
         tq, tk, tv, tid = (torch.from_numpy(x) for x in (q, k, v, ids))
+        hook = {"_block_fn": oracle_block} if path == "scan" else {"_parts_fn": oracle_parts}
         o = tpa_b200.ring_tpa.ring_tp_self_attention(
             tq, tk, tv, tid, tid, mesh=None, pspec=(None, "sp", None, None), num_heads=h,
-            sm_scale=sm, causal=causal, mask_mode=mode, gather_output=True, _block_fn=oracle_block)
+            sm_scale=sm, causal=causal, mask_mode=mode, gather_output=True, **hook)
         if rank == 0:
             ref = orc.ring_tpa_reference(q, k, v, ids, ids, h, world, sm_scale=sm, causal=causal,
                                          mask_mode=mode)
@@ -88,11 +101,12 @@ CASES = [
 
 
 @pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("path", ["scan", "one_call"])
 @pytest.mark.parametrize("case", CASES)
-def test_ring_host_logic_gloo(world, case):
+def test_ring_host_logic_gloo(world, case, path):
     mgr = mp.Manager()
     ret = mgr.dict()
-    mp.spawn(_worker, args=(world, _free_port(), case, ret), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), case + (path,), ret), nprocs=world, join=True)
     assert ret["shape"] == (case[1], case[2], case[5], case[7])
     assert ret["nan_equal"]
     assert ret["err"] < 1e-5, ret["err"]
@@ -117,6 +131,10 @@ def _bwd_worker(rank, world, port, case, ret):
         tq, tk, tv, tid, tdo = (torch.from_numpy(np.ascontiguousarray(x[:, sh])) for x in (q, k, v, ids, do))
         o, lse = tpa_b200.ring_tpa.ring_tpa(tq, tk, tv, tid, tid, None, h, sm_scale=sm, causal=causal,
                                             mask_mode=mode, return_lse=True, _block_fn=oracle_block)
+        # the one-call path must hand the backward the same residuals (balanced exchange included)
+        o1, lse1 = tpa_b200.ring_tpa.ring_tpa(tq, tk, tv, tid, tid, None, h, sm_scale=sm, causal=causal,
+                                              mask_mode=mode, return_lse=True, _parts_fn=oracle_parts)
+        assert torch.allclose(o, o1, atol=1e-5, equal_nan=True) and torch.allclose(lse, lse1, atol=1e-5)
         grads = tpa_b200.ring_tpa.ring_tpa_bwd(tq, tk, tv, tid, tid, o, lse, tdo, None, h, sm_scale=sm,
                                                causal=causal, mask_mode=mode, _block_fn=oracle_bwd_block)
         full = []

@@ -36,24 +36,26 @@ for (dtype, b, l, h, d, rq, rk, seg, mode, causal) in [
     td = torch.float32 if dtype == "f32" else torch.bfloat16
     tq, tk, tv = (torch.from_numpy(x).cuda().to(td) for x in (q, k, v))
     tid = torch.from_numpy(ids).cuda()
-    o = tpa_b200.ring_tpa.ring_tp_self_attention(tq, tk, tv, tid, tid, mesh=None, pspec=(None, "sp", None, None),
-                                                 num_heads=h, sm_scale=d ** -0.5, causal=causal, mask_mode=mode,
-                                                 gather_output=True)
-    st, detail = tpa_b200.tpa.device_status()
-    if st != 0:
-        fails.append((dtype, l, mode, "device status", detail))
-    if rank != 0:
-        continue  # the gathered output is identical on every rank; one oracle run is enough
-    ref = orc.ring_tpa_reference(tq.float().cpu().numpy(), tk.float().cpu().numpy(), tv.float().cpu().numpy(),
-                                 ids, ids, h, world, sm_scale=d ** -0.5, causal=causal, mask_mode=mode,
-                                 dtype=np.float32)
-    diff = np.abs(o.float().cpu().numpy() - ref)
-    ok = (diff.max() <= 1e-5) if dtype == "f32" else (diff.max() <= 2e-2 and diff.mean() <= 5e-3)
-    ok = ok and st == 0 and np.array_equal(np.isnan(o.float().cpu().numpy()), np.isnan(ref))
-    if rank == 0:
-        print(f"ring {dtype} l={l} d={d} {mode} causal={causal}: max {np.nanmax(diff):.2e} mean {np.nanmean(diff):.2e} status {st} {'OK' if ok else 'FAIL'}", flush=True)
-    if not ok:
-        fails.append((dtype, l, mode))
+    ref = None
+    for one_call in (None, False):  # gather + one attention call (default) and the step-by-step scan
+        o = tpa_b200.ring_tpa.ring_tp_self_attention(tq, tk, tv, tid, tid, mesh=None, pspec=(None, "sp", None, None),
+                                                     num_heads=h, sm_scale=d ** -0.5, causal=causal, mask_mode=mode,
+                                                     gather_output=True, one_call=one_call)
+        st, detail = tpa_b200.tpa.device_status()
+        if st != 0:
+            fails.append((dtype, l, mode, "device status", detail))
+        if rank != 0:
+            continue  # the gathered output is identical on every rank; one oracle run is enough
+        if ref is None:
+            ref = orc.ring_tpa_reference(tq.float().cpu().numpy(), tk.float().cpu().numpy(), tv.float().cpu().numpy(),
+                                         ids, ids, h, world, sm_scale=d ** -0.5, causal=causal, mask_mode=mode,
+                                         dtype=np.float32)
+        diff = np.abs(o.float().cpu().numpy() - ref)
+        ok = (diff.max() <= 1e-5) if dtype == "f32" else (diff.max() <= 2e-2 and diff.mean() <= 5e-3)
+        ok = ok and st == 0 and np.array_equal(np.isnan(o.float().cpu().numpy()), np.isnan(ref))
+        print(f"ring {dtype} l={l} d={d} {mode} causal={causal} one_call={one_call}: max {np.nanmax(diff):.2e} mean {np.nanmean(diff):.2e} status {st} {'OK' if ok else 'FAIL'}", flush=True)
+        if not ok:
+            fails.append((dtype, l, mode, one_call))
 # backward: autograd through ring_tpa on every rank's shard, gradients gathered and compared on rank 0
 for (dtype, b, l, h, d, rq, rk, seg, mode, causal) in [
     ("f32", 1, 128 * world, 4, 32, 3, 2, 100, "reference_local", True),
