@@ -544,7 +544,8 @@ def main():
                "sample": sample}
     line = {
         "metric": METRIC if not bwd else "TPA bwd algorithmic TFLOP/s per B200 (2.5x the forward's FLOPs)", "value": value, "unit": "TFLOP/s", "tokens_per_s": toks, "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "warmup": args.warmup, "ms_per_step": ms, "ms_per_step_median": statistics.median(per_step),
+        "ms_per_step_max": max(per_step), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": dtn, "data": "synthetic",
         "config": config_for(name, world, args.mask_mode, args.lq), "kernel": info, "cuda_graph": bool(args.graph),
         "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clock_summary,

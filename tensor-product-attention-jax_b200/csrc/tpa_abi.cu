@@ -94,7 +94,7 @@ static int choose(const TpaFwdArgs* a, const Params& p, int* kernel) {
   if (p.kv_parts > 1 && p.part_len % 64 != 0) return TPA_ERR_UNSUPPORTED;
   const bool dec = !ext && decode_supported(p);
   if (a->kernel == TPA_KERNEL_DECODE && !dec) return TPA_ERR_KERNEL_FORCED;
-  if (a->kernel == TPA_KERNEL_DECODE || (a->kernel == TPA_KERNEL_AUTO && decode_preferred(p))) {
+  if (a->kernel == TPA_KERNEL_DECODE || (a->kernel == TPA_KERNEL_AUTO && dec && decode_preferred(p))) {
     *kernel = TPA_KERNEL_DECODE;
     return TPA_OK;
   }

@@ -20,22 +20,34 @@
 //           (= TMEM lane); warps 8-11 / 12-15: rebuild the K / V tile (all eight rebuild Q once
 //           at the start); warp 16: issues tcgen05.mma: S_u = Q_u K^T (fp32 in TMEM), O_u += P_u V
 //   STAGED  warps 0-7 / 8-15: online softmax of unit 0 / unit 1, two threads per query row
-//           (each takes 64 of the 128 keys of a tile and half of the accumulator columns;
-//           the per-thread instruction stream, not the exponentials, is what the tensor pipe
-//           waits for, so halving it is worth a pair barrier per tile);
-//           warp 16: one thread issues the bulk copies of the staged tiles; warp 17: tcgen05.mma
+//           (each takes 64 of the 128 keys of a tile and half of the accumulator columns);
+//           warp 16: one thread issues the bulk copies of the staged tiles; warp 17: one thread
+//           issues the logits S_u = Q_u K^T; warp 18: one thread issues O_u += P_u V
 //
 // The 1/R_q, 1/R_k means and sm_scale * log2(e) are folded into Q once; the 1/R_k of V is
 // applied with the final 1/l.  K and V tiles are double buffered, in the 128-byte-swizzled
-// layout the tcgen05 shared-memory descriptors describe.  P (bf16) overwrites S in TMEM and
-// feeds the second MMA from there.  The two units alternate on the tensor pipe, so the
-// softmax of one overlaps the MMAs of the other.
+// layout the tcgen05 shared-memory descriptors describe.
 //
-// The running maximum is only raised when the new tile exceeds it by more than 2^8 (the
-// accumulator and row sum are then rescaled); the final 1/l division makes the result
-// independent of which maximum was subtracted.  STAGED goes further: it exponentiates against
-// the carried maximum straight away and only falls back to finding the tile maximum when a
-// row sum shows that some p exceeded 2^15.
+// FUSED: P (bf16) overwrites S in TMEM and feeds the second MMA from there, so per unit
+// softmax(j) -> P V(j) -> S(j+1) -> softmax(j+1) is one serial chain; the two units alternate on
+// the tensor pipe and the softmax of one overlaps the MMAs of the other.
+//
+// STAGED breaks that chain.  A softmax thread takes its 64 logits into registers the moment
+// they are complete and releases the columns; P gets columns of its own.  The next logits of a
+// unit are therefore computed while its softmax still works on the current ones, and only
+// P V waits for the softmax.  (With D = 128, TMEM has room for one set of logit columns beside
+// P0, P1, O0, O1: the two units use it in turn, which also keeps their exponentials apart on
+// the MUFU pipe.)  Issuing a tile's eight MMAs holds the issuing thread for about as long as
+// the tensor pipe needs for what is queued ahead of them, so logits and P V have a thread each:
+// neither sits in an issue while an event the other could act on arrives.  Measured (cycle
+// counters, longest CTA, T = 16384): 3590 cycles per 256 x 128 tile pair with P over S and one
+// issuing thread, 4100 with the logits drained but one issuing thread, 2900 with two.
+//
+// The running maximum is only raised when a tile exceeds it by more than 2^8 (the accumulator
+// and row sum are then rescaled); the final 1/l division makes the result independent of which
+// maximum was subtracted.  STAGED: each thread finds the maximum of its 64 logits, one one-bit
+// vote of the two warps that share the rows says whether any row needs a raise, and only then
+// do the halves exchange their maxima through shared memory.
 //
 // Every mbarrier wait is bounded: after ~2^28 cycles the waiter records where it gave up in
 // the status block, raises a CTA-wide abort flag that makes all later waits fall through,
@@ -61,7 +73,9 @@ struct Roles {
   static constexpr int kSoftmaxWarps = STAGED ? 16 : 8;
   static constexpr int kProducerWarps = STAGED ? 1 : kRebuildWarps;
   static constexpr int kMmaWarp = kSoftmaxWarps + kProducerWarps;
-  static constexpr int kThreads = (kMmaWarp + 1) * 32;  // STAGED 18 warps, FUSED 17
+  // STAGED has two issuing warps: kMmaWarp issues the logits S = Q K^T, kMmaWarp + 1 the P V
+  static constexpr int kMmaWarps = STAGED ? 2 : 1;
+  static constexpr int kThreads = (kMmaWarp + kMmaWarps) * 32;  // STAGED 19 warps, FUSED 17
 };
 constexpr int kUnitRows = 128;
 constexpr int kTileKv = 128;
@@ -75,6 +89,7 @@ struct Barriers {
   uint64_t k_full[2], k_empty[2];
   uint64_t v_full[2], v_empty[2];
   uint64_t s_full[2], p_ready[2], o_done[2];
+  uint64_t s_free[2];  // STAGED: the unit's softmax warps have taken their logits out of TMEM
   uint32_t tmem_base;
   volatile uint32_t abort;
   // key segment ids of the tile in each V stage (filled and released together with it)
@@ -86,8 +101,11 @@ struct Barriers {
 #ifdef TPA_DEBUG_CYCLES
 // tuning builds only: thread-private slots of the status block (words 8..63) get clock values
 #define TPA_TICK(slot) do { if (dbg_on && (slot) < 56) p.status[8 + (slot)] = (uint32_t)clock64(); } while (0)
+// five ticks per tile for tiles 4..13
+#define TPA_TICK5(k) do { if (j >= 4 && j < 14) TPA_TICK(1 + (j - 4) * 5 + (k)); } while (0)
 #else
 #define TPA_TICK(slot) do { } while (0)
+#define TPA_TICK5(k) do { } while (0)
 #endif
 
 struct Waiter {
@@ -382,8 +400,23 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
   constexpr int kTileBytes = kUnitRows * D * 2;  // one Q unit, one K stage or one V stage
   constexpr uint32_t kIdescS = make_idesc(128, kTileKv, false, false);
   constexpr uint32_t kIdescPV = make_idesc(128, D, false, true);
-  constexpr int kOCol = 256;  // TMEM: S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [256+D,256+2D)
+  // TMEM columns (512).  FUSED: S0 [0,128) S1 [128,256), P_u over S_u, O_u at 256 + u D.
+  // STAGED keeps P out of the logits' columns, so that the next logits of a unit can be computed
+  // while its softmax still works on the current ones (they are taken into registers at once):
+  //   D = 128: S [0,128) shared by the two units in turn, P0 [128,192) P1 [192,256), O0 [256,384) O1 [384,512)
+  //   D = 64:  S0 [0,128) S1 [128,256), P0 [256,320) P1 [320,384), O0 [384,448) O1 [448,512)
+  constexpr bool kSharedS = STAGED;  // at D = 64 there is room for two, but taking turns keeps the units' exponentials apart
+  auto s_col = [](int u) -> uint32_t { return kSharedS ? 0u : (uint32_t)u * 128u; };
+  auto p_col = [](int u) -> uint32_t {
+    return !STAGED ? (uint32_t)u * 128u : (D == 128 ? 128u + 64u * u : 256u + 64u * u);
+  };
+  auto o_col = [](int u) -> uint32_t {
+    return !STAGED ? 256u + (uint32_t)u * D : (D == 128 ? 256u + 128u * u : 384u + 64u * u);
+  };
 
+#ifdef TPA_DEBUG_CYCLES
+  const long long dbg_t_entry = clock64();
+#endif
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -471,6 +504,7 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
       mbar_init(&bars->s_full[s], 1);
       mbar_init(&bars->p_ready[s], kSoftmaxWarps / 2);  // one arrival per softmax warp of the unit
       mbar_init(&bars->o_done[s], 1);
+      mbar_init(&bars->s_free[s], kSoftmaxWarps / 2);
     }
     bars->abort = 0;
     fence_mbar_init();
@@ -510,9 +544,9 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
     const bool live = q0u < p.lq;      // the unit exists
     const bool row_ok = grow < p.lq;   // this thread's row exists (the last unit may be ragged)
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-    const uint32_t tS = tmem + lane_base + u * 128;
-    const uint32_t tSh = tS + half * 64;                        // this thread's 64 logits
-    const uint32_t tOh = tmem + lane_base + kOCol + u * D + half * (D / 2);  // its D/2 accumulators
+    const uint32_t tSh = tmem + lane_base + s_col(u) + half * 64;      // this thread's 64 logits
+    const uint32_t tPh = tmem + lane_base + p_col(u) + half * 32;      // ... and where their bf16 P goes
+    const uint32_t tOh = tmem + lane_base + o_col(u) + half * (D / 2);  // its D/2 accumulators
     const int64_t rh = row_ok ? ((int64_t)batch * p.lq + grow) * p.heads + head : 0;
     const int64_t qpos = (int64_t)grow + p.q_offset;
     const int qseg = (has_seg && row_ok) ? p.q_seg[(int64_t)batch * p.q_seg_bstride + grow] : 0;
@@ -564,15 +598,25 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
 
 #ifdef TPA_DEBUG_CYCLES
     const bool dbg_on = blockIdx.x == TPA_DEBUG_CYCLES && warp == 8 && lane == 0 && p.status != nullptr;  // unit 1, half 0
+    if (dbg_on) p.status[8 + 52] = (uint32_t)dbg_t_entry;
     TPA_TICK(0);
 #endif
     // position of walk tile j0 + j: tile (j0 + j) / G of its part, kept by counting
     int pos_tile = kParts ? j0 / G : j0, pos_cnt = kParts ? j0 % G : 0;
     for (int j = 0; j < n_u; ++j) {
-      TPA_TICK(1 + 3 * j);
       wait(&bars->s_full[u], j & 1, 0x100 + u);
       tc_fence_after();
-      TPA_TICK(2 + 3 * j);
+      // The thread's 64 logits leave TMEM at once; the MMA warp may then overwrite them with the
+      // next tile's (of this unit, or of the other one where the two share the columns) while
+      // this tile's softmax runs.
+      uint32_t r0[32], r1[32];
+      tmem_ld32(tSh, r0);
+      tmem_ld32(tSh + 32, r1);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->s_free[u]);
+      TPA_TICK5(0);
       // this thread's 64 columns: index of the first in the walk (= in the key array unless the
       // walk is interleaved, and then no tile is ragged) and its position in the comparisons
       const int k0 = (j0 + j) * kTileKv + half * 64;
@@ -599,12 +643,12 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
         seg_mask = !__all_sync(0xffffffffu, kmin == kmax && qseg == kmin);
       }
       const bool masked = edge || seg_mask || tail || dilated;
-      // The causal rule, the window and the end of the keys leave this thread a range [lo, hi) of
-      // its 64 columns.  rel = its row's position minus its first column's, clamped to 32 bits
-      // (see MaskRule); column c is kept by the causal rule iff c <= rel, by the window iff
-      // |rel - c| < span.
-      int lo = 0, hi = 64, phase = 0;
       if (masked) {
+        // The causal rule, the window and the end of the keys leave this thread a range [lo, hi) of
+        // its 64 columns.  rel = its row's position minus its first column's, clamped to 32 bits
+        // (see MaskRule); column c is kept by the causal rule iff c <= rel, by the window iff
+        // |rel - c| < span.
+        int lo = 0, hi = 64, phase = 0;
         const int rel = clamp_diff(qpos - kp0);
         if (tail) hi = min(hi, p.lk - k0);
         if (edge) {
@@ -613,94 +657,44 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
           if (windowed) lo = max(lo, rel - span + 1);
         }
         if (dilated) phase = diff_phase(qpos - kp0, p.dilation);
+        const unsigned width = hi > lo ? (unsigned)(hi - lo) : 0u;
+        auto mask_chunk = [&](uint32_t(&r)[32], int c) {
+          if (edge || tail) {
+#pragma unroll
+            for (int e = 0; e < 32; ++e)
+              if ((unsigned)(c * 32 + e - lo) >= width) r[e] = 0xff800000u;  // -inf
+          }
+          if (seg_mask) {
+#pragma unroll
+            for (int e = 0; e < 32; ++e)
+              if (qseg != ks[c * 32 + e]) r[e] = 0xff800000u;
+          }
+          if (dilated) {  // a loop of its own: the remainders are only computed when asked for
+#pragma unroll
+            for (int e = 0; e < 32; ++e)
+              if ((phase - (c * 32 + e)) % p.dilation != 0) r[e] = 0xff800000u;
+          }
+        };
+        mask_chunk(r0, 0);
+        mask_chunk(r1, 1);
       }
-      const unsigned width = hi > lo ? (unsigned)(hi - lo) : 0u;
-
-      auto mask_chunk = [&](uint32_t(&r)[32], int c) {
-        if (edge || tail) {
+      // Maximum of the thread's 64 logits.  The reference maximum m carried from earlier tiles
+      // stays as long as no logit of the row exceeds it by more than 2^8 (the final 1 / l makes
+      // the result independent of which maximum was subtracted): one one-bit vote of the two
+      // warps that share the rows.  Only when some row needs a new maximum do the halves
+      // exchange theirs through shared memory.  m is identical in both halves of a row, so both
+      // warps of a pair always take the same branches.
+      float cm4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
 #pragma unroll
-          for (int e = 0; e < 32; ++e)
-            if ((unsigned)(c * 32 + e - lo) >= width) r[e] = 0xff800000u;  // -inf
-        }
-        if (seg_mask) {
-#pragma unroll
-          for (int e = 0; e < 32; ++e)
-            if (qseg != ks[c * 32 + e]) r[e] = 0xff800000u;
-        }
-        if (dilated) {  // a loop of its own: the remainders are only computed when asked for
-#pragma unroll
-          for (int e = 0; e < 32; ++e)
-            if ((phase - (c * 32 + e)) % p.dilation != 0) r[e] = 0xff800000u;
-        }
-      };
-      // p = 2^(s - reference maximum) for one 32-column chunk, packed to bf16, plus the row
-      // sum in four packed partial sums.
-      uint64_t neg_m2 = 0, lsum[4];
-      auto set_reference = [&](float mm) {
-        const float neg_m = (mm == -CUDART_INF_F) ? 0.f : -mm;
-        neg_m2 = pack2(neg_m, neg_m);
-        lsum[0] = lsum[1] = lsum[2] = lsum[3] = 0ull;
-      };
-      auto exp_chunk = [&](const uint32_t(&r)[32], uint32_t* pk) {
-#pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float x0, x1;
-          unpack2(add2(pack2(__uint_as_float(r[e]), __uint_as_float(r[e + 1])), neg_m2), x0, x1);
-          const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
-          lsum[(e >> 1) & 3] = add2(lsum[(e >> 1) & 3], pack2(p0, p1));
-          pk[e / 2] = pack_bf16(p0, p1);
-        }
-      };
-      auto row_sum = [&]() {
-        float a0, a1, a2, a3;
-        unpack2(add2(lsum[0], lsum[1]), a0, a1);
-        unpack2(add2(lsum[2], lsum[3]), a2, a3);
-        return (a0 + a1) + (a2 + a3);
-      };
-
-      uint32_t pk[32];
-      // One 32-column chunk of logits is live at a time (the register budget of 18 warps):
-      // fetch, mask, use, fetch the next.
-      auto load_chunk = [&](uint32_t(&r)[32], int c) {
-        tmem_ld32(tSh + c * 32, r);
-        tmem_ld_wait();
-        if (masked) mask_chunk(r, c);
-      };
-      auto exp_row = [&]() {
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t r[32];
-          load_chunk(r, c);
-          exp_chunk(r, pk + c * 16);
-        }
-      };
-      // Optimistic: exponentiate against the maximum carried from earlier tiles.  A sum of
-      // at most 2^15 over this thread's columns proves each p is at most 2^15 (no overflow,
-      // bf16 keeps its relative precision), so the carried maximum may stay although it can
-      // be stale.  Both halves of every row of the warp pair must agree (one-bit vote);
-      // otherwise, or when a row has no maximum yet, nothing has been stored and the exact
-      // route finds the row maximum first (the logits are still in TMEM and are fetched again).
-      // m is identical in both halves, so both warps of a pair always take the same branches.
-      bool done = false;
-      if (__all_sync(0xffffffffu, m != -CUDART_INF_F)) {
-        set_reference(m);
-        exp_row();
-        const float tsum = row_sum();
-        const bool bad = __any_sync(0xffffffffu, !(tsum <= kOptimisticSumLimit));  // inf / NaN too
-        if (!pair_any(bad)) {
-          l += tsum;
-          done = true;
-        }
+      for (int e = 0; e < 32; e += 4) {  // four independent chains
+        cm4[0] = max3(cm4[0], __uint_as_float(r0[e]), __uint_as_float(r0[e + 1]));
+        cm4[1] = max3(cm4[1], __uint_as_float(r0[e + 2]), __uint_as_float(r0[e + 3]));
+        cm4[2] = max3(cm4[2], __uint_as_float(r1[e]), __uint_as_float(r1[e + 1]));
+        cm4[3] = max3(cm4[3], __uint_as_float(r1[e + 2]), __uint_as_float(r1[e + 3]));
       }
-      if (!done) {
-        float cm = -CUDART_INF_F;
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t r[32];
-          load_chunk(r, c);
-#pragma unroll
-          for (int e = 0; e < 32; e += 2) cm = max3(cm, __uint_as_float(r[e]), __uint_as_float(r[e + 1]));
-        }
+      const float cm = fmaxf(fmaxf(cm4[0], cm4[1]), fmaxf(cm4[2], cm4[3]));
+      const bool need = (m == -CUDART_INF_F) ? (cm != -CUDART_INF_F) : (cm - m > kRescaleThreshold);
+      if (pair_any(__any_sync(0xffffffffu, need))) {
         // row maximum over both halves, through shared memory (slot alternates with the tile)
         float* xch = bars->xch[j & 1][u][0];
         xch[half * kUnitRows + row] = cm;
@@ -719,37 +713,65 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
             tc_fence_after();
           }
 #pragma unroll
-          for (int c = 0; c < kOChunks; ++c) {
-            uint32_t r[32];
-            tmem_ld32(tOh + c * 32, r);
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t a[16];
+            tmem_ld16(tOh + c * 16, a);
             tmem_ld_wait();
 #pragma unroll
-            for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * factor);
-            tmem_st32(tOh + c * 32, r);
+            for (int e = 0; e < 16; ++e) a[e] = __float_as_uint(__uint_as_float(a[e]) * factor);
+            tmem_st16(tOh + c * 16, a);
           }
         }
         l *= factor;
-        set_reference(m);
-        exp_row();
-        l += row_sum();
       }
-      // P of this half overwrites the first 32 columns of its own 64 logits: key k of the tile
-      // is at column (k / 64) * 64 + (k % 64) / 2 (the PV MMAs address it that way)
-      tmem_st32(tSh, pk);
+      TPA_TICK5(1);
+      // p = 2^(s - m), packed to bf16, and the row sum in four packed partial sums
+      const float neg_m = (m == -CUDART_INF_F) ? 0.f : -m;
+      const uint64_t neg_m2 = pack2(neg_m, neg_m);
+      uint64_t lsum[4] = {0ull, 0ull, 0ull, 0ull};
+      uint32_t pk[32];
+      auto exp_chunk = [&](const uint32_t(&r)[32], uint32_t* out) {
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float x0, x1;
+          unpack2(add2(pack2(__uint_as_float(r[e]), __uint_as_float(r[e + 1])), neg_m2), x0, x1);
+          const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+          lsum[(e >> 1) & 3] = add2(lsum[(e >> 1) & 3], pack2(p0, p1));
+          out[e / 2] = pack_bf16(p0, p1);
+        }
+      };
+      exp_chunk(r0, pk);
+      TPA_TICK5(2);
+      exp_chunk(r1, pk + 16);
+      {
+        float a0, a1, a2, a3;
+        unpack2(add2(lsum[0], lsum[1]), a0, a1);
+        unpack2(add2(lsum[2], lsum[3]), a2, a3);
+        l += (a0 + a1) + (a2 + a3);
+      }
+      TPA_TICK5(3);
+      // P has columns of its own: key k of the tile is at column k / 2.  They are free once the
+      // previous tile's P V has been read out (the same barrier the accumulator rescale waits on).
+      if (j > 0) {
+        wait(&bars->o_done[u], (j - 1) & 1, 0x210 + u);
+        tc_fence_after();
+      }
+      tmem_st32(tPh, pk);
       tmem_st_wait();  // warp-wide: every lane's P (and any rescaled accumulator) has landed
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->p_ready[u]);
-      TPA_TICK(3 + 3 * j);
+      TPA_TICK5(4);
     }
 
+    TPA_TICK(53);
     // ---- epilogue: o = acc / (l * R_k), lse = ln2 * (m + log2 l); NaN / -inf for empty rows
     if (live) {
       if (n_u > 0) {
         wait(&bars->o_done[u], (n_u - 1) & 1, 0x300 + u);
         tc_fence_after();
       }
-      TPA_TICK(40);
+      TPA_TICK(54);
       // row sum = this half's share + the partner's
       float* xch = bars->xch[n_u & 1][u][0];
       xch[half * kUnitRows + row] = l;
@@ -809,6 +831,7 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
         }
       }
     }
+    TPA_TICK(55);
    } else {
     // ------------------------------------------------------------------ softmax + epilogue
     const int u = warp >> 2;
@@ -820,7 +843,7 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
     const bool row_ok = grow < p.lq;   // this thread's row exists (the last unit may be ragged)
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t tS = tmem + lane_base + u * 128;
-    const uint32_t tO = tmem + lane_base + kOCol + u * D;
+    const uint32_t tO = tmem + lane_base + o_col(u);
     const int64_t rh = row_ok ? ((int64_t)batch * p.lq + grow) * p.heads + head : 0;
     const int64_t qpos = (int64_t)grow + p.q_offset;
     const int qseg = (has_seg && row_ok) ? p.q_seg[(int64_t)batch * p.q_seg_bstride + grow] : 0;
@@ -1087,14 +1110,14 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
    }
   } else {
     // ------------------------------------------------------------------ MMA issue (one thread)
-    if (warp == kMmaWarp && lane == 0 && n_tiles > 0) {
+    if (lane == 0 && n_tiles > 0) {
       const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), aV = smem_u32(sV);
       auto issue_s = [&](int u, int j) {
         const uint32_t qbase = aQ + u * kTileBytes, kbase = aK + (j & 1) * kTileBytes;
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
           const uint32_t off = (ks >> 2) * (kUnitRows * 128) + (ks & 3) * 32;
-          mma_ss(tmem + u * 128, make_desc(qbase + off, 16, 1024), make_desc(kbase + off, 16, 1024),
+          mma_ss(tmem + s_col(u), make_desc(qbase + off, 16, 1024), make_desc(kbase + off, 16, 1024),
                  kIdescS, ks > 0);
         }
         tc_commit(&bars->s_full[u]);
@@ -1103,20 +1126,68 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
         const uint32_t vbase = aV + (j & 1) * kTileBytes;
 #pragma unroll
         for (int ks = 0; ks < kTileKv / 16; ++ks) {
-          // P of key k: column k / 2 (FUSED), or (k / 64) * 64 + (k % 64) / 2 (STAGED, see softmax)
-          mma_ts(tmem + kOCol + u * D, tmem + u * 128 + (STAGED ? (ks >> 2) * 64 + (ks & 3) * 8 : ks * 8),
+          // P of key k is at column k / 2 of the unit's P columns
+          mma_ts(tmem + o_col(u), tmem + p_col(u) + ks * 8,
                  make_desc(vbase + ks * 2048, kTileKv * 128, 1024), kIdescPV, (acc || ks > 0) ? 1u : 0u);
         }
         tc_commit(&bars->o_done[u]);
       };
-      // Per unit the order is fixed: S(j), O += P V of tile j, S(j+1) (which overwrites P).  The
-      // units are interleaved in a fixed order too, PV0(j) S0(j+1) PV1(j) S1(j+1): it keeps them
-      // half a tile apart, so that the softmax of one always has the other's MMAs to hide behind.
-      // (Measured alternatives that lost: polling for whichever unit is ready first, and one
-      // issuing thread per unit; both let the units drift into phase.)
-      wait(&bars->q_full, 0, 0x600);
-      tc_fence_after();
-      {
+      if constexpr (STAGED) {
+        // Two issuing threads.  Issuing tcgen05.mma holds the thread for about as long as the
+        // tensor pipe needs for what is queued before it (measured: ~670 cycles for the eight
+        // MMAs of a tile), so one thread that issues everything cannot also be waiting for the
+        // next softmax event while the pipe works: every hand-over then costs its full latency
+        // in pipe idle time.  Here one thread issues the logits and another the P V; each waits
+        // only for its own events, and the pipe takes from both.
+        //
+        // The softmax warps take a tile's logits into registers as soon as they are complete and
+        // say so (s_free); from then on the columns may be overwritten, so S_u(j+1) is issued
+        // while softmax_u(j) still runs and only P_u(j) V waits for it.  With D = 128 the two
+        // units share one set of logit columns and use it in turn, S0(j) S1(j) S0(j+1) ..., each
+        // after the previous user has drained.
+        if (warp == kMmaWarp) {
+          wait(&bars->q_full, 0, 0x600);
+          tc_fence_after();
+          int last_u = -1, last_j = 0;  // the last logits issued into the shared columns
+          for (int j = 0; j < n_tiles; ++j) {
+            wait(&bars->k_full[j & 1], (j >> 1) & 1, 0x601);
+            tc_fence_after();
+            for (int u = 0; u < 2; ++u) {
+              if (j >= n_vis[u]) continue;
+              if (kSharedS) {
+                if (last_u >= 0) {
+                  wait(&bars->s_free[last_u], last_j & 1, 0x620 + last_u);
+                  tc_fence_after();
+                }
+              } else if (j > 0) {
+                wait(&bars->s_free[u], (j - 1) & 1, 0x620 + u);
+                tc_fence_after();
+              }
+              issue_s(u, j);
+              last_u = u;
+              last_j = j;
+            }
+            tc_commit(&bars->k_empty[j & 1]);  // both units' logits of tile j are issued
+          }
+        } else {
+          for (int j = 0; j < n_tiles; ++j) {
+            wait(&bars->v_full[j & 1], (j >> 1) & 1, 0x602);
+            tc_fence_after();
+            for (int u = 0; u < 2; ++u) {
+              if (j >= n_vis[u]) continue;
+              wait(&bars->p_ready[u], j & 1, 0x610 + u);
+              tc_fence_after();
+              issue_pv(u, j, load_state || j > 0);
+            }
+            tc_commit(&bars->v_empty[j & 1]);  // both units' P V of tile j are issued
+          }
+        }
+      } else {
+        // Per unit the order is fixed: S(j), O += P V of tile j, S(j+1) (which overwrites P).  The
+        // units are interleaved in a fixed order too, PV0(j) S0(j+1) PV1(j) S1(j+1): it keeps them
+        // half a tile apart, so that the softmax of one always has the other's MMAs to hide behind.
+        wait(&bars->q_full, 0, 0x600);
+        tc_fence_after();
         wait(&bars->k_full[0], 0, 0x601);
         tc_fence_after();
         for (int u = 0; u < 2; ++u)
