@@ -17,6 +17,7 @@ reference itself needs jax, which is not installed) on the host cores instead.
 from __future__ import annotations
 
 import argparse
+import gc
 import json
 import os
 import statistics
@@ -138,14 +139,26 @@ def make_inputs(name, device, shard=None, seed=0):
     return q, k, v
 
 
-def host_threads():
-    """Use every host core this process may run on (torchrun exports OMP_NUM_THREADS=1)."""
+def host_threads(share=1):
+    """Use every host core this process may run on (torchrun exports OMP_NUM_THREADS=1); with
+    `share` > 1 the cores are divided among that many ranks working at the same time -- eight
+    processes each spinning a full team of OpenMP threads on the same cores take minutes for
+    what is seconds of work."""
     try:
         n = len(os.sched_getaffinity(0))
     except AttributeError:
         n = os.cpu_count() or 1
-    torch.set_num_threads(max(1, n))
+    torch.set_num_threads(max(1, n // max(1, share)))
     return torch.get_num_threads()
+
+
+_T0 = time.perf_counter()
+
+
+def progress(msg):
+    """Rank 0's progress on stderr (where a run that does not finish stopped)."""
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(f"[bench {time.perf_counter() - _T0:7.1f}s] {msg}", file=sys.stderr, flush=True)
 
 
 def config_for(name, world, mask_mode, lq=None):
@@ -360,7 +373,15 @@ def main():
         if ring:
             return tpa_b200.ring_tpa.ring_tpa(q, k, v, ids, ids, None, h, sm_scale=sm_scale, causal=causal,
                                               mask_mode=args.mask_mode)
-        return tpa_b200.tpa.fwd_device(q, k, v, h, None, None, sm_scale, causal, q_offset=q_off, kernel=args.kernel)[0]
+        buf = outs[calls[0] % 2]
+        calls[0] += 1
+        return tpa_b200.tpa.fwd_device(q, k, v, h, None, None, sm_scale, causal, q_offset=q_off, kernel=args.kernel,
+                                       out=buf[0], lse=buf[1])[0]
+
+    calls = [0]
+    if not ring and not bwd:  # two result buffers used in turn: no allocator work inside the timed region
+        outs = [(torch.empty((b, q.shape[1], h, d), dtype=q.dtype, device=device),
+                 torch.empty((b, q.shape[1], h), dtype=torch.float32, device=device)) for _ in range(2)]
 
     if args.graph:
         assert not ring, "--graph is a single-GPU measurement"
@@ -386,6 +407,7 @@ def main():
             dist.barrier()
             torch.cuda.synchronize(device)
 
+    progress(f"inputs ready ({name}, {world} GPU(s)); warm-up and timed steps")
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
     with ClockSampler(local_rank) as clocks:
         clocks.wait_first()
@@ -406,12 +428,15 @@ def main():
                 torch.cuda.synchronize(device)
         sync()
         n0 = _capi.lib.tpa_launch_count()
+        gc.collect()
+        gc.disable()  # no collector pause between the launches of the timed region
         ev[0].record()
         last = None
         for i in range(args.steps):
             last = step()
             ev[i + 1].record()
         sync()
+        gc.enable()
         launches = _capi.lib.tpa_launch_count() - n0
         if args.graph:
             launches = launches_per_replay * args.steps
@@ -434,6 +459,7 @@ def main():
     # ------------------------------------------------------------- end to end on pinned host arrays
     e2e = None
     if not args.no_e2e and not bwd and args.lq is None:
+        progress(f"timed steps done ({ms:.3f} ms/step); end to end on pinned host arrays")
         hq, hk, hv = (x.cpu().pin_memory() for x in (q, k, v))
         hid = ids.cpu().pin_memory() if ring else None
         out_host = torch.empty((b, q.shape[1], h, d), dtype=q.dtype).pin_memory()
@@ -470,14 +496,15 @@ def main():
     # ------------------------------------------------------------- parity of what was just timed
     parity = None
     if not args.no_parity and not bwd:
-        host_threads()
+        progress("parity check of the timed output")
+        host_threads(share=world)
         if ring:
             kf = [torch.empty_like(k) for _ in range(world)]
             vf = [torch.empty_like(v) for _ in range(world)]
             dist.all_gather(kf, k)
             dist.all_gather(vf, v)
             mx, mean, nrows = parity_ring(last, q, torch.cat(kf, 1), torch.cat(vf, 1), h, d, causal, args.mask_mode,
-                                          rank, world, dtn)
+                                          rank, world, dtn, n_rows=max(8, 64 // world))
             del kf, vf
             agg = torch.tensor([mx, mean], device=device)
             dist.all_reduce(agg, op=dist.ReduceOp.MAX)
@@ -494,6 +521,7 @@ def main():
     # ------------------------------------------------------------- same-box single-GPU time of the ring workload
     n1_ms = None
     if ring and not args.no_n1:
+        progress("the unsharded workload on rank 0's GPU")
         if rank == 0:
             fq, fk, fv = make_inputs(name, device)
             fid = torch.zeros((b, t), dtype=torch.int32, device=device)
@@ -509,6 +537,43 @@ def main():
             torch.cuda.synchronize(device)
             n1_ms = a0.elapsed_time(a1) / 3
             del fq, fk, fv
+        dist.barrier()
+
+    # ------------------------------------------------------------- where a ring step's time goes (rank 0's view)
+    breakdown = None
+    if ring and args.mask_mode == "reference_local":
+        progress("breakdown of a ring step")
+        from tpa_b200 import ring_tpa as _ring
+        _ring._timing = []
+        for _ in range(3):
+            step()
+        sync()
+        recs, _ring._timing = _ring._timing, None
+        if recs:
+            med = lambda i: statistics.median(r["events"][i].elapsed_time(r["events"][i + 1]) for r in recs)  # noqa: E731
+            own, hops, rest = med(0), med(1), med(2)
+            rq, kbuf, vbuf, rqs, sbuf, state = recs[-1]["operands"]
+            n_rest = world - 1
+            kk, vv, ss = (kbuf, vbuf, sbuf) if n_rest > 1 else (kbuf[0], vbuf[0], sbuf[0])
+            # the second call again on the tiles the last step staged: what remains is its staging pass
+            only = lambda: tpa_b200.tpa.fwd_device(rq, kk, vv, h, rqs, ss, sm_scale, causal, want_lse=False,  # noqa: E731
+                                                   kv_parts=n_rest, per_part=causal and n_rest > 1, state=state,
+                                                   load_state=True, reuse_staged_q=True, reuse_staged_kv=True)
+            only()
+            b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            b0.record()
+            for _ in range(3):
+                only()
+            b1.record()
+            torch.cuda.synchronize(device)
+            attn = b0.elapsed_time(b1) / 3
+            breakdown = {"own_shard_call_ms": own, "exposed_wait_for_hops_ms": hops, "visiting_shards_call_ms": rest,
+                         "of_which_staging_ms": max(rest - attn, 0.0), "of_which_attention_ms": attn,
+                         "note": "rank 0, medians of 3 steps.  All N-1 hops are queued at entry on a side stream and "
+                                 "travel while the first call (Q tiles, own K/V shard, its attention) runs; the "
+                                 "second call rebuilds the N-1 visiting shards as tiles and attends to them, "
+                                 "starting from the first call's partial (o, lse)"}
+            del recs
         dist.barrier()
 
     if rank != 0:
@@ -538,6 +603,7 @@ def main():
                     "traffic": None, "kernel": info["kernel"], "hbm_algorithmic_bytes": stream}
     cpu = None
     if not args.no_cpu_baseline and world == 1 and not bwd and args.lq is None:
+        progress("CPU baseline sample")
         cores = host_threads()
         tf, ctoks, cdt, sample = time_cpu(name, 1, 0, 2048)
         cpu = {"value": tf, "unit": "TFLOP/s", "tokens_per_s": ctoks, "cores": cores, "kind": "port",
@@ -545,7 +611,7 @@ def main():
     line = {
         "metric": METRIC if not bwd else "TPA bwd algorithmic TFLOP/s per B200 (2.5x the forward's FLOPs)", "value": value, "unit": "TFLOP/s", "tokens_per_s": toks, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "ms_per_step_median": statistics.median(per_step),
-        "ms_per_step_max": max(per_step), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "ms_per_step_max": max(per_step), "slowest_step": per_step.index(max(per_step)), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": dtn, "data": "synthetic",
         "config": config_for(name, world, args.mask_mode, args.lq), "kernel": info, "cuda_graph": bool(args.graph),
         "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clock_summary,
@@ -553,7 +619,8 @@ def main():
     }
     if n1_ms is not None:
         # strong scaling on one box: the unsharded workload on one GPU against N GPUs
-        line["ring"] = {"n1_ms": n1_ms, "ring_efficiency": n1_ms / (world * ms), "mask_mode": args.mask_mode}
+        line["ring"] = {"n1_ms": n1_ms, "ring_efficiency": n1_ms / (world * ms), "mask_mode": args.mask_mode,
+                        "breakdown": breakdown}
     print(json.dumps(line), flush=True)
     if ring:
         dist.destroy_process_group()

@@ -151,6 +151,16 @@ __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
   asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
   return r;
 }
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -264,15 +274,19 @@ __global__ void __launch_bounds__(256) tpa_stage_tiles_kernel(const Params p, ui
   // rotary embedding of Q and K rows: table row = row index + offset
   const bool rope = p.rope_cos != nullptr && !is_v;
   const int64_t rope_off = is_q ? p.rope_q_offset : p.rope_k_offset;
+  // Two fp32 columns ride in one 64-bit register and every multiply-add is a packed fma.f32x2:
+  // the kernel is bound by instruction issue, and this halves its FMA count.  The scale is folded
+  // into the head factor (8 multiplies per rank instead of 64 per row).
+  const uint64_t scale2 = pack2(scale, scale);
   for (int row = r_in; row < kUnitRows; row += 256 / CH) {
     const int64_t g = (int64_t)tile * kUnitRows + row;
     const __nv_bfloat16* ap = a + g * fa->stride[1];
     const __nv_bfloat16* bp = b + g * fb->stride[1] + chunk * 8;
-    float acc[8][8];
+    uint64_t acc[8][4];
 #pragma unroll
     for (int h = 0; h < 8; ++h)
 #pragma unroll
-      for (int e = 0; e < 8; ++e) acc[h][e] = 0.f;
+      for (int e = 0; e < 4; ++e) acc[h][e] = 0ull;
     // four ranks at a time: their eight 16-byte loads are issued before any of the FMAs
     // rows past the end of a ragged last tile stay zero (the attention kernel masks them)
     for (int r0 = 0; r0 < (g < length ? rank : 0); r0 += 4) {
@@ -288,17 +302,16 @@ __global__ void __launch_bounds__(256) tpa_stage_tiles_kernel(const Params p, ui
         if (r0 + i < rank) {
           const uint32_t bw[4] = {bv[i].x, bv[i].y, bv[i].z, bv[i].w};
           const uint32_t aw[4] = {av[i].x, av[i].y, av[i].z, av[i].w};
-          float bf[8];
+          uint64_t b2[4];  // columns (2e, 2e + 1) of this thread's eight
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            bf[2 * e] = __uint_as_float(bw[e] << 16);
-            bf[2 * e + 1] = __uint_as_float(bw[e] & 0xffff0000u);
-          }
+          for (int e = 0; e < 4; ++e)
+            b2[e] = pack2(__uint_as_float(bw[e] << 16), __uint_as_float(bw[e] & 0xffff0000u));
 #pragma unroll
           for (int h = 0; h < 8; ++h) {
             const float ah = __uint_as_float((h & 1) ? (aw[h >> 1] & 0xffff0000u) : (aw[h >> 1] << 16));
+            const uint64_t a2 = mul2(pack2(ah, ah), scale2);
 #pragma unroll
-            for (int e = 0; e < 8; ++e) acc[h][e] = fmaf(ah, bf[e], acc[h][e]);
+            for (int e = 0; e < 4; ++e) acc[h][e] = fma2(a2, b2[e], acc[h][e]);
           }
         }
       }
@@ -312,20 +325,22 @@ __global__ void __launch_bounds__(256) tpa_stage_tiles_kernel(const Params p, ui
       for (int h = 0; h < 8; ++h)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const float x = acc[h][2 * e], y = acc[h][2 * e + 1];
-          acc[h][2 * e] = x * c4[e] - y * s4[e];
-          acc[h][2 * e + 1] = x * s4[e] + y * c4[e];
+          float x, y;
+          unpack2(acc[h][e], x, y);
+          acc[h][e] = pack2(x * c4[e] - y * s4[e], x * s4[e] + y * c4[e]);
         }
     }
     const uint32_t off = sw128_offset(row, chunk & 7);
 #pragma unroll
     for (int h = 0; h < 8; ++h) {
-      uint4 o;
-      o.x = pack_bf16(acc[h][0] * scale, acc[h][1] * scale);
-      o.y = pack_bf16(acc[h][2] * scale, acc[h][3] * scale);
-      o.z = pack_bf16(acc[h][4] * scale, acc[h][5] * scale);
-      o.w = pack_bf16(acc[h][6] * scale, acc[h][7] * scale);
-      *reinterpret_cast<uint4*>(out0 + (int64_t)h * ntiles * kTileBytes + off) = o;
+      uint32_t w[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float x, y;
+        unpack2(acc[h][e], x, y);
+        w[e] = pack_bf16(x, y);
+      }
+      *reinterpret_cast<uint4*>(out0 + (int64_t)h * ntiles * kTileBytes + off) = make_uint4(w[0], w[1], w[2], w[3]);
     }
   }
 }
@@ -1481,9 +1496,13 @@ cudaError_t launch_sm100(const Params& p, int variant, void* workspace, TpaKerne
   }
   if (dry_run) return cudaSuccess;
   cudaError_t e;
+  // Scratch layout: staged Q, K, V tiles first (STAGED only; the Q tiles are then at the same
+  // place whatever the key length is, which is what lets consecutive calls with other keys keep
+  // them), then the per-block key-tile ranges, then the key-split partials.
+  uint8_t* const after_tiles = static_cast<uint8_t*>(workspace) + (staged ? staged_q_bytes(p) + 2 * staged_kv_bytes(p) : 0);
   int4* seg_ranges = nullptr;
   if (p.q_seg != nullptr) {
-    seg_ranges = static_cast<int4*>(workspace);
+    seg_ranges = reinterpret_cast<int4*>(after_tiles);
     tpa_seg_ranges_kernel<<<dim3(pairs, p.batch), 128, 0, stream>>>(p, seg_ranges);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
@@ -1494,7 +1513,7 @@ cudaError_t launch_sm100(const Params& p, int variant, void* workspace, TpaKerne
   float* part_o = nullptr;
   float* part_lse = nullptr;
   if (splits > 1) {
-    part_o = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + seg_range_bytes(p));
+    part_o = reinterpret_cast<float*>(after_tiles + seg_range_bytes(p));
     part_lse = part_o + (size_t)splits * p.batch * p.lq * p.heads * p.dv;
     pk.flags = (p.flags & TPA_FLAG_CAUSAL) | TPA_FLAG_STATE_STORE;
     pk.state_o = part_o;
@@ -1502,7 +1521,7 @@ cudaError_t launch_sm100(const Params& p, int variant, void* workspace, TpaKerne
   }
   uint8_t *wq = nullptr, *wk = nullptr, *wv = nullptr;
   if (staged) {
-    wq = static_cast<uint8_t*>(workspace) + seg_range_bytes(p) + split_bytes(p);
+    wq = static_cast<uint8_t*>(workspace);
     wk = wq + staged_q_bytes(p);
     wv = wk + staged_kv_bytes(p);
     const float qscale = p.sm_scale * kLog2e / ((float)p.rank_q * (float)p.rank_k);

@@ -27,6 +27,9 @@ __all__ = ["ring_tpa", "ring_tpa_bwd", "ring_tp_self_attention", "register_axis"
 
 _AXES: dict = {}
 _side_streams: dict = {}
+# Set to a list to have _ring_overlapped append, per call, its CUDA events (entry, own shard done,
+# all hops arrived, visiting shards done) and operands; None (default) records nothing.
+_timing = None
 
 MASK_MODES = ("reference_local", "global")
 
@@ -236,14 +239,71 @@ def _gather_ring(k, v, kseg, group, size, rank):
     return kbuf, vbuf, sbuf
 
 
-def _device_parts(q, kbuf, vbuf, qs, sbuf, num_heads, sm_scale, causal, per_part, q_offset, out, lse, reuse_kv=False):
-    """One tpa_fwd call over gathered key parts (the whole ring for this rank's rows)."""
+def _device_parts(q, kbuf, vbuf, qs, sbuf, num_heads, sm_scale, causal, per_part, q_offset, out, lse, reuse_kv=False,
+                  state=None, load_state=False, store_state=False, reuse_q=False):
+    """One tpa_fwd call over gathered key parts [parts, b, l, ...] (the whole ring for this rank's
+    rows, or a share of it that starts from / leaves a carried partial in `state`)."""
     parts = kbuf.shape[0]
     if parts == 1:  # one shard: the plain call
         kbuf, vbuf, sbuf = kbuf[0], vbuf[0], sbuf[0]
     return _tpa.fwd_device(q, kbuf, vbuf, num_heads, qs, sbuf, sm_scale, causal, q_offset=q_offset, out=out, lse=lse,
                            want_lse=lse is not None, kv_parts=parts, per_part=per_part and parts > 1,
-                           reuse_staged_kv=reuse_kv)
+                           reuse_staged_kv=reuse_kv, reuse_staged_q=reuse_q, state=state, load_state=load_state,
+                           store_state=store_state)
+
+
+def _ring_overlapped(q, k, v, qseg, kseg, group, size, rank, num_heads, sm_scale, causal, return_lse, parts_fn):
+    """The reference's ring (every visiting shard under its own shard-local mask, tpa/ring_tpa.py:73-79)
+    as two attention calls: the rank's own shard at once, while all N - 1 hops are under way on the
+    side stream, then the N - 1 visiting shards in one call that starts from the first call's
+    partial (o, lse) -- the carry of tpa/ring_tpa.py:69-71, used once.  The hops are the scan's
+    neighbour sends (at hop t a rank forwards what it received at hop t - 1) into slots in arrival
+    order; with a shard-local mask the order of the shards does not matter."""
+    b, lq = q.shape[:2]
+    dv = v.shape[-1] - num_heads
+    dev = q.device
+    out = torch.empty((b, lq, num_heads, dv), dtype=q.dtype, device=dev)
+    lse = torch.empty((b, lq, num_heads), dtype=torch.float32, device=dev) if return_lse else None
+    timing = _timing is not None and q.is_cuda
+    if timing:
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        ev[0].record()
+    if size == 1:
+        parts_fn(q, k[None], v[None], qseg, kseg[None], num_heads, sm_scale, causal, False, 0, out, lse, False)
+        return (out, lse) if return_lse else out
+    kbuf = torch.empty((size - 1,) + tuple(k.shape), dtype=k.dtype, device=dev)
+    vbuf = torch.empty((size - 1,) + tuple(v.shape), dtype=v.dtype, device=dev)
+    sbuf = torch.empty((size - 1,) + tuple(kseg.shape), dtype=kseg.dtype, device=dev)
+    use_streams = q.is_cuda
+    if use_streams:
+        main = torch.cuda.current_stream(dev)
+        side = _side_streams.get(dev) or _side_streams.setdefault(dev, torch.cuda.Stream(dev))
+        side.wait_stream(main)  # k, v and the ids are ready, the buffers exist
+        ctx = torch.cuda.stream(side)
+    else:
+        import contextlib
+        ctx = contextlib.nullcontext()
+    with ctx:
+        for hop in range(1, size):
+            have = [k, v, kseg] if hop == 1 else [kbuf[hop - 2], vbuf[hop - 2], sbuf[hop - 2]]
+            for r in _rotate_block(have, [kbuf[hop - 1], vbuf[hop - 1], sbuf[hop - 1]], group, rank, size):
+                r.wait()  # the next hop forwards what this one receives
+    state = (torch.empty((b, lq, num_heads, dv), dtype=torch.float32, device=dev),
+             torch.empty((b, lq, num_heads), dtype=torch.float32, device=dev))
+    parts_fn(q, k[None], v[None], qseg, kseg[None], num_heads, sm_scale, causal, False, 0, None, None, False,
+             state=state, store_state=True)
+    if timing:
+        ev[1].record()
+    if use_streams:
+        main.wait_stream(side)
+    if timing:
+        ev[2].record()
+    parts_fn(q, kbuf, vbuf, qseg, sbuf, num_heads, sm_scale, causal, causal, 0, out, lse, False,
+             state=state, load_state=True, reuse_q=True)
+    if timing:
+        ev[3].record()
+        _timing.append({"events": ev, "operands": (q, kbuf, vbuf, qseg, sbuf, state)})
+    return (out, lse) if return_lse else out
 
 
 def _parts_supported(q, k):
@@ -253,7 +313,10 @@ def _parts_supported(q, k):
 
 
 def _ring_one_call(q, k, v, qseg, kseg, group, size, rank, num_heads, sm_scale, causal, mask_mode, return_lse, parts_fn):
-    """Ring forward as gather + one attention call (two for the balanced global mask)."""
+    """Ring forward as gather + one attention call (two for the balanced global mask); the
+    reference's shard-local mask and the unmasked ring go through _ring_overlapped instead."""
+    if not (causal and mask_mode == "global"):
+        return _ring_overlapped(q, k, v, qseg, kseg, group, size, rank, num_heads, sm_scale, causal, return_lse, parts_fn)
     b, lq = q.shape[:2]
     lk = k.shape[1]
     dv = v.shape[-1] - num_heads

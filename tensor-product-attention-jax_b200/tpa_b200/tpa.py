@@ -269,17 +269,24 @@ def fwd_device(
         ws = _workspace(q.device, nbytes)
         stream = torch.cuda.current_stream(q.device).cuda_stream
         # TPA_FLAG_REUSE_STAGED_Q / _KV are promises about the workspace's contents; keep them only
-        # when the last call that staged into this very buffer had the same operand, shapes and
-        # scale (another call on the stream, or a regrown buffer, silently voids the promise)
-        common = (tuple(q.shape), tuple(k.shape), q.dtype, num_heads, float(sm_scale), ws.data_ptr() if ws is not None else 0,
-                  nbytes, a.kernel, kv_parts, bool(per_part), None if rope is None else (rope[0].data_ptr(), rope_q_offset, rope_k_offset))
-        sig_q = common + (q.data_ptr(), q._version, tuple(q.stride()))
-        sig_kv = common + (k.data_ptr(), v.data_ptr(), tuple(k.stride()), tuple(v.stride()))
+        # when the last call on this stream ran the staged kernel into this very buffer from the
+        # same operand, shapes and scale (another call on the stream, a regrown buffer or a call
+        # that another kernel took silently voids the promise).  The staged Q tiles sit at the
+        # head of the workspace whatever the keys are, so they survive a change of k and v.
+        info = _capi.TpaKernelInfo()
+        staged = (_capi.lib.tpa_query_kernel(C.byref(a), C.byref(info)) == 0
+                  and _capi.KERNEL_NAMES.get(info.kernel) == "sm100_staged")
+        ws_ptr = ws.data_ptr() if ws is not None else 0
+        rope_sig = None if rope is None else (rope[0].data_ptr(), rope[1].data_ptr(), rope_q_offset, rope_k_offset)
+        sig_q = (q.data_ptr(), q._version, tuple(q.shape), tuple(q.stride()), q.dtype, num_heads, float(sm_scale), rank_k,
+                 ws_ptr, rope_sig) if staged else None
+        sig_kv = (k.data_ptr(), v.data_ptr(), k._version, v._version, tuple(k.shape), tuple(v.shape), tuple(k.stride()),
+                  tuple(v.stride()), q.dtype, num_heads, lq, kv_parts, bool(per_part), ws_ptr, rope_sig) if staged else None
         key = (q.device, stream)
         last_q, last_kv = _staged_q.get(key, (None, None))
-        if reuse_staged_q and last_q != sig_q:
+        if reuse_staged_q and (sig_q is None or last_q != sig_q):
             a.flags &= ~_capi.FLAG_REUSE_STAGED_Q
-        if reuse_staged_kv and last_kv != sig_kv:
+        if reuse_staged_kv and (sig_kv is None or last_kv != sig_kv):
             a.flags &= ~_capi.FLAG_REUSE_STAGED_KV
         _staged_q[key] = (sig_q, sig_kv)
         st = _capi.lib.tpa_fwd(

@@ -37,12 +37,27 @@ def oracle_block(q, k, v, qs, ks, num_heads, sm_scale, causal, q_off, k_off, sta
             lse.copy_(torch.from_numpy(l_).float())
 
 
-def oracle_parts(q, kbuf, vbuf, qs, sbuf, num_heads, sm_scale, causal, per_part, q_off, out, lse, reuse_kv):
-    """CPU stand-in for one tpa_fwd call over gathered key parts [parts, b, l, ...]."""
+def oracle_parts(q, kbuf, vbuf, qs, sbuf, num_heads, sm_scale, causal, per_part, q_off, out, lse, reuse_kv,
+                 state=None, load_state=False, store_state=False, reuse_q=False):
+    """CPU stand-in for one tpa_fwd call over gathered key parts [parts, b, l, ...], with the
+    carried partial of a ring step when asked for."""
     n, b, l = kbuf.shape[:3]
     cat = lambda x: x.transpose(0, 1).reshape(b, n * l, *x.shape[3:]).numpy()  # noqa: E731  parts side by side
     o_, l_ = orc.tpa_reference(q.numpy(), cat(kbuf), cat(vbuf), num_heads, qs.numpy(), cat(sbuf), sm_scale=sm_scale,
-                               causal=causal, q_offset=q_off, kv_parts=n, per_part=per_part, return_lse=True)
+                               causal=causal, q_offset=q_off, kv_parts=n, per_part=per_part and n > 1, return_lse=True)
+    if load_state or store_state:
+        o_ = np.nan_to_num(o_, nan=0.0)
+        if load_state:
+            so, sl = state[0].numpy().astype(np.float64), state[1].numpy().astype(np.float64)
+            ln = orc.lse_accum(sl, l_)
+            with np.errstate(invalid="ignore"):
+                o_ = np.nan_to_num(so * np.exp(sl - ln)[..., None]) + np.nan_to_num(o_ * np.exp(l_ - ln)[..., None])
+            l_ = ln
+        if store_state:
+            state[0].copy_(torch.from_numpy(o_).float())
+            state[1].copy_(torch.from_numpy(l_).float())
+            return
+        o_ = np.where(np.isneginf(l_)[..., None], np.nan, o_)
     out.copy_(torch.from_numpy(o_).to(out.dtype))
     if lse is not None:
         lse.copy_(torch.from_numpy(l_).float())
