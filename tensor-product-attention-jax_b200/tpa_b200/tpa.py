@@ -490,6 +490,89 @@ class _TpaFunction(torch.autograd.Function):
         return dq, dk, dv, None, None, None, None, None
 
 
+_copy_streams: dict = {}
+_HOST_CHUNKS = 4  # query-row chunks of the host-array path
+
+
+def _tpa_host_pipelined(q, k, v, num_heads, q_segment_ids, kv_segment_ids, sm_scale, causal, out):
+    """Host arrays in, host array out, with the copies overlapped with the kernels.
+
+    K, V (and the ids) go up first, the query rows follow in chunks on a copy stream; each chunk is
+    one tpa_fwd call (the K / V tiles staged by the first call are kept) and its rows of the
+    result go down on a second copy stream while the next chunk computes.  Copies are
+    asynchronous where the host arrays are pinned.  Returns a CPU tensor (`out` if given)."""
+    dev = torch.device("cuda", torch.cuda.current_device())
+    as_t = lambda x: torch.from_numpy(x) if isinstance(x, np.ndarray) else x  # noqa: E731
+    q, k, v = as_t(q), as_t(k), as_t(v)
+    if q.dtype not in _DTYPES or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise NotImplementedError(f"dtype {q.dtype}/{k.dtype}/{v.dtype}: float32 or bfloat16 factors only")
+    b, lq = q.shape[:2]
+    dv = v.shape[-1] - num_heads
+    if out is None:
+        out = torch.empty((b, lq, num_heads, dv), dtype=q.dtype)
+    if tuple(out.shape) != (b, lq, num_heads, dv) or out.dtype != q.dtype or out.is_cuda:
+        raise ValueError(f"out must be a CPU tensor of shape {(b, lq, num_heads, dv)} and dtype {q.dtype}")
+    # Chunks: whole batch elements when there are enough of them (their K / V go up chunk by chunk
+    # too), else blocks of query rows of the one batch element (K / V tiles staged once, kept).
+    n = _HOST_CHUNKS
+    if b >= n and b % n == 0:
+        plan = [(slice(c * (b // n), (c + 1) * (b // n)), slice(0, lq)) for c in range(n)]
+        by_batch = True
+    elif b == 1 and lq >= n * 1024 and lq % (n * 256) == 0:
+        rows = lq // n
+        # for a causal call the last rows cost the most: they go first, so that the shortest
+        # chunk is the one whose way down is not hidden behind a next one
+        order = range(n - 1, -1, -1) if causal else range(n)
+        plan = [(slice(0, 1), slice(c * rows, (c + 1) * rows)) for c in order]
+        by_batch = False
+    else:
+        plan = [(slice(0, b), slice(0, lq))]
+        by_batch = True
+    main = torch.cuda.current_stream(dev)
+    up, down = _copy_streams.get(dev) or _copy_streams.setdefault(dev, (torch.cuda.Stream(dev), torch.cuda.Stream(dev)))
+    up.wait_stream(main)
+    down.wait_stream(main)
+    put = lambda x: x.to(dev, non_blocking=x.is_pinned())  # noqa: E731
+    ids2 = lambda x: None if x is None else as_t(x)  # noqa: E731
+    hqs, hks = ids2(q_segment_ids), ids2(kv_segment_ids)
+    ops, ready, keep = [], [], []
+    with torch.cuda.stream(up):
+        dqs = None if hqs is None else hqs.to(dev)
+        dks = None if hks is None else hks.to(dev)
+        if not by_batch:
+            dk, dv_ = put(k), put(v)
+        for bs, rs in plan:
+            if by_batch:
+                dk, dv_ = put(k[bs]), put(v[bs])
+            dq = put(q[bs, rs])
+            e = torch.cuda.Event()
+            e.record(up)
+            ops.append((dq, dk, dv_))
+            ready.append(e)
+    o_dev = torch.empty((b, lq, num_heads, dv), dtype=q.dtype, device=dev)
+    for i, (bs, rs) in enumerate(plan):
+        main.wait_event(ready[i])
+        dq, dk, dv_ = ops[i]
+        # a 1-D id row is shared by the whole batch; a 2-D one is cut like its array
+        cut = lambda x, r: None if x is None else (x[r] if x.ndim == 1 else x[bs, r]).contiguous()  # noqa: E731
+        fwd_device(dq, dk, dv_, num_heads, cut(dqs, rs), cut(dks, slice(None)), sm_scale, causal, q_offset=rs.start,
+                   out=o_dev[bs, rs], want_lse=False, reuse_staged_kv=(not by_batch) and i > 0)
+        done = torch.cuda.Event()
+        done.record(main)
+        down.wait_event(done)
+        with torch.cuda.stream(down):
+            out[bs, rs].copy_(o_dev[bs, rs], non_blocking=out.is_pinned())
+    for ts in ops:  # allocated on one stream, used on another: keep the allocator from recycling them early
+        for t in ts:
+            t.record_stream(main)
+    for t in (dqs, dks):
+        if t is not None:
+            t.record_stream(main)
+    o_dev.record_stream(down)
+    down.synchronize()  # the result is a host array: complete on return
+    return out
+
+
 def tpa(
     q,
     k,
@@ -503,6 +586,8 @@ def tpa(
     nomat: bool = False,
     debug: bool = False,
     interpret: bool = False,
+    *,
+    out=None,
 ):
     """Tensor Product Attention forward; same arguments as tpa/tpa.py:73-121.
 
@@ -510,20 +595,26 @@ def tpa(
     [..., :h] and the dim factor in [..., h:]; Q, K, V are rank means of their outer
     products.  Returns o[b, lq, h, dv] in q's dtype; rows whose every key is masked are NaN.
     Host inputs (numpy / CPU tensors) are copied to the current CUDA device and the
-    result comes back as the same kind of host array.
+    result comes back as the same kind of host array; the copies overlap with the kernels
+    (see _tpa_host_pipelined), fully so when the host arrays are pinned.  `out` (keyword only,
+    not in the reference) is a CPU tensor to receive the result of a host-array call, e.g. a
+    pinned buffer that is reused from call to call.
     """
     host_kind = None
     if isinstance(q, np.ndarray):
         host_kind = "numpy"
     elif not q.is_cuda:
         host_kind = "torch"
+    if out is not None and host_kind is None:
+        raise ValueError("out= is for host-array calls; a call on CUDA tensors returns a new CUDA tensor")
     if host_kind is not None:
         if not torch.cuda.is_available():
             raise RuntimeError("tpa_b200 needs a CUDA device: there is no CPU implementation")
-        dev = torch.device("cuda", torch.cuda.current_device())
-        q, k, v = (_to_device(x, dev) for x in (q, k, v))
-        q_segment_ids = _to_device(q_segment_ids, dev)
-        kv_segment_ids = _to_device(kv_segment_ids, dev)
+        _tpa_fwd_checks(q, k, block_sizes)
+        o = _tpa_host_pipelined(q, k, v, num_heads, q_segment_ids, kv_segment_ids, sm_scale, causal, out)
+        if host_kind == "numpy":
+            return o.float().numpy() if o.dtype == torch.bfloat16 else o.numpy()
+        return o
     if host_kind is None and torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad):
         _tpa_fwd_checks(q, k, block_sizes)
         return _TpaFunction.apply(q, k, v, num_heads, q_segment_ids, kv_segment_ids, sm_scale, causal)
@@ -541,10 +632,6 @@ def tpa(
         debug=debug,
         interpret=interpret,
     )
-    if host_kind == "numpy":
-        return o.float().cpu().numpy() if o.dtype == torch.bfloat16 else o.cpu().numpy()
-    if host_kind == "torch":
-        return o.cpu()
     return o
 
 

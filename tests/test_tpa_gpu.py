@@ -84,6 +84,34 @@ def test_host_arrays_round_trip():
     assert np.max(np.abs(o - orc.tpa_reference(q, k, v, 4, sm_scale=0.25, causal=True))) <= 1e-5
 
 
+@pytest.mark.parametrize("b,t,seg,causal,pinned", [(1, 4096, 0, True, True), (1, 4096, 700, True, False),
+                                                   (4, 1024, 0, False, True), (8, 512, 100, True, True),
+                                                   (3, 512, 0, True, True)])
+def test_host_arrays_pipelined(b, t, seg, causal, pinned):
+    """Host tensors through tpa(): the call moves them in chunks (query-row blocks of one batch
+    element, or batch elements) while it computes, and gives the device call's result (to bf16
+    rounding: a chunk of few rows may split its keys over CTAs and merge partials)."""
+    h, d = 8, 64
+    q, k, v = orc.make_factors(6, b, t, t, 3, 2, h, d, d)
+    hq, hk, hv = (torch.from_numpy(x).bfloat16() for x in (q, k, v))
+    ids = torch.from_numpy(orc.segment_ids(b, t, seg)) if seg else None
+    if pinned:
+        hq, hk, hv = hq.pin_memory(), hk.pin_memory(), hv.pin_memory()
+    out = torch.empty((b, t, h, d), dtype=torch.bfloat16)
+    out = out.pin_memory() if pinned else out
+    got = tpa_b200.tpa.tpa(hq, hk, hv, h, ids, ids, sm_scale=d**-0.5, causal=causal, out=out)
+    assert got is out and not got.is_cuda
+    dq, dk, dv_ = hq.cuda(), hk.cuda(), hv.cuda()
+    did = None if ids is None else ids.cuda()
+    want = tpa_b200.tpa.tpa(dq, dk, dv_, h, did, did, sm_scale=d**-0.5, causal=causal)
+    assert torch.equal(torch.isnan(got), torch.isnan(want.cpu()))
+    assert (torch.nan_to_num(got.float()) - torch.nan_to_num(want.float().cpu())).abs().max() <= 2e-3
+    fresh = tpa_b200.tpa.tpa(hq, hk, hv, h, ids, ids, sm_scale=d**-0.5, causal=causal)  # no out=: a new host tensor
+    assert torch.equal(torch.nan_to_num(fresh.float()), torch.nan_to_num(got.float()))
+    with pytest.raises(ValueError):
+        tpa_b200.tpa.tpa(dq, dk, dv_, h, sm_scale=1.0, out=out)
+
+
 @pytest.mark.parametrize("shape", [(1, 100, 77, 3, 2, 3, 7, 9), (2, 33, 200, 1, 5, 5, 20, 130), (1, 64, 64, 2, 2, 2, 256, 256)])
 @pytest.mark.parametrize("causal", [False, True])
 def test_ragged_shapes_low_level(shape, causal):
