@@ -43,9 +43,16 @@ WORKLOADS = {
 }
 METRIC = "TPA forward throughput (algorithmic attention FLOPs 4*B*h*d*pairs per second; tokens/s beside it)"
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
-# captures summarised under profiles/ (bytes; None until a capture for that workload exists)
-NCU_TRAFFIC = {"c2": 1231663104 + 264633856}  # attention kernel at full size, profiles/c2_launch_list.md
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu capture
+# summarised in profiles/tpa_fwd_sm100_staged_c2_T8192.md: taken on the T = 8192 case of the c2 shape
+# (305.8 MB read + 62.9 MB written) and scaled by the sequence length, with which every byte the
+# attention kernel moves grows in proportion (see profiles/c2_launch_list.md).
+NCU_T8192_BYTES = 305767424 + 62907648
+
+
+def ncu_traffic(name, t):
+    """Scaled DRAM traffic per attention launch, for the shape the capture was taken on only."""
+    return NCU_T8192_BYTES * t // 8192 if name.split("@")[0] == "c2" else None
 
 
 def flops(b, t, h, d, causal):
@@ -456,6 +463,35 @@ def main():
     value = fl / (ms * 1e-3) / 1e12
     toks = b * t / (ms * 1e-3)
 
+    # ------------------------------------------------------------- configuration 4's dense-attention arm
+    dense_arm = None
+    if name.split("@")[0] == "c4" and not ring and not bwd and args.lq is None:
+        # the same Q, K, V materialised (fp32 rank mean of the bf16 factors, one bf16 rounding -- what the
+        # staging kernel produces) and run as dense attention through the library's mha(), timed the same way
+        def dense(x, r_):
+            xf = x.float()
+            return (torch.einsum("blrh,blrd->blhd", xf[..., :h], xf[..., h:]) / r_).to(q.dtype)
+
+        mq, mk, mv = dense(q, rq), dense(k, rk), dense(v, rk)
+        run_dense = lambda: tpa_b200.mha.mha(mq, mk, mv, sm_scale=sm_scale, causal=causal)  # noqa: E731
+        od = run_dense()
+        for _ in range(max(args.warmup, 3)):
+            run_dense()
+        torch.cuda.synchronize(device)
+        d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        d0.record()
+        for _ in range(args.steps):
+            run_dense()
+        d1.record()
+        torch.cuda.synchronize(device)
+        d_ms = d0.elapsed_time(d1) / args.steps
+        fo = last if not isinstance(last, tuple) else last[0]
+        dense_arm = {"ms_per_step": d_ms, "value": fl / (d_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                     "max_abs_vs_factored": float((od.float() - fo.float()).abs().max()),
+                     "what": "mha() of tpa/mha.py:10-37 on the materialised Q, K, V: the same kernels with "
+                             "one-hot head factors of rank h; the difference to the factored call is the staging pass"}
+        del mq, mk, mv, od
+
     # ------------------------------------------------------------- end to end on pinned host arrays
     e2e = None
     if not args.no_e2e and not bwd and args.lq is None:
@@ -600,7 +636,7 @@ def main():
         info = dict(info, kernel="bwd:" + ("simt" if args.kernel == "simt" or info["kernel"] == "simt" else "sm100"))
     roofline = {"bound": "tensor", "achieved": achieved, "peak": burst, "unit": "TFLOP/s", "frac": achieved / burst,
                 "frac_of_sustained": achieved / sustained if sustained else None, "peak_source": src,
-                "traffic": None if bwd else NCU_TRAFFIC.get(name), "kernel": info["kernel"],
+                "traffic": None if bwd else ncu_traffic(name, t), "kernel": info["kernel"],
                 "hbm_algorithmic_bytes": sum(x.numel() * x.element_size() for x in (q, k, v))
                 + b * q.shape[1] * h * d * q.element_size() + b * q.shape[1] * h * 4,
                 "hbm_peak_gbs": hbm}
@@ -626,6 +662,8 @@ def main():
         "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clock_summary,
         "parity": parity,
     }
+    if dense_arm is not None:
+        line["dense_cross_check"] = dense_arm
     if n1_ms is not None:
         # strong scaling on one box: the unsharded workload on one GPU against N GPUs
         line["ring"] = {"n1_ms": n1_ms, "ring_efficiency": n1_ms / (world * ms), "mask_mode": args.mask_mode,

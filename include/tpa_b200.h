@@ -69,9 +69,11 @@ enum {
   TPA_FLAG_STATE_STORE = 4, /* write the merged partial back to state_o / state_lse
                                (tpa/ring_tpa.py:82-91) instead of the final o / lse            */
   TPA_FLAG_REUSE_STAGED_Q = 8,/* the workspace is the one the previous call used, with the same
-                               q operand, sm_scale, ranks and shapes (the ring scan keeps q
-                               fixed, tpa/ring_tpa.py:73-79): the STAGED variant then skips
-                               re-staging Q.  Ignored by the other kernels.                    */
+                               q operand, sm_scale, ranks, heads, batch and lq (the ring scan keeps
+                               q fixed, tpa/ring_tpa.py:73-79): the STAGED variant then skips
+                               re-staging Q.  The staged Q tiles sit right behind the status block
+                               whatever the keys are, so k, v and lk may differ from the previous
+                               call's.  Ignored by the other kernels.                          */
   TPA_FLAG_REUSE_STAGED_KV = 32,/* likewise for the K and V tiles: same k, v operands, ranks, lk and
                                lq as the previous call on this workspace (two query chunks of
                                one rank against the same gathered keys); STAGED only          */

@@ -235,7 +235,7 @@ __device__ __forceinline__ void rebuild_tile(uint8_t* dst, const __nv_bfloat16* 
 // grid = (heads/8, lq/128 + 2 * lk/128, batch), 256 threads: the head groups of one tile are
 // adjacent in launch order, so the factor rows they share are read from HBM once.
 template <int D>
-__global__ void __launch_bounds__(256) tpa_stage_tiles_kernel(const Params p, uint8_t* ws_q,
+__global__ void __launch_bounds__(256, 2) tpa_stage_tiles_kernel(const Params p, uint8_t* ws_q,
                                                               uint8_t* ws_k, uint8_t* ws_v,
                                                               float qscale, int first_tile) {
   constexpr int CH = D / 8;
