@@ -185,7 +185,7 @@ size_t tpa_fwd_workspace_bytes(const TpaFwdArgs* args) {
   Params p;
   int kernel;
   if (validate(args, &p) != TPA_OK || choose(args, p, &kernel) != TPA_OK) return 0;
-  if (kernel == TPA_KERNEL_SIMT) return 0;
+  if (kernel == TPA_KERNEL_SIMT) return simt_workspace_bytes(p) ? kStatusBytes + simt_workspace_bytes(p) : 0;
   if (kernel == TPA_KERNEL_DECODE) return kStatusBytes + decode_workspace_bytes(p);
   return kStatusBytes + sm100_workspace_bytes(p, kernel);
 }
@@ -201,7 +201,7 @@ int tpa_query_kernel(const TpaFwdArgs* args, TpaKernelInfo* info) {
   if (st != TPA_OK) return st;
   cudaError_t e = kernel == TPA_KERNEL_DECODE ? launch_decode(p, nullptr, info, true, nullptr)
                   : kernel != TPA_KERNEL_SIMT ? launch_sm100(p, kernel, nullptr, info, true, nullptr)
-                                              : launch_simt(p, info, true, nullptr);
+                                              : launch_simt(p, nullptr, info, true, nullptr);
   return e == cudaSuccess ? TPA_OK : fail_cuda(e);
 }
 
@@ -227,7 +227,15 @@ int tpa_fwd(const TpaFwdArgs* args, void* workspace, size_t workspace_bytes, voi
             ? launch_decode(p, static_cast<char*>(workspace) + kStatusBytes, nullptr, false, s)
             : launch_sm100(p, kernel, static_cast<char*>(workspace) + kStatusBytes, nullptr, false, s);
   } else {
-    e = launch_simt(p, nullptr, false, s);
+    const size_t need = simt_workspace_bytes(p);
+    if (need != 0 && (workspace == nullptr || workspace_bytes < kStatusBytes + need ||
+                      (reinterpret_cast<uintptr_t>(workspace) & 255) != 0))
+      return TPA_ERR_WORKSPACE;
+    if (need != 0) {
+      e = cudaMemsetAsync(workspace, 0, kStatusBytes, s);
+      if (e != cudaSuccess) return fail_cuda(e);
+    }
+    e = launch_simt(p, need ? static_cast<char*>(workspace) + kStatusBytes : nullptr, nullptr, false, s);
   }
   return e == cudaSuccess ? TPA_OK : fail_cuda(e);
 }

@@ -109,7 +109,10 @@ cudaError_t launch_stage_tiles(const Params& p, uint8_t* wq, uint8_t* wk, uint8_
                                cudaStream_t stream);
 
 // Launchers: enqueue on `stream`, return a cudaError_t.  `info` is filled either way.
-cudaError_t launch_simt(const Params& p, TpaKernelInfo* info, bool dry_run, cudaStream_t stream);
+// `workspace` holds simt_workspace_bytes(p) (0 unless the key tiles are split over CTAs)
+cudaError_t launch_simt(const Params& p, void* workspace, TpaKernelInfo* info, bool dry_run, cudaStream_t stream);
+int simt_pick_splits(const Params& p);
+size_t simt_workspace_bytes(const Params& p);
 bool sm100_supported(const Params& p);
 int sm100_pick_variant(const Params& p);  // TPA_KERNEL_SM100_FUSED or TPA_KERNEL_SM100_STAGED
 size_t sm100_workspace_bytes(const Params& p, int variant);

@@ -37,17 +37,37 @@ __device__ __forceinline__ void rebuild_tile(float* dst, int ld, int rows, int r
                                              const T* bfac, const int64_t* bs, int rank, int h,
                                              float inv_rank, int tid) {
   // dst[r][t] = inv_rank * sum_rho a[row0+r, rho, h] * b[row0+r, rho, t]; zero past row_end/cols.
-  for (int idx = tid; idx < rows * ld; idx += SIMT_THREADS) {
-    const int r = idx / ld, t = idx - r * ld;
-    const int row = row0 + r;
-    float acc = 0.f;
-    if (row < row_end && t < cols) {
-      const T* ap = a + (int64_t)row * as[1] + h;
-      const T* bp = bfac + (int64_t)row * bs[1] + t;
-      for (int rho = 0; rho < rank; ++rho)
-        acc = fmaf(to_float(ap[rho * as[2]]), to_float(bp[rho * bs[2]]), acc);
+  // A thread keeps one column (mod 64) and takes four rows at a time: their 2 * rank factor loads
+  // are independent and in flight together (one element after the other, each waiting for its
+  // own loads, this rebuild was most of the kernel's time at short sequence lengths).  The sum
+  // over rho runs in the same order for every element, whatever the grouping.
+  constexpr int CW = 64, RS = SIMT_THREADS / CW, U = 4;
+  const int tc = tid & (CW - 1), tr = tid / CW;
+  for (int t = tc; t < ld; t += CW) {
+    const bool col_ok = t < cols;
+    for (int r = tr; r < rows; r += RS * U) {
+      float acc[U];
+      const T* ap[U];
+      const T* bp[U];
+      bool ok[U];
+#pragma unroll
+      for (int i = 0; i < U; ++i) {
+        const int ri = r + i * RS, row = row0 + ri;
+        ok[i] = col_ok && ri < rows && row < row_end;
+        const int64_t safe = ok[i] ? row : row0;  // a valid row: the pointers are only read when ok
+        ap[i] = a + safe * as[1] + h;
+        bp[i] = bfac + safe * bs[1] + (col_ok ? t : 0);
+        acc[i] = 0.f;
+      }
+      for (int rho = 0; rho < rank; ++rho) {
+#pragma unroll
+        for (int i = 0; i < U; ++i)
+          if (ok[i]) acc[i] = fmaf(to_float(ap[i][rho * as[2]]), to_float(bp[i][rho * bs[2]]), acc[i]);
+      }
+#pragma unroll
+      for (int i = 0; i < U; ++i)
+        if (r + i * RS < rows) dst[(r + i * RS) * ld + t] = acc[i] * inv_rank;
     }
-    dst[idx] = acc * inv_rank;
   }
 }
 
@@ -67,7 +87,7 @@ __device__ __forceinline__ void rope_tile(float* dst, int ld, int rows, int cols
 
 template <typename T, int JJ>
 __global__ void __launch_bounds__(SIMT_THREADS)
-tpa_fwd_simt_kernel(const Params p) {
+tpa_fwd_simt_kernel(const Params p, const int splits) {
   extern __shared__ float smem[];
   const int dk = p.dk, dv = p.dv;
   const int ldk = dk + 1;       // +1: rows of K land in different banks
@@ -78,7 +98,13 @@ tpa_fwd_simt_kernel(const Params p) {
   float* Ps = Vs + SIMT_BK * ldv;       // [BQ][BK]
   int* ksegs = reinterpret_cast<int*>(Ps + SIMT_BQ * SIMT_BK);  // [BK]
 
-  const int q0 = blockIdx.x * SIMT_BQ, h = blockIdx.y, b = blockIdx.z;
+  // grid.z = batch * splits: with key splits (few row blocks against many keys) this CTA walks only
+  // its share of the visible tiles and leaves a partial (o, lse) in its slice of the scratch, which
+  // tpa_combine_splits_kernel merges as a ring merges steps; the host has then set STATE_STORE
+  const int q0 = blockIdx.x * SIMT_BQ, h = blockIdx.y, b = blockIdx.z / splits, split = blockIdx.z % splits;
+  const int64_t split_rows = (int64_t)split * p.batch * p.lq * p.heads;
+  float* const st_o = p.state_o + split_rows * p.dv;
+  float* const st_lse = p.state_lse + split_rows;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const bool causal = (p.flags & TPA_FLAG_CAUSAL) != 0;
   const bool has_seg = p.q_seg != nullptr;
@@ -117,14 +143,14 @@ tpa_fwd_simt_kernel(const Params p) {
     for (int jj = 0; jj < JJ; ++jj) acc[i][jj] = 0.f;
     if (load_state && live) {
       const int64_t rh = ((int64_t)b * p.lq + row) * p.heads + h;
-      const float prev = p.state_lse[rh];
+      const float prev = st_lse[rh];
       if (prev != -CUDART_INF_F) {
         m[i] = prev;
         l[i] = 1.f;
 #pragma unroll
         for (int jj = 0; jj < JJ; ++jj) {
           const int j = lane + 32 * jj;
-          if (j < dv) acc[i][jj] = p.state_o[rh * dv + j];
+          if (j < dv) acc[i][jj] = st_o[rh * dv + j];
         }
       }
     }
@@ -146,8 +172,14 @@ tpa_fwd_simt_kernel(const Params p) {
   const int64_t q_lo = (int64_t)q0 + p.q_offset, q_hi = q_lo + SIMT_BQ - 1;
   const int64_t span = rule.span;
 
+  int tile_begin = 0, tile_end = n_tiles;
+  if (splits > 1) {
+    const int chunk = (n_tiles + splits - 1) / splits;
+    tile_begin = min(n_tiles, split * chunk);
+    tile_end = min(n_tiles, tile_begin + chunk);
+  }
   const float inv_rk = 1.f / (float)p.rank_k;
-  for (int tile = 0; tile < n_tiles; ++tile) {
+  for (int tile = tile_begin; tile < tile_end; ++tile) {
     const int k0 = tile * SIMT_BK;
     // a tile (it lies in one part: parts are multiples of the tile) no row of the block can see
     const int64_t kp_lo = (int64_t)(p.per_part ? k0 % p.part_len : k0) + p.k_offset, kp_hi = kp_lo + SIMT_BK - 1;
@@ -183,7 +215,8 @@ tpa_fwd_simt_kernel(const Params p) {
     const float* k0p = Ks + lane * ldk;
     const float* k1p = Ks + (lane + 32) * ldk;
     const float* qp = Qs + warp * SIMT_RPW * ldk;
-    for (int t = 0; t < dk; ++t) {
+#pragma unroll 8
+    for (int t = 0; t < dk; ++t) {  // unrolled: eight steps' shared-memory loads are in flight together
       const float ka0 = k0p[t], ka1 = k1p[t];
 #pragma unroll
       for (int i = 0; i < SIMT_RPW; ++i) {
@@ -226,6 +259,7 @@ tpa_fwd_simt_kernel(const Params p) {
 
     // acc += P V : this lane owns value columns lane + 32*jj
     const float* pp = Ps + warp * SIMT_RPW * SIMT_BK;
+#pragma unroll 8
     for (int c = 0; c < SIMT_BK; ++c) {
       float vv[JJ];
 #pragma unroll
@@ -253,9 +287,9 @@ tpa_fwd_simt_kernel(const Params p) {
 #pragma unroll
       for (int jj = 0; jj < JJ; ++jj) {
         const int j = lane + 32 * jj;
-        if (j < dv) p.state_o[rh * dv + j] = acc[i][jj] * inv;
+        if (j < dv) st_o[rh * dv + j] = acc[i][jj] * inv;
       }
-      if (lane == 0) p.state_lse[rh] = lse;
+      if (lane == 0) st_lse[rh] = lse;
     } else {
       T* op = static_cast<T*>(p.o) + rh * dv;
 #pragma unroll
@@ -269,13 +303,40 @@ tpa_fwd_simt_kernel(const Params p) {
   }
 }
 
+// Few row blocks against enough keys leave most of the GPU idle and every CTA latency-bound on a
+// serial walk (fp32 c0: 128 CTAs of up to 8 tiles): the key tiles are then split over several CTAs
+// per block and the partials merged, as the tensor-core kernel does for decode-like shapes.
+int simt_pick_splits(const Params& p) {
+  if (p.dv % 4 != 0 || p.kv_parts > 1 || p.has_window()) return 1;
+  // the merge kernel moves 16 bytes at a time
+  auto aligned16 = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; };
+  if (!(p.flags & TPA_FLAG_STATE_STORE) && !aligned16(p.o)) return 1;
+  if ((p.flags & (TPA_FLAG_STATE_STORE | TPA_FLAG_STATE_LOAD)) && !aligned16(p.state_o)) return 1;
+  const int64_t items = (int64_t)((p.lq + SIMT_BQ - 1) / SIMT_BQ) * p.heads * p.batch;
+  const int n_kv = (p.lk + SIMT_BK - 1) / SIMT_BK;
+  if (items > 2 * 148 || n_kv < 4) return 1;
+  int splits = (int)((4 * 148 + items - 1) / items);
+  if (splits > n_kv / 2) splits = n_kv / 2;
+  if (splits > 16) splits = 16;
+  if ((int64_t)p.batch * splits > 65535) return 1;
+  return splits < 2 ? 1 : splits;
+}
+
+size_t simt_workspace_bytes(const Params& p) {
+  const int splits = simt_pick_splits(p);
+  if (splits == 1) return 0;
+  const size_t bytes = (size_t)splits * p.batch * p.lq * p.heads * (p.dv + 1) * sizeof(float);
+  return (bytes + 255) & ~(size_t)255;
+}
+
 template <typename T, int JJ>
-static cudaError_t launch_one(const Params& p, TpaKernelInfo* info, bool dry_run,
+static cudaError_t launch_one(const Params& p, void* workspace, TpaKernelInfo* info, bool dry_run,
                               cudaStream_t stream) {
   const int ldk = p.dk + 1, ldv = JJ * 32;
   const size_t smem = sizeof(float) * ((size_t)SIMT_BQ * ldk + (size_t)SIMT_BK * ldk +
                                        (size_t)SIMT_BK * ldv + SIMT_BQ * SIMT_BK + SIMT_BK);
-  dim3 grid((p.lq + SIMT_BQ - 1) / SIMT_BQ, p.heads, p.batch);
+  const int splits = simt_pick_splits(p);
+  dim3 grid((p.lq + SIMT_BQ - 1) / SIMT_BQ, p.heads, p.batch * splits);
   if (info) {
     info->kernel = TPA_KERNEL_SIMT;
     info->block_q = SIMT_BQ;
@@ -285,28 +346,41 @@ static cudaError_t launch_one(const Params& p, TpaKernelInfo* info, bool dry_run
     info->grid[1] = grid.y;
     info->grid[2] = grid.z;
     info->smem_bytes = (int)smem;
-    info->launches = 1;
+    info->launches = splits > 1 ? 2 : 1;
   }
   if (dry_run) return cudaSuccess;
+  // with key splits the kernel stores partials (as a ring step would) into scratch
+  Params pk = p;
+  float* part_o = nullptr;
+  float* part_lse = nullptr;
+  if (splits > 1) {
+    part_o = static_cast<float*>(workspace);
+    part_lse = part_o + (size_t)splits * p.batch * p.lq * p.heads * p.dv;
+    pk.flags = (p.flags & ~(uint32_t)TPA_FLAG_STATE_LOAD) | TPA_FLAG_STATE_STORE;
+    pk.state_o = part_o;
+    pk.state_lse = part_lse;
+  }
   auto kern = tpa_fwd_simt_kernel<T, JJ>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
-  kern<<<grid, SIMT_THREADS, smem, stream>>>(p);
+  kern<<<grid, SIMT_THREADS, smem, stream>>>(pk, splits);
   count_launch(1);
-  return cudaGetLastError();
+  e = cudaGetLastError();
+  if (e != cudaSuccess || splits == 1) return e;
+  return launch_combine_splits(p, part_o, part_lse, splits, stream);
 }
 
 template <typename T>
-static cudaError_t launch_t(const Params& p, TpaKernelInfo* info, bool dry, cudaStream_t s) {
-  if (p.dv <= 32) return launch_one<T, 1>(p, info, dry, s);
-  if (p.dv <= 64) return launch_one<T, 2>(p, info, dry, s);
-  if (p.dv <= 128) return launch_one<T, 4>(p, info, dry, s);
-  return launch_one<T, 8>(p, info, dry, s);
+static cudaError_t launch_t(const Params& p, void* ws, TpaKernelInfo* info, bool dry, cudaStream_t s) {
+  if (p.dv <= 32) return launch_one<T, 1>(p, ws, info, dry, s);
+  if (p.dv <= 64) return launch_one<T, 2>(p, ws, info, dry, s);
+  if (p.dv <= 128) return launch_one<T, 4>(p, ws, info, dry, s);
+  return launch_one<T, 8>(p, ws, info, dry, s);
 }
 
-cudaError_t launch_simt(const Params& p, TpaKernelInfo* info, bool dry_run, cudaStream_t stream) {
-  if (p.dtype == TPA_DTYPE_F32) return launch_t<float>(p, info, dry_run, stream);
-  return launch_t<__nv_bfloat16>(p, info, dry_run, stream);
+cudaError_t launch_simt(const Params& p, void* workspace, TpaKernelInfo* info, bool dry_run, cudaStream_t stream) {
+  if (p.dtype == TPA_DTYPE_F32) return launch_t<float>(p, workspace, info, dry_run, stream);
+  return launch_t<__nv_bfloat16>(p, workspace, info, dry_run, stream);
 }
 
 }  // namespace tpa

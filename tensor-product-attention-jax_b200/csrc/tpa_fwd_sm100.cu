@@ -1371,10 +1371,15 @@ __global__ void __launch_bounds__(256) tpa_combine_splits_kernel(const Params p,
           make_float4(acc[i].x * inv, acc[i].y * inv, acc[i].z * inv, acc[i].w * inv);
     } else {
       const float q = none ? CUDART_NAN_F : 1.f;  // rows that saw no key are NaN (tpa/tpa.py:439)
-      uint2 o;
-      o.x = pack_bf16(acc[i].x * inv * q, acc[i].y * inv * q);
-      o.y = pack_bf16(acc[i].z * inv * q, acc[i].w * inv * q);
-      *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(p.o) + rh * d + c * 4) = o;
+      if (p.dtype == TPA_DTYPE_F32) {  // the generic kernel's partials
+        *reinterpret_cast<float4*>(static_cast<float*>(p.o) + rh * d + c * 4) =
+            make_float4(acc[i].x * inv * q, acc[i].y * inv * q, acc[i].z * inv * q, acc[i].w * inv * q);
+      } else {
+        uint2 o;
+        o.x = pack_bf16(acc[i].x * inv * q, acc[i].y * inv * q);
+        o.y = pack_bf16(acc[i].z * inv * q, acc[i].w * inv * q);
+        *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(p.o) + rh * d + c * 4) = o;
+      }
     }
   }
   if (lane == 0) {

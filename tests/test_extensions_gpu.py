@@ -77,7 +77,12 @@ def test_parts_in_sequence_order_equal_one_array(kernel, dtype):
     want, wl = tpa_b200.tpa.fwd_device(tq, tk, tv, h, None, None, 0.2, True, q_offset=2 * l, kernel=kernel)
     got, gl = tpa_b200.tpa.fwd_device(tq, _parts(tk, n), _parts(tv, n), h, None, None, 0.2, True, q_offset=2 * l,
                                       kv_parts=n, kernel=kernel)
-    assert torch.equal(want, got) and torch.equal(wl, gl)
+    # the same tiles in the same order on the tensor-core path; the generic kernel may split the keys
+    # of the plain call over CTAs and merge partials, which rounds differently
+    if kernel == "simt":
+        assert (want - got).abs().max() <= 1e-6 and (wl - gl).abs().max() <= 1e-5
+    else:
+        assert torch.equal(want, got) and torch.equal(wl, gl)
 
 
 WINDOWS = [  # lq, lk, causal, window, dilation, q_off, k_off
