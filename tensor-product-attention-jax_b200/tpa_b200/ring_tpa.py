@@ -531,6 +531,81 @@ def _device_bwd_block(q, k, v, qs, ks, num_heads, sm_scale, causal, q_offset, k_
                     accumulate_dq=accumulate_dq, accumulate_dkv=True)
 
 
+def _ring_bwd_global_zigzag(q, k, v, qseg, kseg, o, lse, do, group, size, rank, num_heads, sm_scale, block):
+    """Backward of causal attention over the whole sequence with balanced ranks.
+
+    With contiguous shards rank r would run r + 1 of the N key blocks (efficiency bound 0.53 at
+    N = 8).  As in the forward (_ring_global_zigzag), the sequence is cut into 2N chunks and rank
+    r takes chunks r (early) and 2N-1-r (late): the rows of q, o, lse, do and their ids, and the
+    K/V factors of those chunks, are re-dealt that way first.  The K/V chunks of every rank then
+    ring-rotate together with their fp32 dk / dv accumulators (tpa/ring_tpa.py:147-160); each
+    step costs two chunk-by-chunk block backwards on every rank (late queries against the
+    visiting early chunk always; against the visiting late chunk, or the early queries against
+    the visiting early chunk, as positions allow).  After N rotations the accumulators are back
+    with the rank that dealt them, and dq, dk, dv travel back to the ranks that own those rows.
+    """
+    b, lq = q.shape[:2]
+    if lq % 2 != 0 or k.shape[1] != lq:
+        raise AssertionError("the balanced global mask needs equal, even shard lengths")
+    c = lq // 2
+    f32 = torch.float32
+    mine = [2 * rank, 2 * rank + 1]            # chunks this rank holds on entry
+    want = [rank, 2 * size - 1 - rank]         # chunks it works on (early, late)
+    holder = lambda ch: ch // 2                # noqa: E731  rank that holds chunk `ch` on entry
+
+    def halves(x):
+        return [x[:, :c].contiguous(), x[:, c:].contiguous()]
+
+    per_row = (q, k, v, qseg, kseg, o, lse, do)
+    src = {ch: [h[i] for h in map(halves, per_row)] for i, ch in enumerate(mine)}
+    got = {ch: [torch.empty_like(t) for t in src[mine[0]]] for ch in want}
+    send = sorted(((_zigzag_owner(ch, size), ch) for ch in mine), key=lambda x: x[1])
+    recv = sorted(((holder(ch), ch) for ch in want), key=lambda x: x[1])
+    _exchange_chunks([(peer, src[ch]) for peer, ch in send], [(peer, got[ch]) for peer, ch in recv], group, rank)
+    (q_e, k_e, v_e, qs_e, ks_e, o_e, l_e, do_e), (q_l, k_l, v_l, qs_l, ks_l, o_l, l_l, do_l) = got[want[0]], got[want[1]]
+
+    dq_e = torch.zeros(q_e.shape, dtype=f32, device=q.device)
+    dq_l = torch.zeros(q_l.shape, dtype=f32, device=q.device)
+    # the travelling bundle: factors and ids of (early, late) chunk, and their gradient accumulators
+    cur = [k_e, v_e, ks_e, k_l, v_l, ks_l]
+    acc = [torch.zeros(t.shape, dtype=f32, device=q.device) for t in (k_e, v_e, k_l, v_l)]
+    spare = [torch.empty_like(t) for t in cur]
+    acc_spare = [torch.empty_like(t) for t in acc]
+    started_e = started_l = False
+    pos_e, pos_l = rank * c, (2 * size - 1 - rank) * c          # positions of this rank's query chunks
+    for s in range(size):
+        origin = (rank - s) % size  # the rank whose chunks (origin, 2N-1-origin) are visiting
+        ke, ve, se, kl, vl, sl = cur
+        # late queries against the visiting early chunk: always wholly visible
+        block(q_l, ke, ve, qs_l, se, num_heads, sm_scale, False, 0, 0, o_l, l_l, do_l, (dq_l, acc[0], acc[1]), started_l)
+        started_l = True
+        if origin > rank:      # ... and against the visiting late chunk, which lies before theirs
+            block(q_l, kl, vl, qs_l, sl, num_heads, sm_scale, False, 0, 0, o_l, l_l, do_l, (dq_l, acc[2], acc[3]), True)
+        elif origin == rank:   # their own chunk: the diagonal
+            block(q_l, kl, vl, qs_l, sl, num_heads, sm_scale, True, pos_l, pos_l, o_l, l_l, do_l, (dq_l, acc[2], acc[3]), True)
+        # early queries see early chunks of ranks <= this one only
+        if origin <= rank:
+            block(q_e, ke, ve, qs_e, se, num_heads, sm_scale, origin == rank, pos_e, origin * c, o_e, l_e, do_e,
+                  (dq_e, acc[0], acc[1]), started_e)
+            started_e = True
+        if size > 1:  # factors and accumulators move on together, every step, so that they end at home
+            for r in _rotate_block(cur + acc, spare + acc_spare, group, rank, size):
+                r.wait()
+            cur, spare = spare, cur
+            acc, acc_spare = acc_spare, acc
+    # home again: acc holds the gradients of this rank's (early, late) K/V chunks; everything goes
+    # back to the ranks that own those rows
+    outs = {want[0]: [dq_e, acc[0], acc[1]], want[1]: [dq_l, acc[2], acc[3]]}
+    back_send = sorted(((holder(ch), ch, ts) for ch, ts in outs.items()), key=lambda x: x[1])
+    back_recv = sorted(((_zigzag_owner(ch, size), ch) for ch in mine), key=lambda x: x[1])
+    tmp = {ch: [torch.empty_like(t) for t in outs[want[0]]] for _, ch in back_recv}
+    _exchange_chunks([(peer, ts) for peer, _, ts in back_send], [(peer, tmp[ch]) for peer, ch in back_recv], group, rank)
+    dq = torch.cat([tmp[mine[0]][0], tmp[mine[1]][0]], 1).to(q.dtype)
+    dk = torch.cat([tmp[mine[0]][1], tmp[mine[1]][1]], 1).to(k.dtype)
+    dv = torch.cat([tmp[mine[0]][2], tmp[mine[1]][2]], 1).to(v.dtype)
+    return dq, dk, dv
+
+
 def ring_tpa_bwd(
     q,
     k,
@@ -571,6 +646,9 @@ def ring_tpa_bwd(
     kseg = kv_segment_ids.to(torch.int32).contiguous()
     qseg = q_segment_ids.to(torch.int32).contiguous()
     f32 = torch.float32
+    if causal and mask_mode == "global" and size > 1 and lq == lk and lq % 2 == 0:
+        return _ring_bwd_global_zigzag(q, k.contiguous(), v.contiguous(), qseg, kseg, o, lse.to(f32), do, group, size,
+                                       rank, num_heads, sm_scale, block)
     dq = torch.zeros(q.shape, dtype=f32, device=q.device)
     cur = [k.contiguous(), v.contiguous(), kseg]
     acc = [torch.zeros(k.shape, dtype=f32, device=q.device), torch.zeros(v.shape, dtype=f32, device=q.device)]
