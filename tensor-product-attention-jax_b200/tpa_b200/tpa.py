@@ -491,7 +491,7 @@ class _TpaFunction(torch.autograd.Function):
 
 
 _copy_streams: dict = {}
-_HOST_CHUNKS = 4  # query-row chunks of the host-array path
+_HOST_CHUNKS = 4  # chunks of the host-array path (batch elements, or query-row blocks of one); eight measured no better
 
 
 def _tpa_host_pipelined(q, k, v, num_heads, q_segment_ids, kv_segment_ids, sm_scale, causal, out):
@@ -515,7 +515,9 @@ def _tpa_host_pipelined(q, k, v, num_heads, q_segment_ids, kv_segment_ids, sm_sc
     # Chunks: whole batch elements when there are enough of them (their K / V go up chunk by chunk
     # too), else blocks of query rows of the one batch element (K / V tiles staged once, kept).
     n = _HOST_CHUNKS
-    if b >= n and b % n == 0:
+    nb_ = max([m for m in range(1, n + 1) if b % m == 0])  # batch chunks: the largest divisor of b up to n
+    if nb_ > 1:
+        n = nb_
         plan = [(slice(c * (b // n), (c + 1) * (b // n)), slice(0, lq)) for c in range(n)]
         by_batch = True
     elif b == 1 and lq >= n * 1024 and lq % (n * 256) == 0:
