@@ -356,6 +356,10 @@ __global__ void __launch_bounds__(256, 2) tpa_stage_tiles_kernel(const Params p,
 __global__ void __launch_bounds__(128) tpa_seg_ranges_kernel(const Params p, int4* ranges) {
   __shared__ int red[4][4];   // per warp: min/max of unit 0, min/max of unit 1
   __shared__ int first, last[2];
+  // one bit per key tile (walk order): set when the tile's keys do not all carry the block's one id
+  constexpr int kBitmapTiles = 8192;
+  __shared__ uint32_t odd_tile[kBitmapTiles / 32];
+  __shared__ int mixed;
   const int pair = blockIdx.x, batch = blockIdx.y, t = threadIdx.x;
   const int32_t* qs = p.q_seg + (int64_t)batch * p.q_seg_bstride;
   const int32_t* ks = p.kv_seg + (int64_t)batch * p.kv_seg_bstride;
@@ -371,13 +375,16 @@ __global__ void __launch_bounds__(128) tpa_seg_ranges_kernel(const Params p, int
   if ((t & 31) == 0) {
     red[t >> 5][0] = lo[0]; red[t >> 5][1] = hi[0]; red[t >> 5][2] = lo[1]; red[t >> 5][3] = hi[1];
   }
-  if (t == 0) { first = n_kv; last[0] = -1; last[1] = -1; }
+  if (t == 0) { first = n_kv; last[0] = -1; last[1] = -1; mixed = 0; }
+  for (int i = t; i < kBitmapTiles / 32; i += 128) odd_tile[i] = 0u;
   __syncthreads();
 #pragma unroll
   for (int u = 0; u < 2; ++u) {
     lo[u] = min(min(red[0][2 * u], red[1][2 * u]), min(red[2][2 * u], red[3][2 * u]));
     hi[u] = max(max(red[0][2 * u + 1], red[1][2 * u + 1]), max(red[2][2 * u + 1], red[3][2 * u + 1]));
   }
+  // do all rows of the block carry one id?  (an absent second unit has lo > hi)
+  const bool one_id = lo[0] == hi[0] && (lo[1] > hi[1] || (lo[1] == hi[1] && lo[1] == lo[0]));
   for (int tile = t; tile < n_kv; tile += 128) {  // `tile` counts in walk order
     const int key_tile = walk_to_key_tile(p, tile);
     const int4* src = reinterpret_cast<const int4*>(ks + kseg_offset(p, key_tile * kTileKv));
@@ -395,11 +402,27 @@ __global__ void __launch_bounds__(128) tpa_seg_ranges_kernel(const Params p, int
         atomicMax(&last[u], tile);
       }
     }
+    if (!(kmin == kmax && kmin == lo[0])) {
+      if (tile < kBitmapTiles) atomicOr(&odd_tile[tile >> 5], 1u << (tile & 31));
+      else mixed = 1;  // beyond the bitmap: no claim
+    }
+  }
+  __syncthreads();
+  // Uniform: one id on every row of the block and on every key of every tile it walks.  The
+  // attention kernel then drops the id handling for this block altogether (no key ids copied, no
+  // per-tile test): the all-zero ids a ring call must pass cost nothing.
+  const int f = first < n_kv ? first : 0;
+  const int e = max(f, max(last[0], last[1]) + 1);
+  for (int w = (f >> 5) + t; w <= ((e - 1) >> 5) && e > f && w < kBitmapTiles / 32; w += 128) {
+    uint32_t bits = odd_tile[w];
+    if (w == (f >> 5)) bits &= 0xffffffffu << (f & 31);
+    if (w == ((e - 1) >> 5) && ((e & 31) != 0)) bits &= 0xffffffffu >> (32 - (e & 31));
+    if (bits != 0u) mixed = 1;
   }
   __syncthreads();
   if (t == 0) {
-    const int f = first < n_kv ? first : 0;
-    ranges[(int64_t)batch * gridDim.x + pair] = make_int4(f, max(f, last[0] + 1), max(f, last[1] + 1), 0);
+    const int uniform = (one_id && mixed == 0) ? 1 : 0;
+    ranges[(int64_t)batch * gridDim.x + pair] = make_int4(f, max(f, last[0] + 1), max(f, last[1] + 1), uniform);
   }
 }
 
@@ -451,7 +474,7 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
   const int batch = slice / p.heads;
   const int q0 = pair * 2 * kUnitRows;
   const bool causal = (p.flags & TPA_FLAG_CAUSAL) != 0;
-  const bool has_seg = p.q_seg != nullptr;
+  bool has_seg = p.q_seg != nullptr;  // cleared below for a block whose rows and walked keys all carry one id
   const bool load_state = (p.flags & TPA_FLAG_STATE_LOAD) != 0;
   const bool store_state = (p.flags & TPA_FLAG_STATE_STORE) != 0;
 
@@ -486,6 +509,7 @@ tpa_fwd_sm100_kernel(const Params p, const uint8_t* ws_q, const uint8_t* ws_k, c
   }
   if (seg_ranges != nullptr) {
     const int4 r = seg_ranges[(int64_t)batch * pairs + pair];
+    if (r.w != 0) has_seg = false;
     j0 = max(j0, r.x);
     n_vis[0] = min(n_vis[0], r.y);
     n_vis[1] = min(n_vis[1], r.z);

@@ -313,6 +313,29 @@ def test_packed_sequences_walk_only_their_own_tiles(kernel, seg):
         assert run(dev(orc.segment_ids(1, t2, 1024))) < 0.6 * run(one)
 
 
+@pytest.mark.parametrize("odd_key", [None, 5, 700, 1023])
+def test_uniform_ids_are_dropped_only_when_every_walked_key_agrees(odd_key):
+    """All-equal ids (what a ring call passes) cost the tensor-core kernel nothing: a block whose
+    rows and walked key tiles carry one id runs without id handling.  One key with another id
+    anywhere in the walk must keep the element-wise test alive for the blocks that see it."""
+    b, t, h, d = 1, 1024, 8, 64
+    q, k, v = orc.make_factors(79, b, t, t, 2, 2, h, d, d)
+    tq, tk, tv = dev(q, torch.bfloat16), dev(k, torch.bfloat16), dev(v, torch.bfloat16)
+    ids = np.zeros((b, t), np.int32)
+    kids = ids.copy()
+    if odd_key is not None:
+        kids[:, odd_key] = 3
+    o, lse = tpa_b200.tpa.fwd_device(tq, tk, tv, h, dev(ids), dev(kids), d**-0.5, False, kernel="sm100_staged")
+    ref, lref = orc.tpa_reference_torch(tq.float().cpu(), tk.float().cpu(), tv.float().cpu(), h, torch.from_numpy(ids),
+                                        torch.from_numpy(kids), sm_scale=d**-0.5, causal=False, return_lse=True)
+    diff = (o.float().cpu() - ref).abs()
+    assert diff.max() <= 2e-2 and diff.mean() <= 5e-3
+    assert (lse.cpu() - lref).abs().max() <= 1e-2
+    if odd_key is not None:  # and the odd key really is excluded: the result differs from the id-free call
+        plain, _ = tpa_b200.tpa.fwd_device(tq, tk, tv, h, None, None, d**-0.5, False, kernel="sm100_staged")
+        assert (plain.float() - o.float()).abs().max() > 0
+
+
 @pytest.mark.parametrize("kernel", ["sm100_fused", "sm100_staged"])
 @pytest.mark.parametrize("lq,lk,h,causal", [(128, 4096, 8, False), (256, 8192, 16, True), (384, 2048, 8, True)])
 def test_few_queries_many_keys_split_over_ctas(kernel, lq, lk, h, causal):
