@@ -227,6 +227,15 @@ size_t tpa_bwd_workspace_bytes(const TpaBwdArgs* args);
 /* Bytes of scratch tpa_fwd needs for these arguments (0 is possible). */
 size_t tpa_fwd_workspace_bytes(const TpaFwdArgs* args);
 
+/* The least scratch tpa_fwd accepts for these arguments (no counterpart in the reference, whose Pallas
+ * call owns its scratch).  The staged tensor-core kernel keeps the rebuilt Q, K, V tiles of every head
+ * in the workspace (c3 on one GPU: 3.2 GB), which is the fast layout; given anything from this many
+ * bytes upwards it instead works through the heads in groups (multiples of 8) whose tiles fit, one
+ * group's staging and attention launches after the other's, at the price of a tail of idle SMs per
+ * group and a strided copy of o and lse.  Same results.  Equal to tpa_fwd_workspace_bytes() where
+ * grouping does not apply (other kernels, up to 8 heads, carried state, kept tiles). */
+size_t tpa_fwd_workspace_bytes_min(const TpaFwdArgs* args);
+
 /* Which kernel, tiles and grid tpa_fwd would use; TPA_OK or the error tpa_fwd would return. */
 int tpa_query_kernel(const TpaFwdArgs* args, TpaKernelInfo* info);
 

@@ -1,5 +1,6 @@
 // C ABI of libtpa_b200.so: argument validation, kernel choice, status reporting.
 // Declarations and the reference interfaces they replace are in include/tpa_b200.h.
+#include <algorithm>
 #include <atomic>
 #include <cstdio>
 #include <cstring>
@@ -110,6 +111,65 @@ constexpr size_t kStatusBytes = 256;  // status block at the head of every non-e
 
 static size_t round256(size_t n) { return (n + 255) & ~(size_t)255; }
 
+// ---- the staged forward with bounded scratch: head groups one after the other --------------------
+// A caller that passes less than tpa_fwd_workspace_bytes() (but at least tpa_fwd_workspace_bytes_min())
+// gets the same result from a workspace that holds the tiles of `hc` heads at a time: for each group
+// the staging launch and the attention launch run on that group's heads (the head factors are
+// offset pointers, everything else is unchanged), o and lse of the group go to a compact block
+// behind the tiles, and a strided device-to-device copy puts them at their heads' place in the
+// caller's arrays.  The kernels themselves are the ones every other call uses.
+static size_t esize(const Params& p) { return p.dtype == TPA_DTYPE_BF16 ? 2 : 4; }
+static Params group_params(const Params& p, int h0, int hc) {
+  Params g = p;
+  g.heads = hc;
+  const size_t es = esize(p);
+  g.qa.ptr = static_cast<const char*>(p.qa.ptr) + (size_t)h0 * es;
+  g.ka.ptr = static_cast<const char*>(p.ka.ptr) + (size_t)h0 * es;
+  g.va.ptr = static_cast<const char*>(p.va.ptr) + (size_t)h0 * es;
+  return g;
+}
+struct GroupLayout {
+  size_t o, lse, total;  // offsets behind the status block
+};
+static GroupLayout group_layout(const Params& p, int hc) {
+  GroupLayout l;
+  const Params g = group_params(p, 0, hc);
+  l.o = round256(sm100_workspace_bytes(g, TPA_KERNEL_SM100_STAGED));
+  l.lse = l.o + round256((size_t)p.batch * p.lq * hc * p.dv * esize(p));
+  l.total = l.lse + round256((size_t)p.batch * p.lq * hc * sizeof(float));
+  return l;
+}
+// largest head group (a multiple of 8, what one staging CTA rebuilds) whose scratch fits; 0 if none
+static int group_heads_for(const Params& p, size_t workspace_bytes) {
+  if (p.flags & (TPA_FLAG_STATE_LOAD | TPA_FLAG_STATE_STORE | TPA_FLAG_REUSE_STAGED_Q | TPA_FLAG_REUSE_STAGED_KV))
+    return 0;  // carried state and kept tiles belong to the one-pass layout
+  int best = 0;  // equal groups only: every group then has the scratch layout that was sized
+  for (int hc = 8; hc < p.heads; hc += 8)
+    if (p.heads % hc == 0 && kStatusBytes + group_layout(p, hc).total <= workspace_bytes) best = hc;
+  return best;
+}
+static cudaError_t launch_sm100_grouped(const Params& p, int hc, char* ws, cudaStream_t s) {
+  const GroupLayout l = group_layout(p, hc);
+  const size_t es = esize(p);
+  for (int h0 = 0; h0 < p.heads; h0 += hc) {
+    Params g = group_params(p, h0, std::min(hc, p.heads - h0));
+    g.o = ws + l.o;
+    g.lse = p.lse != nullptr ? reinterpret_cast<float*>(ws + l.lse) : nullptr;
+    cudaError_t e = launch_sm100(g, TPA_KERNEL_SM100_STAGED, ws, nullptr, false, s);
+    if (e != cudaSuccess) return e;
+    const size_t rows = (size_t)p.batch * p.lq;
+    e = cudaMemcpy2DAsync(static_cast<char*>(p.o) + (size_t)h0 * p.dv * es, (size_t)p.heads * p.dv * es, g.o,
+                          (size_t)g.heads * p.dv * es, (size_t)g.heads * p.dv * es, rows, cudaMemcpyDeviceToDevice, s);
+    if (e != cudaSuccess) return e;
+    if (p.lse != nullptr) {
+      e = cudaMemcpy2DAsync(p.lse + h0, (size_t)p.heads * sizeof(float), g.lse, (size_t)g.heads * sizeof(float),
+                            (size_t)g.heads * sizeof(float), rows, cudaMemcpyDeviceToDevice, s);
+      if (e != cudaSuccess) return e;
+    }
+  }
+  return cudaSuccess;
+}
+
 // Scratch of the backward: status block, delta, dense fp32 dQ / dK / dV.
 struct BwdLayout {
   size_t delta, dq, dk, dv, tc, total;  // tc: scratch of the tensor-core passes
@@ -190,6 +250,22 @@ size_t tpa_fwd_workspace_bytes(const TpaFwdArgs* args) {
   return kStatusBytes + sm100_workspace_bytes(p, kernel);
 }
 
+size_t tpa_fwd_workspace_bytes_min(const TpaFwdArgs* args) {
+  Params p;
+  int kernel;
+  if (validate(args, &p) != TPA_OK || choose(args, p, &kernel) != TPA_OK) return 0;
+  const size_t full = tpa_fwd_workspace_bytes(args);
+  if (kernel != TPA_KERNEL_SM100_STAGED || p.heads <= 8 ||
+      (p.flags & (TPA_FLAG_STATE_LOAD | TPA_FLAG_STATE_STORE | TPA_FLAG_REUSE_STAGED_Q | TPA_FLAG_REUSE_STAGED_KV)))
+    return full;
+  // not simply the smallest group: a small group of few row blocks splits its keys over CTAs and
+  // keeps the partials in scratch, which can outweigh the tiles it saves
+  size_t least = full;
+  for (int hc = 8; hc < p.heads; hc += 8)
+    if (p.heads % hc == 0) least = std::min(least, kStatusBytes + group_layout(p, hc).total);
+  return least;
+}
+
 int tpa_query_kernel(const TpaFwdArgs* args, TpaKernelInfo* info) {
   if (info == nullptr) return TPA_ERR_BAD_ARG;
   std::memset(info, 0, sizeof(*info));
@@ -217,12 +293,20 @@ int tpa_fwd(const TpaFwdArgs* args, void* workspace, size_t workspace_bytes, voi
   if (kernel != TPA_KERNEL_SIMT) {
     const size_t need = kStatusBytes + (kernel == TPA_KERNEL_DECODE ? decode_workspace_bytes(p)
                                                                      : sm100_workspace_bytes(p, kernel));
-    if (workspace == nullptr || workspace_bytes < need ||
-        (reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
-      return TPA_ERR_WORKSPACE;
+    if (workspace == nullptr || (reinterpret_cast<uintptr_t>(workspace) & 255) != 0) return TPA_ERR_WORKSPACE;
+    int group_heads = 0;
+    if (workspace_bytes < need) {
+      // less scratch than the one-pass layout: the staged kernel can still run head group by head group
+      if (kernel == TPA_KERNEL_SM100_STAGED) group_heads = group_heads_for(p, workspace_bytes);
+      if (group_heads == 0) return TPA_ERR_WORKSPACE;
+    }
     p.status = static_cast<uint32_t*>(workspace);
     e = cudaMemsetAsync(workspace, 0, kStatusBytes, s);
     if (e != cudaSuccess) return fail_cuda(e);
+    if (group_heads != 0) {
+      e = launch_sm100_grouped(p, group_heads, static_cast<char*>(workspace) + kStatusBytes, s);
+      return e == cudaSuccess ? TPA_OK : fail_cuda(e);
+    }
     e = kernel == TPA_KERNEL_DECODE
             ? launch_decode(p, static_cast<char*>(workspace) + kStatusBytes, nullptr, false, s)
             : launch_sm100(p, kernel, static_cast<char*>(workspace) + kStatusBytes, nullptr, false, s);

@@ -39,6 +39,7 @@ EXPORTS = (
     "tpa_fwd_static_scratch",
     "tpa_read_status_static_scratch",
     "tpa_fwd_workspace_bytes",
+    "tpa_fwd_workspace_bytes_min",
     "tpa_bwd",
     "tpa_bwd_workspace_bytes",
     "tpa_query_kernel",
@@ -144,6 +145,8 @@ def _load():
     lib.tpa_read_status_static_scratch.restype = C.c_int
     lib.tpa_fwd_workspace_bytes.argtypes = [C.POINTER(TpaFwdArgs)]
     lib.tpa_fwd_workspace_bytes.restype = C.c_size_t
+    lib.tpa_fwd_workspace_bytes_min.argtypes = [C.POINTER(TpaFwdArgs)]
+    lib.tpa_fwd_workspace_bytes_min.restype = C.c_size_t
     lib.tpa_bwd.argtypes = [C.POINTER(TpaBwdArgs), C.c_void_p, C.c_size_t, C.c_void_p]
     lib.tpa_bwd.restype = C.c_int
     lib.tpa_bwd_workspace_bytes.argtypes = [C.POINTER(TpaBwdArgs)]

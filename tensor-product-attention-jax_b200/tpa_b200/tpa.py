@@ -197,8 +197,13 @@ def fwd_device(
     rope=None,
     rope_q_offset=0,
     rope_k_offset=0,
+    workspace_limit=None,
 ):
     """One tpa_fwd call on CUDA tensors; returns (o, lse_fp32).
+
+    `workspace_limit` (bytes): give the call at most this much scratch.  The staged tensor-core
+    kernel then works through the heads in groups whose tiles fit (tpa_fwd_workspace_bytes_min is
+    the least it accepts); same result, some speed for memory.
 
     Beyond the reference (all off by default): `kv_parts` > 1 takes k, v as
     [parts, b, lk / parts, r, h + d] and key ids as [parts, b, lk / parts] -- the shards of a ring
@@ -266,6 +271,8 @@ def fwd_device(
 
     with torch.cuda.device(q.device):
         nbytes = _capi.lib.tpa_fwd_workspace_bytes(C.byref(a))
+        if workspace_limit is not None and workspace_limit < nbytes:
+            nbytes = max(_capi.lib.tpa_fwd_workspace_bytes_min(C.byref(a)), int(workspace_limit))
         ws = _workspace(q.device, nbytes)
         stream = torch.cuda.current_stream(q.device).cuda_stream
         # TPA_FLAG_REUSE_STAGED_Q / _KV are promises about the workspace's contents; keep them only

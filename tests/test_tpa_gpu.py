@@ -5,6 +5,8 @@ rtol = atol = 1e-3 (tpa/tpa_test.py:125) on the reference's own test matrix, whe
 tighter 2e-5 bound is also asserted; bf16 max-abs <= 2e-2 and mean-abs <= 5e-3.
 """
 
+import ctypes as C
+
 import numpy as np
 import pytest
 import torch
@@ -311,6 +313,38 @@ def test_packed_sequences_walk_only_their_own_tiles(kernel, seg):
             return e0.elapsed_time(e1)
         one = dev(np.zeros((1, t2), np.int32))
         assert run(dev(orc.segment_ids(1, t2, 1024))) < 0.6 * run(one)
+
+
+@pytest.mark.parametrize("d,seg,causal", [(128, 0, True), (64, 300, True), (128, 0, False)])
+def test_bounded_scratch_runs_head_groups_with_the_same_result(d, seg, causal):
+    """A workspace smaller than the one-pass layout: the staged kernel takes the heads in groups
+    whose tiles fit and copies each group's o / lse to its place; bitwise the one-pass result."""
+    b, t, h = 2, 1024, 32
+    q, k, v = orc.make_factors(80, b, t, t, 3, 2, h, d, d)
+    tq, tk, tv = dev(q, torch.bfloat16), dev(k, torch.bfloat16), dev(v, torch.bfloat16)
+    ids = dev(orc.segment_ids(b, t, seg)) if seg else None
+    a = _capi.TpaFwdArgs()
+    keep = tpa_b200.tpa._fill_operands(a, tq, tk, tv, h, ids, ids)
+    a.o, a.sm_scale, a.flags = 4096, d**-0.5, _capi.FLAG_CAUSAL if causal else 0
+    full = _capi.lib.tpa_fwd_workspace_bytes(C.byref(a))
+    least = _capi.lib.tpa_fwd_workspace_bytes_min(C.byref(a))
+    assert 0 < least < full, (least, full)
+    del keep
+    want, wl = tpa_b200.tpa.fwd_device(tq, tk, tv, h, ids, ids, d**-0.5, causal)
+    for limit in (least, (least + full) // 2):
+        n0 = _capi.lib.tpa_launch_count()
+        got, gl = tpa_b200.tpa.fwd_device(tq, tk, tv, h, ids, ids, d**-0.5, causal, workspace_limit=limit)
+        torch.cuda.synchronize()
+        assert _capi.lib.tpa_launch_count() - n0 >= 4  # at least two groups of staging + attention
+        assert torch.equal(torch.nan_to_num(want.float()), torch.nan_to_num(got.float())) and torch.equal(wl, gl)
+    # less than the least is refused
+    a2 = _capi.TpaFwdArgs()
+    keep = tpa_b200.tpa._fill_operands(a2, tq, tk, tv, h, ids, ids)
+    a2.o, a2.sm_scale = want.data_ptr(), d**-0.5
+    small = torch.empty(least, dtype=torch.uint8, device="cuda")
+    st = _capi.lib.tpa_fwd(C.byref(a2), small.data_ptr(), least - 256, None)
+    assert st == _capi.TPA_ERR_WORKSPACE, (st, least, full)
+    del keep
 
 
 @pytest.mark.parametrize("odd_key", [None, 5, 700, 1023])
