@@ -67,6 +67,40 @@ def test_whole_ring_in_one_call(dtype, kernel, d, n, seg, causal):
         assert torch.isfinite(lse).all()
 
 
+@pytest.mark.parametrize("dtype,kernel,d", [(torch.float32, "simt", 32), (torch.bfloat16, "sm100_staged", 64),
+                                            (torch.bfloat16, "sm100_staged", 128)])
+@pytest.mark.parametrize("n,seg,causal", [(4, 0, True), (8, 200, True), (3, 0, False)])
+def test_ring_as_own_shard_then_visiting_parts(dtype, kernel, d, n, seg, causal):
+    """What ring_tpa does on every rank: the rank's own shard first (the partial (o, lse) stays as
+    carried state), then the N - 1 visiting shards in ONE call as key parts that starts from that
+    state -- in arrival order, which the shard-local mask makes irrelevant.  Equals the N steps of
+    the reference's scan (tpa/ring_tpa.py:60-112)."""
+    b, l, h, rq, rk = 2, 256, 8, 3, 2
+    t = n * l
+    q, k, v = orc.make_factors(67, b, t, t, rq, rk, h, d, d)
+    tq, tk, tv = dev(q, dtype), dev(k, dtype), dev(v, dtype)
+    q, k, v = (x.float().cpu().numpy() for x in (tq, tk, tv))
+    ids = orc.segment_ids(b, t, seg) if seg else np.zeros((b, t), np.int32)
+    ref = orc.ring_tpa_reference(q, k, v, ids, ids, h, n, sm_scale=d**-0.5, causal=causal, mask_mode="reference_local",
+                                 dtype=np.float32)
+    tid = dev(ids)
+    for r in (0, n // 2, n - 1):
+        sl = slice(r * l, (r + 1) * l)
+        order = [(r - hop) % n for hop in range(1, n)]  # the shards in the order the hops deliver them
+        kp = torch.stack([tk[:, s * l:(s + 1) * l] for s in order]).contiguous()
+        vp = torch.stack([tv[:, s * l:(s + 1) * l] for s in order]).contiguous()
+        ip = torch.stack([tid[:, s * l:(s + 1) * l] for s in order]).contiguous()
+        qr, idr = tq[:, sl].contiguous(), tid[:, sl].contiguous()
+        state = (torch.empty((b, l, h, d), dtype=torch.float32, device="cuda"),
+                 torch.empty((b, l, h), dtype=torch.float32, device="cuda"))
+        tpa_b200.tpa.fwd_device(qr, tk[:, sl].contiguous(), tv[:, sl].contiguous(), h, idr, idr, d**-0.5, causal,
+                                state=state, store_state=True, kernel=kernel)
+        o, lse = tpa_b200.tpa.fwd_device(qr, kp, vp, h, idr, ip, d**-0.5, causal, kv_parts=n - 1, per_part=causal,
+                                         state=state, load_state=True, reuse_staged_q=True, kernel=kernel)
+        _cmp(o, ref[:, sl], dtype)
+        assert torch.isfinite(lse).all()
+
+
 @pytest.mark.parametrize("kernel,dtype", [("simt", torch.float32), ("sm100_staged", torch.bfloat16)])
 def test_parts_in_sequence_order_equal_one_array(kernel, dtype):
     """Without the part-local flag the parts are just the key array cut in pieces: same result as
